@@ -1,0 +1,391 @@
+// Memory-bound glue of the transformer layers: RMSNorm (zero-centred gain), the sandwich-norm
+// residual update, QK-norm + rotary embedding, the scaled token embedding, the judgment
+// head and the per-question candidate softmax.  All kernels move 16 bytes per thread per
+// access, keep a row in registers between the reduction and the write, and reduce with
+// warp shuffles; the roofline that bounds them is HBM bandwidth.
+#include "common.cuh"
+
+namespace {
+
+using namespace bg;
+
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 t = __bfloat1622float2(h[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+    uint4 v;
+    v.x = pack_bf16(f[0], f[1]);
+    v.y = pack_bf16(f[2], f[3]);
+    v.z = pack_bf16(f[4], f[5]);
+    v.w = pack_bf16(f[6], f[7]);
+    return v;
+}
+__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// Block-wide sum; every thread receives the total.  `scratch` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();   // scratch may still be read from a previous reduction
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = lane < warps ? scratch[lane] : 0.f;
+    return warp_sum(t);
+}
+
+// out = rmsnorm(x) * (1 + w).  One block per row, one 16-byte chunk per thread.
+// Restates transformers T5Gemma2RMSNorm (modeling_t5gemma2.py:61-69): fp32 math, the gain is
+// applied before the result is rounded to bf16.
+__global__ void rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const __nv_bfloat16* __restrict__ w,
+                               __nv_bfloat16* __restrict__ out, int64_t ldo, int h, float eps) {
+    __shared__ float scratch[33];
+    const int64_t row = blockIdx.x;
+    const int c = threadIdx.x * 8;
+    float f[8];
+    const bool active = c < h;
+    float ss = 0.f;
+    if (active) {
+        unpack8(*reinterpret_cast<const uint4*>(x + row * ldx + c), f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+    }
+    const float r = rsqrtf(block_sum(ss, scratch) / float(h) + eps);
+    if (active) {
+        float g[8];
+        unpack8(*reinterpret_cast<const uint4*>(w + c), g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = f[i] * r * (1.f + g[i]);
+        *reinterpret_cast<uint4*>(out + row * ldo + c) = pack8(f);
+    }
+}
+
+// Sandwich-norm residual update fused with the next pre-norm:
+//   resid <- resid + bf16(rmsnorm(y) * (1 + w_post));   normed <- rmsnorm(resid) * (1 + w_next)
+// (transformers modeling_t5gemma2.py:496-502: post-norm, residual add, then the next block's
+// pre-norm).  The rounding points of the bf16 module chain are kept: the post-norm output
+// and the updated residual are each rounded to bf16 before they are used again.
+// w_next == nullptr skips the second norm.
+__global__ void add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ w_post,
+                                   __nv_bfloat16* __restrict__ resid, const __nv_bfloat16* __restrict__ w_next,
+                                   __nv_bfloat16* __restrict__ normed, int h, float eps) {
+    __shared__ float scratch[33];
+    const int64_t row = blockIdx.x;
+    const int c = threadIdx.x * 8;
+    const bool active = c < h;
+    float f[8], x[8];
+    float ss = 0.f;
+    if (active) {
+        unpack8(*reinterpret_cast<const uint4*>(y + row * h + c), f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+    }
+    float r = rsqrtf(block_sum(ss, scratch) / float(h) + eps);
+    ss = 0.f;
+    if (active) {
+        float g[8];
+        unpack8(*reinterpret_cast<const uint4*>(w_post + c), g);
+        unpack8(*reinterpret_cast<const uint4*>(resid + row * h + c), x);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            x[i] = round_bf16(x[i] + round_bf16(f[i] * r * (1.f + g[i])));
+            ss += x[i] * x[i];
+        }
+        *reinterpret_cast<uint4*>(resid + row * h + c) = pack8(x);
+    }
+    if (w_next == nullptr) return;
+    r = rsqrtf(block_sum(ss, scratch) / float(h) + eps);
+    if (active) {
+        float g[8];
+        unpack8(*reinterpret_cast<const uint4*>(w_next + c), g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = x[i] * r * (1.f + g[i]);
+        *reinterpret_cast<uint4*>(normed + row * h + c) = pack8(x);
+    }
+}
+
+// QK-norm + RoPE in place.  One warp per token walks that token's query heads and key heads:
+// per head an fp32 RMSNorm over head_dim with (1 + w) gain, then rotate-half RoPE with the
+// angle position * inv_freq[i mod D/2] (bongard/attention.py:172-180; the fused form follows
+// bongard/qk_norm_rope.metal:4-33: partner j = (i + D/2) mod D, sign - for i < D/2).
+// Lane l owns elements [l*D/32, (l+1)*D/32): its rotation partner lives in lane l ^ 16.
+// rotate == 0 leaves out the rotation (decoder state keys: bongard/model.py:135-139).
+template <int D>
+__global__ void qk_norm_rope_kernel(__nv_bfloat16* __restrict__ q, int64_t ldq, int q_heads,
+                                    __nv_bfloat16* __restrict__ k, int64_t ldk, int k_heads,
+                                    const __nv_bfloat16* __restrict__ qw, const __nv_bfloat16* __restrict__ kw,
+                                    const int32_t* __restrict__ positions, const float* __restrict__ inv_freq,
+                                    int64_t tokens, float eps, int rotate) {
+    constexpr int E = D / 32;  // elements per lane
+    const int lane = threadIdx.x & 31;
+    const int64_t token = int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (token >= tokens) return;
+    float cs[E], sn[E];
+    if (rotate) {
+        const float pos = float(positions[token]);
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            const int i = (lane * E + e) & (D / 2 - 1);
+            sincosf(pos * inv_freq[i], &sn[e], &cs[e]);
+        }
+    }
+    const float sign = lane < 16 ? -1.f : 1.f;
+    for (int head = 0; head < q_heads + k_heads; ++head) {
+        const bool is_q = head < q_heads;
+        if (!is_q && k == nullptr) break;
+        __nv_bfloat16* p = is_q ? q + token * ldq + head * D : k + token * ldk + (head - q_heads) * D;
+        const __nv_bfloat16* w = is_q ? qw : kw;
+        p += lane * E;
+        float f[E], g[E];
+        if constexpr (E == 8) {
+            unpack8(*reinterpret_cast<const uint4*>(p), f);
+            unpack8(*reinterpret_cast<const uint4*>(w + lane * E), g);
+        } else {
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+                f[e] = __bfloat162float(p[e]);
+                g[e] = __bfloat162float(w[lane * E + e]);
+            }
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < E; ++e) ss += f[e] * f[e];
+        const float r = rsqrtf(warp_sum(ss) / float(D) + eps);
+#pragma unroll
+        for (int e = 0; e < E; ++e) f[e] = f[e] * r * (1.f + g[e]);
+        if (rotate) {
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+                const float other = __shfl_xor_sync(0xffffffffu, f[e], 16);
+                g[e] = f[e] * cs[e] + sign * other * sn[e];
+            }
+#pragma unroll
+            for (int e = 0; e < E; ++e) f[e] = g[e];
+        }
+        if constexpr (E == 8) {
+            *reinterpret_cast<uint4*>(p) = pack8(f);
+        } else {
+#pragma unroll
+            for (int e = 0; e < E; ++e) p[e] = __float2bfloat16_rn(f[e]);
+        }
+    }
+}
+
+// Scaled word embedding with the end-of-image override (transformers modeling_t5gemma2.py:644-647).
+__global__ void embed_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
+                             const __nv_bfloat16* __restrict__ eoi, __nv_bfloat16* __restrict__ out, int h,
+                             float scale, int64_t eoi_token, int64_t vocab) {
+    const int64_t row = blockIdx.x;
+    const int c = threadIdx.x * 8;
+    if (c >= h) return;
+    int64_t id = ids[row];
+    uint4 v;
+    if (id == eoi_token) {
+        v = *reinterpret_cast<const uint4*>(eoi + c);
+    } else {
+        if (id < 0 || id >= vocab) id = 0;
+        float f[8];
+        unpack8(*reinterpret_cast<const uint4*>(table + id * h + c), f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] *= scale;
+        v = pack8(f);
+    }
+    *reinterpret_cast<uint4*>(out + row * h + c) = v;
+}
+
+// Judgment head (bongard/model.py:92-95): logit = w.h + (C h).(G g) / sqrt(rank).
+// One block per candidate; thread j < rank owns row j of C and G.  fp32 throughout.
+__global__ void judgment_head_kernel(const __nv_bfloat16* __restrict__ hidden, int64_t ldh,
+                                     const int32_t* __restrict__ cand_rows, const int32_t* __restrict__ dec_rows,
+                                     const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ cmat,
+                                     const __nv_bfloat16* __restrict__ gmat, float* __restrict__ logits, int h,
+                                     int rank) {
+    extern __shared__ float sh[];      // h floats of the candidate row, h floats of the decision row
+    __shared__ float scratch[33];
+    float* hc = sh;
+    float* hg = sh + h;
+    const int cand = blockIdx.x;
+    const __nv_bfloat16* pc = hidden + int64_t(cand_rows[cand]) * ldh;
+    const __nv_bfloat16* pg = hidden + int64_t(dec_rows[cand]) * ldh;
+    for (int i = threadIdx.x; i < h; i += blockDim.x) {
+        hc[i] = __bfloat162float(pc[i]);
+        hg[i] = __bfloat162float(pg[i]);
+    }
+    __syncthreads();
+    float acc = 0.f;
+    for (int j = threadIdx.x; j < rank; j += blockDim.x) {
+        const __nv_bfloat16* cr = cmat + int64_t(j) * h;
+        const __nv_bfloat16* gr = gmat + int64_t(j) * h;
+        float a = 0.f, b = 0.f;
+        for (int i = 0; i < h; i += 8) {
+            float fc[8], fg[8];
+            unpack8(*reinterpret_cast<const uint4*>(cr + i), fc);
+            unpack8(*reinterpret_cast<const uint4*>(gr + i), fg);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                a += fc[e] * hc[i + e];
+                b += fg[e] * hg[i + e];
+            }
+        }
+        acc += a * b;
+    }
+    acc *= rsqrtf(float(rank));
+    for (int i = threadIdx.x; i < h; i += blockDim.x) acc += __bfloat162float(w[i]) * hc[i];
+    const float total = block_sum(acc, scratch);
+    if (threadIdx.x == 0) logits[cand] = total;
+}
+
+// Per-question temperature softmax in float64 (bongard/inference.py:54-73), one thread per question.
+__global__ void candidate_softmax_kernel(const float* __restrict__ logits, const int32_t* __restrict__ offsets,
+                                         double* __restrict__ probs, int questions, double temperature) {
+    const int q = blockIdx.x * blockDim.x + threadIdx.x;
+    if (q >= questions) return;
+    const int lo = offsets[q], hi = offsets[q + 1];
+    if (hi <= lo) return;
+    double zmax = -INFINITY;
+    for (int i = lo; i < hi; ++i) {
+        double z = double(logits[i]);
+        if (temperature >= 1.0) z /= temperature;
+        zmax = fmax(zmax, z);
+    }
+    double sum = 0.0;
+    for (int i = lo; i < hi; ++i) {
+        double z = double(logits[i]);
+        z = temperature >= 1.0 ? z / temperature - zmax : (z - zmax) / temperature;
+        const double e = exp(z);
+        probs[i] = e;
+        sum += e;
+    }
+    double total = 0.0;
+    for (int i = lo; i < hi; ++i) {
+        probs[i] /= sum;
+        total += probs[i];
+    }
+    for (int i = lo; i < hi; ++i) probs[i] /= total;
+}
+
+int check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        bg_set_error("%s: launch: %s", what, cudaGetErrorString(e));
+        return BG_ERR_LAUNCH;
+    }
+    return BG_OK;
+}
+
+int row_threads(int64_t h) { return int(((h / 8 + 31) / 32) * 32); }
+
+}  // namespace
+
+extern "C" {
+
+int bg_rmsnorm(const void* x, int64_t ldx, const void* w, void* out, int64_t ldo, int64_t rows, int64_t h,
+               float eps, void* stream) {
+    if (rows < 0 || h <= 0 || h % 8 || h > 8192 || ldx % 8 || ldo % 8) {
+        bg_set_error("bg_rmsnorm: hidden size must be a multiple of 8 up to 8192 (got %lld)", (long long)h);
+        return BG_ERR_SHAPE;
+    }
+    if (rows == 0) return BG_OK;
+    rmsnorm_kernel<<<(unsigned)rows, row_threads(h), 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(w),
+        static_cast<__nv_bfloat16*>(out), ldo, (int)h, eps);
+    return check_launch("bg_rmsnorm");
+}
+
+int bg_add_rmsnorm(const void* y, const void* w_post, void* resid, const void* w_next, void* normed, int64_t rows,
+                   int64_t h, float eps, void* stream) {
+    if (rows < 0 || h <= 0 || h % 8 || h > 8192) {
+        bg_set_error("bg_add_rmsnorm: hidden size must be a multiple of 8 up to 8192 (got %lld)", (long long)h);
+        return BG_ERR_SHAPE;
+    }
+    if (rows == 0) return BG_OK;
+    add_rmsnorm_kernel<<<(unsigned)rows, row_threads(h), 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(w_post),
+        static_cast<__nv_bfloat16*>(resid), static_cast<const __nv_bfloat16*>(w_next),
+        static_cast<__nv_bfloat16*>(normed), (int)h, eps);
+    return check_launch("bg_add_rmsnorm");
+}
+
+int bg_qk_norm_rope(void* q, int64_t ldq, int q_heads, void* k, int64_t ldk, int k_heads, const void* q_weight,
+                    const void* k_weight, const int32_t* positions, const float* inv_freq, int64_t tokens,
+                    int head_dim, float eps, int rotate, void* stream) {
+    if (tokens < 0 || (head_dim != 64 && head_dim != 128 && head_dim != 256) || q_heads < 0 || k_heads < 0) {
+        bg_set_error("bg_qk_norm_rope: head_dim must be 64, 128 or 256 (got %d)", head_dim);
+        return BG_ERR_SHAPE;
+    }
+    if (ldq % 8 || ldk % 8) {
+        bg_set_error("bg_qk_norm_rope: token strides must be multiples of 8 elements");
+        return BG_ERR_ALIGN;
+    }
+    if (tokens == 0) return BG_OK;
+    const int warps = 4;
+    const unsigned grid = (unsigned)((tokens + warps - 1) / warps);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    auto* qp = static_cast<__nv_bfloat16*>(q);
+    auto* kp = static_cast<__nv_bfloat16*>(k);
+    auto* qw = static_cast<const __nv_bfloat16*>(q_weight);
+    auto* kw = static_cast<const __nv_bfloat16*>(k_weight);
+    if (qp == nullptr) q_heads = 0;
+    if (head_dim == 64)
+        qk_norm_rope_kernel<64><<<grid, warps * 32, 0, s>>>(qp, ldq, q_heads, kp, ldk, k_heads, qw, kw, positions,
+                                                             inv_freq, tokens, eps, rotate);
+    else if (head_dim == 128)
+        qk_norm_rope_kernel<128><<<grid, warps * 32, 0, s>>>(qp, ldq, q_heads, kp, ldk, k_heads, qw, kw, positions,
+                                                              inv_freq, tokens, eps, rotate);
+    else
+        qk_norm_rope_kernel<256><<<grid, warps * 32, 0, s>>>(qp, ldq, q_heads, kp, ldk, k_heads, qw, kw, positions,
+                                                              inv_freq, tokens, eps, rotate);
+    return check_launch("bg_qk_norm_rope");
+}
+
+int bg_embed(const int64_t* ids, const void* table, const void* eoi_embedding, void* out, int64_t rows, int64_t h,
+             float scale, int64_t eoi_token, int64_t vocab, void* stream) {
+    if (rows < 0 || h <= 0 || h % 8 || h > 8192) {
+        bg_set_error("bg_embed: hidden size must be a multiple of 8 up to 8192");
+        return BG_ERR_SHAPE;
+    }
+    if (rows == 0) return BG_OK;
+    embed_kernel<<<(unsigned)rows, row_threads(h), 0, static_cast<cudaStream_t>(stream)>>>(
+        ids, static_cast<const __nv_bfloat16*>(table), static_cast<const __nv_bfloat16*>(eoi_embedding),
+        static_cast<__nv_bfloat16*>(out), (int)h, scale, eoi_token, vocab);
+    return check_launch("bg_embed");
+}
+
+int bg_judgment_head(const void* hidden, int64_t ldh, const int32_t* cand_rows, const int32_t* dec_rows,
+                     const void* w, const void* cmat, const void* gmat, float* logits, int64_t candidates, int64_t h,
+                     int rank, void* stream) {
+    if (candidates < 0 || h <= 0 || h % 8 || rank <= 0 || 2 * h * sizeof(float) > 96 * 1024) {
+        bg_set_error("bg_judgment_head: bad shape");
+        return BG_ERR_SHAPE;
+    }
+    if (candidates == 0) return BG_OK;
+    const size_t smem = 2 * h * sizeof(float);
+    static bool configured = false;
+    if (!configured && smem > 48 * 1024) {
+        cudaFuncSetAttribute(judgment_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        configured = true;
+    }
+    judgment_head_kernel<<<(unsigned)candidates, 256, smem, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(hidden), ldh, cand_rows, dec_rows, static_cast<const __nv_bfloat16*>(w),
+        static_cast<const __nv_bfloat16*>(cmat), static_cast<const __nv_bfloat16*>(gmat), logits, (int)h, rank);
+    return check_launch("bg_judgment_head");
+}
+
+int bg_candidate_softmax(const float* logits, const int32_t* offsets, double* probs, int64_t questions,
+                         double temperature, void* stream) {
+    if (questions < 0 || !(temperature > 0.0)) {
+        bg_set_error("bg_candidate_softmax: temperature must be finite and positive");
+        return BG_ERR_SHAPE;
+    }
+    if (questions == 0) return BG_OK;
+    candidate_softmax_kernel<<<(unsigned)((questions + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        logits, offsets, probs, (int)questions, temperature);
+    return check_launch("bg_candidate_softmax");
+}
+
+}  // extern "C"

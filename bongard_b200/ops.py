@@ -1,0 +1,303 @@
+"""Torch-tensor front end of the C ABI: each function borrows device pointers from its
+arguments, launches on torch's current stream and returns torch tensors.  Nothing here
+computes on the host and nothing falls back to PyTorch arithmetic."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from functools import lru_cache
+
+import numpy as np
+import torch
+
+from . import _lib
+
+BF16 = torch.bfloat16
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def _need(t, name, dtype=BF16):
+    if not t.is_cuda:
+        raise ValueError(f'{name} must live on a CUDA device (there is no CPU path)')
+    if t.dtype != dtype:
+        raise ValueError(f'{name} must be {dtype}, got {t.dtype}')
+    return t
+
+
+def _rows(t, name):
+    """View [..., h] as rows with one stride; returns (tensor, rows, h, row_stride)."""
+    _need(t, name)
+    if t.stride(-1) != 1:
+        raise ValueError(f'{name} must be contiguous in its last dimension')
+    flat = t.reshape(-1, t.shape[-1])
+    return flat, flat.shape[0], flat.shape[1], (flat.stride(0) if flat.shape[0] > 1 else flat.shape[1])
+
+
+def device_check():
+    lib = _lib.load()
+    _lib.check(lib.bg_device_check(), 'bg_device_check')
+
+
+def read_status():
+    """Synchronise the current stream and raise if a bounded device wait ran out."""
+    lib = _lib.load()
+    code = lib.bg_read_status(_stream())
+    if code != 0:
+        raise _lib.B200Error(f'device status {code}: {lib.bg_last_error_string().decode()}')
+
+
+def rmsnorm(x, weight, eps=1e-6):
+    lib = _lib.load()
+    flat, rows, h, ldx = _rows(x, 'x')
+    out = torch.empty((rows, h), device=x.device, dtype=BF16)
+    _lib.check(lib.bg_rmsnorm(_ptr(flat), ldx, _ptr(_need(weight, 'weight')), _ptr(out), h, rows, h, eps, _stream()),
+               'bg_rmsnorm')
+    return out.view(x.shape)
+
+
+def add_rmsnorm_(y, w_post, resid, w_next=None, eps=1e-6):
+    """resid += rmsnorm(y)*(1+w_post) in place; returns rmsnorm(resid)*(1+w_next) or None."""
+    lib = _lib.load()
+    _need(y, 'y'), _need(resid, 'resid')
+    if not (y.is_contiguous() and resid.is_contiguous()) or y.shape != resid.shape:
+        raise ValueError('y and resid must be contiguous and of equal shape')
+    h = y.shape[-1]
+    rows = y.numel() // h
+    normed = torch.empty_like(resid) if w_next is not None else None
+    _lib.check(lib.bg_add_rmsnorm(_ptr(y), _ptr(_need(w_post, 'w_post')), _ptr(resid), _ptr(w_next), _ptr(normed),
+                                  rows, h, eps, _stream()), 'bg_add_rmsnorm')
+    return normed
+
+
+@lru_cache(maxsize=32)
+def inv_freq(head_dim, theta, device):
+    """theta^(-2i/D) in fp32, computed the way the rotary module does
+    (transformers modeling_t5gemma2.py:147-150)."""
+    value = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.int64).float() / head_dim))
+    return value.to(device)
+
+
+def qk_norm_rope_(q, k, q_weight, k_weight, positions, freqs, eps=1e-6, rotate=True):
+    """In place on q [T,Hq,D] and k [T,Hkv,D] (views with a token stride are fine)."""
+    lib = _lib.load()
+    ref = q if q is not None else k
+    tokens, head_dim = ref.shape[0], ref.shape[-1]
+    for t, name in ((q, 'q'), (k, 'k')):
+        if t is not None:
+            _need(t, name)
+            if t.stride(-1) != 1 or t.stride(1) != head_dim:
+                raise ValueError(f'{name} heads must be contiguous [T, heads, D]')
+    if rotate:
+        _need(positions, 'positions', torch.int32), _need(freqs, 'inv_freq', torch.float32)
+    _lib.check(lib.bg_qk_norm_rope(
+        _ptr(q), q.stride(0) if q is not None else 0, q.shape[1] if q is not None else 0,
+        _ptr(k), k.stride(0) if k is not None else 0, k.shape[1] if k is not None else 0,
+        _ptr(q_weight), _ptr(k_weight), _ptr(positions) if rotate else 0, _ptr(freqs) if rotate else 0,
+        tokens, head_dim, eps, 1 if rotate else 0, _stream()), 'bg_qk_norm_rope')
+
+
+def embed(ids, table, eoi_embedding, scale, eoi_token=256_000):
+    lib = _lib.load()
+    _need(ids, 'ids', torch.int64), _need(table, 'table')
+    ids = ids.reshape(-1).contiguous()
+    out = torch.empty((ids.numel(), table.shape[1]), device=table.device, dtype=BF16)
+    _lib.check(lib.bg_embed(_ptr(ids), _ptr(table), _ptr(_need(eoi_embedding, 'eoi_embedding')), _ptr(out),
+                            ids.numel(), table.shape[1], scale, eoi_token, table.shape[0], _stream()), 'bg_embed')
+    return out
+
+
+def linear(x, weight, out=None):
+    """x [..., K] @ weight[N, K].T -> [..., N] on the tensor cores."""
+    lib = _lib.load()
+    flat, m, k, lda = _rows(x, 'x')
+    _need(weight, 'weight')
+    if weight.ndim != 2 or weight.shape[1] != k or weight.stride(1) != 1:
+        raise ValueError(f'weight must be [N, {k}] with contiguous rows')
+    n = weight.shape[0]
+    if out is None:
+        out = torch.empty((m, n), device=x.device, dtype=BF16)
+    _lib.check(lib.bg_gemm_bf16(_ptr(flat), lda, _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), m, n, k, 0,
+                                _stream()), 'bg_gemm_bf16')
+    return out.view(*x.shape[:-1], n)
+
+
+def linear_geglu(x, gate_up):
+    """gelu_tanh(x @ gate.T) * (x @ up.T) with gate_up = cat([gate, up]) of shape [2I, K]."""
+    lib = _lib.load()
+    flat, m, k, lda = _rows(x, 'x')
+    _need(gate_up, 'gate_up')
+    if gate_up.ndim != 2 or gate_up.shape[1] != k or gate_up.shape[0] % 2 or gate_up.stride(1) != 1:
+        raise ValueError(f'gate_up must be [2I, {k}] with contiguous rows')
+    n = gate_up.shape[0] // 2
+    out = torch.empty((m, n), device=x.device, dtype=BF16)
+    _lib.check(lib.bg_gemm_bf16(_ptr(flat), lda, _ptr(gate_up), gate_up.stride(0), _ptr(out), n, m, n, k, 1,
+                                _stream()), 'bg_gemm_bf16')
+    return out.view(*x.shape[:-1], n)
+
+
+# --------------------------------------------------------------------------------------
+# packed variable-length attention
+# --------------------------------------------------------------------------------------
+
+@dataclass
+class AttentionPlan:
+    """Device-side description of one pack for bg_varlen_attention: query tiles (heaviest
+    first) and every token's own-key range.  Built once per pack and window, shared by all
+    layers with that window."""
+
+    tiles: torch.Tensor      # int32 [n_tiles, 8]
+    row_lo: torch.Tensor     # int32 [T]
+    row_hi: torch.Tensor     # int32 [T]
+    tokens: int
+    n_tiles: int
+    pairs: int               # visible (query, key) pairs, for FLOP accounting
+
+
+def plan_rows(lengths, window, *, decoder):
+    """Own-key range [lo, hi) of every packed token (numpy int64).
+
+    Encoder: the segment, clipped to the bidirectional window with the odd-width rule
+    (key visible iff 0 <= d < (w+1)//2 or 0 < -d < w//2+1, d = query - key position;
+    bongard/packing.py:131-133).  Decoder: causal, optionally windowed (0 <= d < w;
+    bongard/packing.py:122-125)."""
+    lengths = np.asarray(lengths, dtype=np.int64)
+    ends = np.cumsum(lengths)
+    starts = ends - lengths
+    seg_start = np.repeat(starts, lengths)
+    seg_end = np.repeat(ends, lengths)
+    t = np.arange(int(ends[-1]) if len(ends) else 0, dtype=np.int64)
+    if decoder:
+        lo = seg_start if window is None else np.maximum(seg_start, t - window + 1)
+        hi = t + 1
+    elif window is None:
+        lo, hi = seg_start, seg_end
+    else:
+        lo = np.maximum(seg_start, t - (window + 1) // 2 + 1)
+        hi = np.minimum(seg_end, t + window // 2 + 1)
+    return lo, hi
+
+
+def make_plan(lengths, window, device, *, group, owners=None, state_lengths=None):
+    """Tile a pack of segments for the attention kernel.
+
+    Encoder (owners None): tiles never cross a segment.  Decoder: consecutive questions of the
+    same owner form one run; a tile is up to 128/group consecutive tokens of a run, so
+    questions that share a state also share its key stream."""
+    lengths = [int(n) for n in lengths]
+    decoder = owners is not None
+    lo, hi = plan_rows(lengths, window, decoder=decoder)
+    total = len(lo)
+    tq = 128 // group
+    runs = []      # (start, end, prefix_start, prefix_len)
+    offset = 0
+    if decoder:
+        state_offsets = np.concatenate(([0], np.cumsum(np.asarray(state_lengths, dtype=np.int64))))
+        for n, owner in zip(lengths, owners):
+            if runs and runs[-1][4] == owner:
+                runs[-1][1] = offset + n
+            else:
+                runs.append([offset, offset + n, int(state_offsets[owner]), int(state_lengths[owner]), owner])
+            offset += n
+    else:
+        for n in lengths:
+            runs.append([offset, offset + n, 0, 0, -1])
+            offset += n
+    q_start, q_count, pre_start, pre_len = [], [], [], []
+    for start, end, ps, pl, _ in runs:
+        s = np.arange(start, end, tq, dtype=np.int64)
+        q_start.append(s)
+        q_count.append(np.minimum(end - s, tq))
+        pre_start.append(np.full(len(s), ps, dtype=np.int64))
+        pre_len.append(np.full(len(s), pl, dtype=np.int64))
+    if not q_start or total == 0:
+        empty = torch.zeros((0, 8), dtype=torch.int32, device=device)
+        z = torch.zeros(0, dtype=torch.int32, device=device)
+        return AttentionPlan(empty, z, z, 0, 0, 0)
+    q_start, q_count = np.concatenate(q_start), np.concatenate(q_count)
+    pre_start, pre_len = np.concatenate(pre_start), np.concatenate(pre_len)
+    keep = q_count > 0
+    q_start, q_count, pre_start, pre_len = q_start[keep], q_count[keep], pre_start[keep], pre_len[keep]
+    order = np.argsort(q_start, kind='stable')
+    q_start, q_count, pre_start, pre_len = q_start[order], q_count[order], pre_start[order], pre_len[order]
+    own_lo = np.minimum.reduceat(lo, q_start)
+    own_hi = np.maximum.reduceat(hi, q_start)
+    lo_max = np.maximum.reduceat(lo, q_start)
+    hi_min = np.minimum.reduceat(hi, q_start)
+    tiles = np.stack([q_start, q_count, own_lo, own_hi, lo_max, hi_min, pre_start, pre_len], axis=1)
+    work = pre_len + own_hi - own_lo
+    tiles = tiles[np.argsort(-work, kind='stable')].astype(np.int32)
+    packed = np.concatenate([tiles.reshape(-1), lo.astype(np.int32), hi.astype(np.int32)])
+    dev = torch.from_numpy(packed).to(device, non_blocking=True)
+    n8 = tiles.shape[0] * 8
+    pairs = int((hi - lo).sum())
+    if decoder:
+        pairs += int(sum(n * state_lengths[o] for n, o in zip(lengths, owners)))
+    return AttentionPlan(dev[:n8].view(-1, 8), dev[n8:n8 + total], dev[n8 + total:], total, tiles.shape[0], pairs)
+
+
+def varlen_attention(q, k, v, plan, scale, cross=None, return_lse=False):
+    """q [T,Hq,D], k/v [T,Hkv,D] (token-strided views allowed), cross = (ck, cv) [S,Hkv,D].
+    Returns out [T, Hq*D] (and lse [Hq,T] fp32)."""
+    lib = _lib.load()
+    for t, name in ((q, 'q'), (k, 'k'), (v, 'v')):
+        _need(t, name)
+        if t.ndim != 3 or t.stride(2) != 1 or t.stride(1) != t.shape[2]:
+            raise ValueError(f'{name} must be [T, heads, D] with contiguous heads')
+    if k.stride(0) != v.stride(0) or k.shape != v.shape:
+        raise ValueError('k and v must share shape and token stride')
+    tq, hq, d = q.shape
+    tk, hkv = k.shape[0], k.shape[1]
+    if plan.tokens != tq:
+        raise ValueError(f'plan was built for {plan.tokens} tokens, q has {tq}')
+    ck = cv = None
+    ts = ldc = 0
+    if cross is not None:
+        ck, cv = cross
+        _need(ck, 'cross keys'), _need(cv, 'cross values')
+        if ck.shape != cv.shape or ck.stride(0) != cv.stride(0) or ck.shape[1:] != k.shape[1:] \
+                or ck.stride(2) != 1 or ck.stride(1) != d:
+            raise ValueError('cross keys/values must be [S, kv_heads, D] with one token stride')
+        ts, ldc = ck.shape[0], ck.stride(0)
+    out = torch.empty((tq, hq * d), device=q.device, dtype=BF16)
+    lse = torch.empty((hq, tq), device=q.device, dtype=torch.float32) if return_lse else None
+    _lib.check(lib.bg_varlen_attention(
+        _ptr(q), q.stride(0), _ptr(k), _ptr(v), k.stride(0), _ptr(ck), _ptr(cv), ldc, _ptr(out), _ptr(lse),
+        _ptr(plan.tiles), plan.n_tiles, _ptr(plan.row_lo), _ptr(plan.row_hi), tq, tk, ts, hq, hkv, d,
+        float(scale), _stream()), 'bg_varlen_attention')
+    return (out, lse) if return_lse else out
+
+
+# --------------------------------------------------------------------------------------
+# judgment head
+# --------------------------------------------------------------------------------------
+
+def judgment_head(hidden, cand_rows, dec_rows, w, candidate, global_readout):
+    lib = _lib.load()
+    _need(hidden, 'hidden'), _need(cand_rows, 'cand_rows', torch.int32), _need(dec_rows, 'dec_rows', torch.int32)
+    for t in (w, candidate, global_readout):
+        _need(t, 'head weight')
+        if not t.is_contiguous():
+            raise ValueError('head weights must be contiguous')
+    n = cand_rows.numel()
+    logits = torch.empty(n, device=hidden.device, dtype=torch.float32)
+    _lib.check(lib.bg_judgment_head(_ptr(hidden), hidden.stride(0), _ptr(cand_rows), _ptr(dec_rows), _ptr(w),
+                                    _ptr(candidate), _ptr(global_readout), _ptr(logits), n, hidden.shape[1],
+                                    candidate.shape[0], _stream()), 'bg_judgment_head')
+    return logits
+
+
+def candidate_softmax(logits, offsets, temperature=1.0):
+    """Per-question float64 probabilities; question i owns logits[offsets[i]:offsets[i+1]]."""
+    lib = _lib.load()
+    _need(logits, 'logits', torch.float32), _need(offsets, 'offsets', torch.int32)
+    probs = torch.empty(logits.numel(), device=logits.device, dtype=torch.float64)
+    _lib.check(lib.bg_candidate_softmax(_ptr(logits), _ptr(offsets), _ptr(probs), offsets.numel() - 1,
+                                        float(temperature), _stream()), 'bg_candidate_softmax')
+    return probs

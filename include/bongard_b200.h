@@ -1,0 +1,113 @@
+/* libbongard_b200 - C ABI of the B200 (sm_100a) kernels behind bongard's transformer
+ * inference hot path.
+ *
+ * Conventions for every entry point
+ *   - Pointers are DEVICE pointers borrowed from the caller (bf16 unless stated).  The caller
+ *     keeps them alive until `stream` has passed the call.  The library allocates nothing.
+ *   - Sizes and strides are in ELEMENTS.  `stream` is a cudaStream_t (NULL = default stream).
+ *   - Return value: 0 on success, a negative BG_ERR_* code otherwise; bg_last_error_string()
+ *     then describes the failure.  Nothing throws, exits or synchronises, except
+ *     bg_read_status().
+ *   - Kernels that wait on hardware barriers bound every wait; a wait that runs out is
+ *     reported through bg_read_status(), never by a trap.
+ *
+ * "Replaces" names the reference code (path inside AgentBull/bongard, or `HF:` for
+ * transformers/models/t5gemma2/modeling_t5gemma2.py, release 5.5.0) whose arithmetic the
+ * entry point performs.
+ */
+#ifndef BONGARD_B200_H
+#define BONGARD_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BG_OK 0
+#define BG_ERR_SHAPE (-1)
+#define BG_ERR_ALIGN (-2)
+#define BG_ERR_ARCH (-3)
+#define BG_ERR_LAUNCH (-4)
+#define BG_ERR_WORKSPACE (-5)
+#define BG_ERR_DRIVER (-6)
+#define BG_ERR_TIMEOUT (-7)
+
+int bg_version(void);
+const char* bg_last_error_string(void);
+
+/* 0 if the current device is sm_100 and the driver offers TMA descriptors.
+ * Replaces the device gates of bongard/float8_training.py:31-34 and bongard/te_linear.py:110-111. */
+int bg_device_check(void);
+
+/* Synchronises `stream`, returns and clears the status word: 0, or the site code of the first
+ * bounded wait that ran out (1xx BF16 GEMM, 2xx attention, 3xx FP8 GEMM). */
+int bg_read_status(void* stream);
+
+/* out[r, :] = rmsnorm(x[r, :]) * (1 + w), fp32 math, rounded once.
+ * Replaces HF:61-69 T5Gemma2RMSNorm.forward / bongard/mps_inference.py:70-83 MPSRMSNorm. */
+int bg_rmsnorm(const void* x, int64_t ldx, const void* w, void* out, int64_t ldo, int64_t rows, int64_t h,
+               float eps, void* stream);
+
+/* resid += bf16(rmsnorm(y) * (1 + w_post)); normed = rmsnorm(resid) * (1 + w_next) (skipped when
+ * w_next is NULL).  y, resid, normed are contiguous [rows, h].
+ * Replaces the post-norm + residual + next pre-norm chain of HF:496-502 and HF:555-561. */
+int bg_add_rmsnorm(const void* y, const void* w_post, void* resid, const void* w_next, void* normed,
+                   int64_t rows, int64_t h, float eps, void* stream);
+
+/* In-place per-head RMSNorm (1 + w gain) and rotate-half RoPE of q [tokens, q_heads, D] and
+ * k [tokens, k_heads, D] (token strides ldq / ldk).  positions int32 [tokens]; inv_freq fp32 [D/2].
+ * rotate = 0 normalises only; q or k may be NULL.
+ * Replaces bongard/attention.py:172-180 project_qk (after the projections), the fused surface
+ * bongard/flash_attention.py:76-125 metal_qk_norm_rope + bongard/qk_norm_rope.metal:4-33, and the
+ * k_norm of bongard/model.py:135-139 project_state_kv (rotate = 0). */
+int bg_qk_norm_rope(void* q, int64_t ldq, int q_heads, void* k, int64_t ldk, int k_heads, const void* q_weight,
+                    const void* k_weight, const int32_t* positions, const float* inv_freq, int64_t tokens,
+                    int head_dim, float eps, int rotate, void* stream);
+
+/* out[r, :] = table[ids[r], :] * scale, or eoi_embedding where ids[r] == eoi_token.  ids int64.
+ * Replaces HF:644-647 T5Gemma2TextScaledWordEmbedding.forward. */
+int bg_embed(const int64_t* ids, const void* table, const void* eoi_embedding, void* out, int64_t rows, int64_t h,
+             float scale, int64_t eoi_token, int64_t vocab, void* stream);
+
+/* out[m, n] = a[m, k] . w[n, k]^T on tcgen05 tensor cores, fp32 accumulate, bf16 out.
+ * epilogue 0: plain.  epilogue 1 (GeGLU): w is the stacked [gate; up] weight of 2n rows and
+ * out = gelu_tanh(a . gate^T) * (a . up^T).
+ * Replaces F.linear in eval mode of bongard/te_linear.py:59-62 TELinear.forward (stacked weights,
+ * 47-55), bongard/float8_training.py:17-21, and for epilogue 1 the gate_up -> GeGLU step of
+ * bongard/te_linear.py:98-103 TEMLP.forward / HF:87-91 T5Gemma2MLP.forward. */
+int bg_gemm_bf16(const void* a, int64_t lda, const void* w, int64_t ldw, void* out, int64_t ldo, int64_t m,
+                 int64_t n, int64_t k, int epilogue, void* stream);
+
+/* Packed variable-length attention, one softmax over [prefix keys | own keys].
+ *   q [tq, q_heads, D] (token stride ldq); k, v [tk, kv_heads, D] (stride ldkv);
+ *   ck, cv [ts, kv_heads, D] (stride ldc) or NULL; out [tq, q_heads * D] contiguous;
+ *   lse fp32 [q_heads, tq] (natural log) or NULL.
+ *   tiles int32 [n_tiles, 8] = {q_start, q_count, own_lo, own_hi, lo_max, hi_min, prefix_start,
+ *   prefix_len}: q_count <= 128 / (q_heads / kv_heads) consecutive query tokens; [own_lo, own_hi)
+ *   covers every row's own-key range, [lo_max, hi_min) is the part visible to all rows; the
+ *   prefix keys are visible to every row.  row_lo / row_hi int32 [tq]: own-key range per token.
+ * Replaces bongard/flash_varlen.py:129-139 attention, 13-22 _forward (op bongard::flash_packed_forward),
+ * 61-77 _prefix (op bongard::flash_prefix_forward, without materialising the gathered keys), the
+ * windowed layers bongard/packing.py:154-175 packed_attention serves, and the two-partition
+ * serving path bongard/attention.py:122-169. */
+int bg_varlen_attention(const void* q, int64_t ldq, const void* k, const void* v, int64_t ldkv, const void* ck,
+                        const void* cv, int64_t ldc, void* out, float* lse, const int32_t* tiles,
+                        int32_t n_tiles, const int32_t* row_lo, const int32_t* row_hi, int64_t tq, int64_t tk,
+                        int64_t ts, int q_heads, int kv_heads, int head_dim, float scale, void* stream);
+
+/* logits[c] = w . h + (C h) . (G g) / sqrt(rank) with h = hidden[cand_rows[c]], g = hidden[dec_rows[c]].
+ * Replaces bongard/model.py:85-95 JudgmentHead.forward as called by 520-529 score_readouts. */
+int bg_judgment_head(const void* hidden, int64_t ldh, const int32_t* cand_rows, const int32_t* dec_rows,
+                     const void* w, const void* cmat, const void* gmat, float* logits, int64_t candidates,
+                     int64_t h, int rank, void* stream);
+
+/* Per-question float64 temperature softmax: question i owns logits [offsets[i], offsets[i+1]).
+ * Replaces bongard/inference.py:54-73 probabilities. */
+int bg_candidate_softmax(const float* logits, const int32_t* offsets, double* probs, int64_t questions,
+                         double temperature, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BONGARD_B200_H */

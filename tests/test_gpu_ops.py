@@ -1,0 +1,163 @@
+"""Parity of every CUDA entry point (called through the C ABI) against the CPU oracle.
+
+Tolerances: bf16 attention / MLP / linear outputs within 2e-2 absolute + 1e-2 relative of the
+fp32 oracle evaluated on the same bf16-rounded inputs; glue kernels within one bf16 rounding.
+"""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from bongard_b200 import ops  # noqa: E402
+from oracle import reference_math as om  # noqa: E402
+
+DEV = 'cuda'
+ATOL, RTOL = 2e-2, 1e-2
+
+
+def rnd(*shape, seed=0, std=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * std).bfloat16()
+
+
+def assert_close(got, want, atol=ATOL, rtol=RTOL):
+    got, want = got.detach().float().cpu(), want.detach().float().cpu()
+    assert got.shape == want.shape
+    assert torch.isfinite(got).all()
+    err = (got - want).abs()
+    bound = atol + rtol * want.abs()
+    worst = float((err - bound).max())
+    assert worst <= 0, f'max abs err {float(err.max()):.4g}, exceeds bound by {worst:.4g}'
+
+
+@pytest.fixture(scope='module', autouse=True)
+def device():
+    ops.device_check()
+    yield
+    ops.read_status()
+
+
+@pytest.mark.parametrize('rows,h', [(1, 256), (7, 256), (33, 2560), (5, 8192), (0, 256)])
+def test_rmsnorm(rows, h):
+    x, w = rnd(rows, h, seed=1), rnd(h, seed=2, std=0.2)
+    got = ops.rmsnorm(x.to(DEV), w.to(DEV))
+    want = om.rmsnorm(x.float(), w.float())
+    assert_close(got, want, atol=1e-2, rtol=8e-3)
+
+
+@pytest.mark.parametrize('rows,h', [(9, 256), (40, 2560)])
+def test_add_rmsnorm(rows, h):
+    y, resid = rnd(rows, h, seed=3), rnd(rows, h, seed=4)
+    wp, wn = rnd(h, seed=5, std=0.2), rnd(h, seed=6, std=0.2)
+    r = resid.to(DEV).clone()
+    normed = ops.add_rmsnorm_(y.to(DEV), wp.to(DEV), r, wn.to(DEV))
+    want_r = resid + om.rmsnorm(y, wp)          # bf16 chain, as the module sequence computes it
+    want_n = om.rmsnorm(want_r, wn)
+    assert_close(r, want_r, atol=1e-6, rtol=8e-3)
+    assert_close(normed, want_n, atol=1e-2, rtol=8e-3)
+    r2 = resid.to(DEV).clone()
+    assert ops.add_rmsnorm_(y.to(DEV), wp.to(DEV), r2, None) is None
+    assert torch.equal(r2, r)
+
+
+@pytest.mark.parametrize('d,hq,hkv,theta', [(64, 4, 2, 1e4), (256, 8, 4, 1e6), (256, 8, 4, 1e4), (128, 2, 1, 1e4)])
+def test_qk_norm_rope(d, hq, hkv, theta):
+    lengths = [5, 130, 1, 700]
+    t = sum(lengths)
+    qkv = rnd(t, (hq + 2 * hkv) * d, seed=7)
+    qw, kw = rnd(d, seed=8, std=0.2), rnd(d, seed=9, std=0.2)
+    positions = torch.cat([torch.arange(n) for n in lengths])
+    buf = qkv.to(DEV).clone()
+    q = buf[:, :hq * d].view(t, hq, d)
+    k = buf[:, hq * d:(hq + hkv) * d].view(t, hkv, d)
+    ops.qk_norm_rope_(q, k, qw.to(DEV), kw.to(DEV), positions.int().to(DEV), ops.inv_freq(d, theta, DEV))
+    cos, sin = om.rope_tables(positions, d, theta, torch.float32)
+    wq, wk = om.qk_norm_rope(qkv[:, :hq * d].float().view(t, hq, d), qkv[:, hq * d:(hq + hkv) * d].float().view(t, hkv, d),
+                             qw.float(), kw.float(), cos, sin)
+    assert_close(q, wq, atol=1.5e-2, rtol=8e-3)
+    assert_close(k, wk, atol=1.5e-2, rtol=8e-3)
+    assert torch.equal(buf[:, (hq + hkv) * d:].cpu(), qkv[:, (hq + hkv) * d:])   # v untouched
+    # normalise only (decoder state keys)
+    buf2 = qkv.to(DEV).clone()
+    k2 = buf2[:, hq * d:(hq + hkv) * d].view(t, hkv, d)
+    ops.qk_norm_rope_(None, k2, None, kw.to(DEV), None, None, rotate=False)
+    assert_close(k2, om.rmsnorm(qkv[:, hq * d:(hq + hkv) * d].float().view(t, hkv, d), kw.float()), atol=1e-2, rtol=8e-3)
+    assert torch.equal(buf2[:, :hq * d].cpu(), qkv[:, :hq * d])
+
+
+def test_embed():
+    table, eoi = rnd(300, 256, seed=10, std=0.02), rnd(256, seed=11, std=0.1)
+    ids = torch.tensor([5, 123, 299, 0, 123, 17])
+    scale = float(torch.tensor(math.sqrt(256)).bfloat16())
+    got = ops.embed(ids.to(DEV), table.to(DEV), eoi.to(DEV), scale, eoi_token=123)
+    want = om.embed(ids, table, eoi, 256, eoi_token=123)
+    assert torch.equal(got.cpu(), want)
+
+
+@pytest.mark.parametrize('m,n,k', [(1, 256, 256), (129, 512, 256), (300, 2560, 1024), (1000, 4096, 2560),
+                                   (77, 264, 72), (4096, 2560, 10240)])
+def test_linear(m, n, k):
+    x, w = rnd(m, k, seed=12), rnd(n, k, seed=13, std=0.02)
+    got = ops.linear(x.to(DEV), w.to(DEV))
+    want = x.float() @ w.float().t()
+    assert_close(got, want)
+
+
+def test_linear_strided_input_and_output():
+    x = rnd(200, 1024, seed=14)
+    w = rnd(512, 256, seed=15, std=0.05)
+    xd = x.to(DEV)
+    out = torch.zeros(200, 1024, device=DEV, dtype=torch.bfloat16)
+    ops.linear(xd[:, 256:512], w.to(DEV), out=out[:, 512:])
+    assert_close(out[:, 512:], x[:, 256:512].float() @ w.float().t())
+    assert float(out[:, :512].abs().max()) == 0
+
+
+@pytest.mark.parametrize('m,i,k', [(5, 1024, 256), (300, 1024, 256), (1500, 10240, 2560)])
+def test_linear_geglu(m, i, k):
+    x = rnd(m, k, seed=16)
+    gate, up = rnd(i, k, seed=17, std=0.02), rnd(i, k, seed=18, std=0.02)
+    got = ops.linear_geglu(x.to(DEV), torch.cat([gate, up]).to(DEV))
+    want = torch.nn.functional.gelu(x.float() @ gate.float().t(), approximate='tanh') * (x.float() @ up.float().t())
+    assert_close(got, want)
+
+
+def test_geglu_mlp_matches_golden(golden_dir):
+    g = {k: torch.from_numpy(v) for k, v in np.load(golden_dir / 'ops.npz').items() if k.startswith('mlp_')}
+    x = g['mlp_x'].bfloat16()
+    gate_up = torch.cat([g['mlp_gate'], g['mlp_up']]).bfloat16()
+    h = ops.linear_geglu(x.to(DEV), gate_up.to(DEV))
+    y = ops.linear(h, g['mlp_down'].bfloat16().to(DEV))
+    assert_close(y, g['mlp_y'])
+
+
+def test_linear_rejects_bad_arguments():
+    x, w = rnd(8, 256).to(DEV), rnd(256, 256).to(DEV)
+    with pytest.raises(ValueError):
+        ops.linear(x.float(), w)
+    with pytest.raises(ValueError):
+        ops.linear(x.cpu(), w.cpu())
+    with pytest.raises(ValueError):
+        ops.linear(x[:, :100], w[:, :100].contiguous())   # K not a multiple of 8
+
+
+def test_judgment_head_and_softmax(golden_dir):
+    g = {k: torch.from_numpy(v) for k, v in np.load(golden_dir / 'ops.npz').items()}
+    h, gg = g['head_h'].bfloat16(), g['head_g'][:1].bfloat16()
+    hidden = torch.cat([h, gg]).to(DEV)
+    cand = torch.arange(6, dtype=torch.int32, device=DEV)
+    dec = torch.full((6,), 6, dtype=torch.int32, device=DEV)
+    w, c, gr = (g[k].bfloat16() for k in ('head_w', 'head_c', 'head_gr'))
+    logits = ops.judgment_head(hidden, cand, dec, w.to(DEV), c.to(DEV), gr.to(DEV))
+    want = om.judgment_head(h.float(), gg.float().expand(6, -1), w.float(), c.float(), gr.float())
+    assert_close(logits, want, atol=2e-4, rtol=1e-4)
+    offsets = torch.tensor([0, 2, 6], dtype=torch.int32, device=DEV)
+    for temp in (1.0, 0.5, 2.0):
+        probs = ops.candidate_softmax(logits, offsets, temp).cpu()
+        l = logits.cpu()
+        want = torch.cat([om.probabilities(l[:2], temp), om.probabilities(l[2:], temp)])
+        assert float((probs - want).abs().max()) < 1e-12
