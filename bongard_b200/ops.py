@@ -15,6 +15,34 @@ from . import _lib
 BF16 = torch.bfloat16
 
 
+class KernelTimer:
+    """Optional CUDA-event timing of one kernel family on the launching stream.  Set
+    `ops.GEMM_TIMER = KernelTimer()` to collect; reading the total synchronises."""
+
+    def __init__(self):
+        self.events, self.flops, self.launches = [], 0, 0
+
+    def start(self):
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        return e
+
+    def stop(self, begin, flops):
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        self.events.append((begin, e))
+        self.flops += flops
+        self.launches += 1
+
+    def total_ms(self):
+        torch.cuda.synchronize()
+        return sum(a.elapsed_time(b) for a, b in self.events)
+
+
+GEMM_TIMER = None
+ATTN_TIMER = None
+
+
 def _stream():
     return torch.cuda.current_stream().cuda_stream
 
@@ -123,8 +151,12 @@ def linear(x, weight, out=None):
     n = weight.shape[0]
     if out is None:
         out = torch.empty((m, n), device=x.device, dtype=BF16)
+    timer = GEMM_TIMER
+    begin = timer.start() if timer is not None else None
     _lib.check(lib.bg_gemm_bf16(_ptr(flat), lda, _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), m, n, k, 0,
                                 _stream()), 'bg_gemm_bf16')
+    if timer is not None:
+        timer.stop(begin, 2 * m * n * k)
     return out.view(*x.shape[:-1], n)
 
 
@@ -137,8 +169,12 @@ def linear_geglu(x, gate_up):
         raise ValueError(f'gate_up must be [2I, {k}] with contiguous rows')
     n = gate_up.shape[0] // 2
     out = torch.empty((m, n), device=x.device, dtype=BF16)
+    timer = GEMM_TIMER
+    begin = timer.start() if timer is not None else None
     _lib.check(lib.bg_gemm_bf16(_ptr(flat), lda, _ptr(gate_up), gate_up.stride(0), _ptr(out), n, m, n, k, 1,
                                 _stream()), 'bg_gemm_bf16')
+    if timer is not None:
+        timer.stop(begin, 4 * m * n * k)
     return out.view(*x.shape[:-1], n)
 
 
@@ -184,18 +220,36 @@ def plan_rows(lengths, window, *, decoder):
     return lo, hi
 
 
-def make_plan(lengths, window, device, *, group, owners=None, state_lengths=None):
-    """Tile a pack of segments for the attention kernel.
+@dataclass
+class HostPlan:
+    """Host half of an attention plan: one int32 array [tiles*8 | row_lo | row_hi]."""
+
+    packed: np.ndarray
+    tokens: int
+    n_tiles: int
+    pairs: int
+
+    def to(self, device):
+        dev = torch.from_numpy(self.packed).to(device, non_blocking=True)
+        return self.view(dev)
+
+    def view(self, dev):
+        n8, t = self.n_tiles * 8, self.tokens
+        return AttentionPlan(dev[:n8].view(-1, 8), dev[n8:n8 + t], dev[n8 + t:n8 + 2 * t], t, self.n_tiles, self.pairs)
+
+
+def make_host_plan(lengths, window, *, group, owners=None, state_lengths=None):
+    """Tile a pack of segments for the attention kernel (host arithmetic on lengths only).
 
     Encoder (owners None): tiles never cross a segment.  Decoder: consecutive questions of the
     same owner form one run; a tile is up to 128/group consecutive tokens of a run, so
-    questions that share a state also share its key stream."""
+    questions that share a state also share its key stream.  Tiles are ordered heaviest first."""
     lengths = [int(n) for n in lengths]
     decoder = owners is not None
     lo, hi = plan_rows(lengths, window, decoder=decoder)
     total = len(lo)
     tq = 128 // group
-    runs = []      # (start, end, prefix_start, prefix_len)
+    runs = []      # [start, end, prefix_start, prefix_len, owner]
     offset = 0
     if decoder:
         state_offsets = np.concatenate(([0], np.cumsum(np.asarray(state_lengths, dtype=np.int64))))
@@ -209,37 +263,31 @@ def make_plan(lengths, window, device, *, group, owners=None, state_lengths=None
         for n in lengths:
             runs.append([offset, offset + n, 0, 0, -1])
             offset += n
-    q_start, q_count, pre_start, pre_len = [], [], [], []
-    for start, end, ps, pl, _ in runs:
-        s = np.arange(start, end, tq, dtype=np.int64)
-        q_start.append(s)
-        q_count.append(np.minimum(end - s, tq))
-        pre_start.append(np.full(len(s), ps, dtype=np.int64))
-        pre_len.append(np.full(len(s), pl, dtype=np.int64))
-    if not q_start or total == 0:
-        empty = torch.zeros((0, 8), dtype=torch.int32, device=device)
-        z = torch.zeros(0, dtype=torch.int32, device=device)
-        return AttentionPlan(empty, z, z, 0, 0, 0)
-    q_start, q_count = np.concatenate(q_start), np.concatenate(q_count)
-    pre_start, pre_len = np.concatenate(pre_start), np.concatenate(pre_len)
-    keep = q_count > 0
-    q_start, q_count, pre_start, pre_len = q_start[keep], q_count[keep], pre_start[keep], pre_len[keep]
-    order = np.argsort(q_start, kind='stable')
-    q_start, q_count, pre_start, pre_len = q_start[order], q_count[order], pre_start[order], pre_len[order]
+    runs = [r for r in runs if r[1] > r[0]]
+    if not runs:
+        return HostPlan(np.zeros(0, dtype=np.int32), 0, 0, 0)
+    run = np.asarray([r[:4] for r in runs], dtype=np.int64)
+    counts = (run[:, 1] - run[:, 0] + tq - 1) // tq
+    which = np.repeat(np.arange(len(runs)), counts)
+    first = np.cumsum(counts) - counts
+    q_start = run[which, 0] + (np.arange(int(counts.sum())) - first[which]) * tq
+    q_count = np.minimum(run[which, 1] - q_start, tq)
     own_lo = np.minimum.reduceat(lo, q_start)
     own_hi = np.maximum.reduceat(hi, q_start)
     lo_max = np.maximum.reduceat(lo, q_start)
     hi_min = np.minimum.reduceat(hi, q_start)
-    tiles = np.stack([q_start, q_count, own_lo, own_hi, lo_max, hi_min, pre_start, pre_len], axis=1)
-    work = pre_len + own_hi - own_lo
+    tiles = np.stack([q_start, q_count, own_lo, own_hi, lo_max, hi_min, run[which, 2], run[which, 3]], axis=1)
+    work = run[which, 3] + own_hi - own_lo
     tiles = tiles[np.argsort(-work, kind='stable')].astype(np.int32)
     packed = np.concatenate([tiles.reshape(-1), lo.astype(np.int32), hi.astype(np.int32)])
-    dev = torch.from_numpy(packed).to(device, non_blocking=True)
-    n8 = tiles.shape[0] * 8
     pairs = int((hi - lo).sum())
     if decoder:
         pairs += int(sum(n * state_lengths[o] for n, o in zip(lengths, owners)))
-    return AttentionPlan(dev[:n8].view(-1, 8), dev[n8:n8 + total], dev[n8 + total:], total, tiles.shape[0], pairs)
+    return HostPlan(packed, total, tiles.shape[0], pairs)
+
+
+def make_plan(lengths, window, device, *, group, owners=None, state_lengths=None):
+    return make_host_plan(lengths, window, group=group, owners=owners, state_lengths=state_lengths).to(device)
 
 
 def varlen_attention(q, k, v, plan, scale, cross=None, return_lse=False):
@@ -267,10 +315,14 @@ def varlen_attention(q, k, v, plan, scale, cross=None, return_lse=False):
         ts, ldc = ck.shape[0], ck.stride(0)
     out = torch.empty((tq, hq * d), device=q.device, dtype=BF16)
     lse = torch.empty((hq, tq), device=q.device, dtype=torch.float32) if return_lse else None
+    timer = ATTN_TIMER
+    begin = timer.start() if timer is not None else None
     _lib.check(lib.bg_varlen_attention(
         _ptr(q), q.stride(0), _ptr(k), _ptr(v), k.stride(0), _ptr(ck), _ptr(cv), ldc, _ptr(out), _ptr(lse),
         _ptr(plan.tiles), plan.n_tiles, _ptr(plan.row_lo), _ptr(plan.row_hi), tq, tk, ts, hq, hkv, d,
         float(scale), _stream()), 'bg_varlen_attention')
+    if timer is not None:
+        timer.stop(begin, 4 * d * hq * plan.pairs)
     return (out, lse) if return_lse else out
 
 

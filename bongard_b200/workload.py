@@ -152,13 +152,18 @@ def weight_names(shape: ModelShape):
     return names
 
 
-def make_weights(shape: ModelShape, seed: int, *, std=0.02, norm_std=0.0, dtype=torch.float32):
+def make_weights(shape: ModelShape, seed: int, *, std=0.02, norm_std=0.0, dtype=torch.float32, portable=True):
     """Seeded random-init weights as CPU tensors keyed by Hugging Face names.
 
     Matrices ~ N(0, std).  One-dimensional tensors (RMSNorm gains, stored zero-centred,
     and the end-of-image embedding row) ~ N(0, norm_std); norm_std=0 leaves them at the
     library's initial value, i.e. gain 1.  The decoder embedding is tied to the encoder's.
     """
+    if not portable:
+        # Faster multi-threaded generator for cases checked inside one process (no fixture involved).
+        gen = torch.Generator().manual_seed(seed)
+        return {name: (torch.randn(dims, generator=gen) * (std if len(dims) >= 2 else norm_std)).to(dtype)
+                for name, dims in weight_names(shape)}
     rng = np.random.Generator(np.random.PCG64(seed))
     out = {}
     for name, dims in weight_names(shape):

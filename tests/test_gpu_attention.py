@@ -21,6 +21,8 @@ def assert_close(got, want, atol=2e-2, rtol=1e-2):
     got, want = got.detach().float().cpu(), want.detach().float().cpu()
     assert got.shape == want.shape
     assert torch.isfinite(got).all()
+    if got.numel() == 0:
+        return
     err = (got - want).abs()
     worst = float((err - (atol + rtol * want.abs())).max())
     assert worst <= 0, f'max abs err {float(err.max()):.4g}, exceeds bound by {worst:.4g}'
