@@ -1,0 +1,138 @@
+"""Op-level timings of the C-ABI kernels on seeded synthetic inputs.
+
+    python -m bongard_b200.microbench attention [--variant global|window] [--sequences 16]
+    python -m bongard_b200.microbench mlp [--tokens 32768]
+    python -m bongard_b200.microbench linear [--tokens 32768]
+    python -m bongard_b200.microbench glue [--tokens 32768]
+
+attention: packed encoder self-attention, lengths uniform in 256-4096 (seed 2), 8 query / 4 KV
+heads of 256, QK-norm + RoPE applied by the glue kernel first; FLOPs = 4 D Hq (visible pairs).
+mlp: tokens x 2560 -> GeGLU(2 x 10240) -> 2560.  linear: the q|k|v and o projections.
+Each op is timed with CUDA events over `--iters` launches after `--warmup`; inputs are larger
+than L2 or L2 is flushed between launches (--flush).  Prints one JSON object per op.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from . import ops, workload as wl
+
+DEV = 'cuda'
+
+
+def timed(fn, iters, warmup, flush=None):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if flush is None:
+        begin.record()
+        for _ in range(iters):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        return begin.elapsed_time(end) / iters
+    for _ in range(iters):
+        flush.zero_()
+        begin.record()
+        fn()
+        end.record()
+        torch.cuda.synchronize()
+        total += begin.elapsed_time(end)
+    return total / iters
+
+
+def randn(*shape, std=1.0, seed=0):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    return (torch.randn(*shape, device=DEV, generator=g) * std).bfloat16()
+
+
+def attention(args, flush):
+    lengths = wl.varlen_lengths(2, args.sequences)
+    t, hq, hkv, d = sum(lengths), 8, 4, 256
+    window, theta = (None, 1e6) if args.variant == 'global' else (1024, 1e4)
+    qkv = randn(t, (hq + 2 * hkv) * d, seed=2)
+    q = qkv[:, :hq * d].view(t, hq, d)
+    k = qkv[:, hq * d:(hq + hkv) * d].view(t, hkv, d)
+    v = qkv[:, (hq + hkv) * d:].view(t, hkv, d)
+    gain = torch.zeros(d, device=DEV, dtype=torch.bfloat16)
+    positions = torch.cat([torch.arange(n, dtype=torch.int32) for n in lengths]).to(DEV)
+    ops.qk_norm_rope_(q, k, gain, gain, positions, ops.inv_freq(d, theta, DEV))
+    plan = ops.make_plan(lengths, window, DEV, group=hq // hkv)
+    ms = timed(lambda: ops.varlen_attention(q, k, v, plan, d ** -0.5), args.iters, args.warmup, flush)
+    flops = 4 * d * hq * plan.pairs
+    return dict(op=f'varlen_attention_{args.variant}', tokens=t, sequences=len(lengths), tiles=plan.n_tiles,
+                ms=ms, tflops=flops / ms / 1e9, algorithmic_tflop=flops / 1e12,
+                min_bytes=2 * t * (2 * hq + 2 * hkv) * d)
+
+
+def mlp(args, flush):
+    t, h, i = args.tokens, 2560, 10240
+    x = randn(t, h, seed=3)
+    wgu, wd = randn(2 * i, h, std=0.02, seed=4), randn(h, i, std=0.02, seed=5)
+    out = []
+    hidden = ops.linear_geglu(x, wgu)
+    for name, fn, flops, nbytes in (
+            ('gate_up_geglu', lambda: ops.linear_geglu(x, wgu), 4 * t * h * i, 2 * (t * h + 2 * i * h + t * i)),
+            ('down', lambda: ops.linear(hidden, wd), 2 * t * h * i, 2 * (t * i + i * h + t * h))):
+        ms = timed(fn, args.iters, args.warmup, flush)
+        out.append(dict(op=f'gemm_bf16_{name}', tokens=t, ms=ms, tflops=flops / ms / 1e9, min_bytes=nbytes))
+    both = timed(lambda: ops.linear(ops.linear_geglu(x, wgu), wd), args.iters, args.warmup, flush)
+    out.append(dict(op='geglu_mlp', tokens=t, ms=both, tflops=6 * t * h * i / both / 1e9))
+    return out
+
+
+def linear(args, flush):
+    t = args.tokens
+    out = []
+    for name, n, k in (('qkv', 4096, 2560), ('o', 2560, 2048)):
+        x, w = randn(t, k, seed=6), randn(n, k, std=0.02, seed=7)
+        ms = timed(lambda: ops.linear(x, w), args.iters, args.warmup, flush)
+        out.append(dict(op=f'gemm_bf16_{name}', tokens=t, ms=ms, tflops=2 * t * n * k / ms / 1e9,
+                        min_bytes=2 * (t * k + n * k + t * n)))
+    return out
+
+
+def glue(args, flush):
+    t, h = args.tokens, 2560
+    x, y, w = randn(t, h, seed=8), randn(t, h, seed=9), randn(h, std=0.1, seed=10)
+    out = []
+    ms = timed(lambda: ops.rmsnorm(x, w), args.iters, args.warmup, flush)
+    out.append(dict(op='rmsnorm', tokens=t, ms=ms, gbs=2 * t * h * 2 / ms / 1e6))
+    ms = timed(lambda: ops.add_rmsnorm_(y, w, x, w), args.iters, args.warmup, flush)
+    out.append(dict(op='add_rmsnorm', tokens=t, ms=ms, gbs=4 * t * h * 2 / ms / 1e6))
+    qkv = randn(t, 4096, seed=11)
+    q, k = qkv[:, :2048].view(t, 8, 256), qkv[:, 2048:3072].view(t, 4, 256)
+    gain = randn(256, std=0.1, seed=12)
+    positions = (torch.arange(t, device=DEV, dtype=torch.int32) % 4096)
+    freqs = ops.inv_freq(256, 1e4, DEV)
+    ms = timed(lambda: ops.qk_norm_rope_(q, k, gain, gain, positions, freqs), args.iters, args.warmup, flush)
+    out.append(dict(op='qk_norm_rope', tokens=t, ms=ms, gbs=2 * t * 3072 * 2 / ms / 1e6))
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('op', choices=['attention', 'mlp', 'linear', 'glue'])
+    ap.add_argument('--variant', default='global', choices=['global', 'window'])
+    ap.add_argument('--sequences', type=int, default=16)
+    ap.add_argument('--tokens', type=int, default=32768)
+    ap.add_argument('--iters', type=int, default=20)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--flush', action='store_true', help='write a 256 MB buffer between launches')
+    args = ap.parse_args()
+    ops.device_check()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV) if args.flush else None
+    result = {'attention': attention, 'mlp': mlp, 'linear': linear, 'glue': glue}[args.op](args, flush)
+    ops.read_status()
+    for row in result if isinstance(result, list) else [result]:
+        print(json.dumps(row))
+
+
+if __name__ == '__main__':
+    main()
