@@ -34,8 +34,8 @@ from bongard_b200 import workload as wl  # noqa: E402
 
 METRIC = 'judged_questions_per_second'
 UNIT = 'questions/s'
-# dram bytes per GEMM launch measured with ncu on a small case, see profiles/; None until captured
-GEMM_TRAFFIC_PER_FLOP = None
+# DRAM bytes per algorithmic FLOP of the GEMM, from the ncu capture of the 8192-token MLP GEMMs (scaled to a launch by its FLOPs)
+GEMM_TRAFFIC_PER_FLOP = 9.14e-4   # (607.4 + 570.1) MB over (0.859 + 0.429) TFLOP, profiles/gemm_bf16_mlp_8192tokens.md
 
 
 def parse():

@@ -21,9 +21,15 @@ SIGNATURES = {
     'bg_rmsnorm': ([P, I64, P, P, I64, I64, I64, F32, P], INT),
     'bg_add_rmsnorm': ([P, P, P, P, P, I64, I64, F32, P], INT),
     'bg_qk_norm_rope': ([P, I64, INT, P, I64, INT, P, P, P, P, I64, INT, F32, INT, P], INT),
+    'bg_qk_norm_rope_table': ([P, I64, INT, P, I64, INT, P, P, P, P, I64, INT, F32, P], INT),
     'bg_embed': ([P, P, P, P, I64, I64, F32, I64, I64, P], INT),
     'bg_gemm_bf16': ([P, I64, P, I64, P, I64, I64, I64, I64, INT, P], INT),
-    'bg_varlen_attention': ([P, I64, P, P, I64, P, P, I64, P, P, P, I32, P, P, I64, I64, I64, INT, INT, INT,
+    'bg_quantize_e4m3_rows': ([P, I64, P, I64, P, I64, I64, P], INT),
+    'bg_quantize_e4m3_tiles': ([P, I64, P, I64, P, I64, I64, P], INT),
+    'bg_gemm_fp8_block128': ([P, I64, P, P, I64, P, P, I64, I64, I64, I64, INT, P], INT),
+    'bg_linear_fp8_workspace_bytes': ([I64, I64], I64),
+    'bg_linear_fp8': ([P, I64, P, I64, P, P, I64, I64, I64, I64, INT, P, I64, P], INT),
+    'bg_varlen_attention': ([P, I64, I64, P, P, I64, I64, P, P, I64, I64, P, P, P, I32, P, P, I64, I64, I64, INT, INT, INT,
                              F32, P], INT),
     'bg_judgment_head': ([P, I64, P, P, P, P, P, P, I64, I64, INT, P], INT),
     'bg_candidate_softmax': ([P, P, P, I64, F64, P], INT),

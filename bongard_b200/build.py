@@ -8,9 +8,9 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / 'csrc'
 LIB = HERE / 'libbongard_b200.so'
-SOURCES = ['api.cu', 'glue.cu', 'gemm_bf16.cu', 'attn.cu']
+SOURCES = ['api.cu', 'glue.cu', 'gemm_bf16.cu', 'gemm_fp8.cu', 'attn.cu']
 FLAGS = ['-gencode', 'arch=compute_100a,code=sm_100a', '-lineinfo', '-O3', '-std=c++17',
-         '--use_fast_math', '-Xcompiler', '-fPIC', '-cudart', 'static']
+         '-Xcompiler', '-fPIC', '-cudart', 'static']
 
 
 def nvcc():

@@ -354,9 +354,9 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
     return BG_OK;
 }
 
-int kv_map(CUtensorMap* map, const void* base, int64_t tokens, int heads, int d, int64_t ld) {
+int kv_map(CUtensorMap* map, const void* base, int64_t tokens, int heads, int d, int64_t ld, int64_t hs) {
     uint64_t dims[3] = {(uint64_t)d, (uint64_t)heads, (uint64_t)tokens};
-    uint64_t strides[2] = {(uint64_t)d * 2, (uint64_t)ld * 2};
+    uint64_t strides[2] = {(uint64_t)hs * 2, (uint64_t)ld * 2};
     uint32_t box[3] = {64, 1, KEYS};
     return bg_make_tensor_map(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides, box,
                               CU_TENSOR_MAP_SWIZZLE_128B);
@@ -364,8 +364,9 @@ int kv_map(CUtensorMap* map, const void* base, int64_t tokens, int heads, int d,
 
 }  // namespace
 
-extern "C" int bg_varlen_attention(const void* q, int64_t ldq, const void* k, const void* v, int64_t ldkv,
-                                   const void* ck, const void* cv, int64_t ldc, void* out, float* lse,
+extern "C" int bg_varlen_attention(const void* q, int64_t ldq, int64_t hsq, const void* k, const void* v,
+                                   int64_t ldkv, int64_t hskv, const void* ck, const void* cv, int64_t ldc,
+                                   int64_t hsc, void* out, float* lse,
                                    const int32_t* tiles, int32_t n_tiles, const int32_t* row_lo,
                                    const int32_t* row_hi, int64_t tq, int64_t tk, int64_t ts, int q_heads,
                                    int kv_heads, int head_dim, float scale, void* stream) {
@@ -379,7 +380,7 @@ extern "C" int bg_varlen_attention(const void* q, int64_t ldq, const void* k, co
                      "(got head_dim %d, group %d)", head_dim, g);
         return BG_ERR_SHAPE;
     }
-    if (ldq % 8 || ldkv % 8 || (ck && ldc % 8) ||
+    if (ldq % 8 || ldkv % 8 || hsq % 8 || hskv % 8 || (ck && (ldc % 8 || hsc % 8)) ||
         ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
           reinterpret_cast<uintptr_t>(ck) | reinterpret_cast<uintptr_t>(cv) | reinterpret_cast<uintptr_t>(out)) & 15)) {
         bg_set_error("bg_varlen_attention: pointers must be 16-byte aligned and strides multiples of 8 elements");
@@ -390,16 +391,16 @@ extern "C" int bg_varlen_attention(const void* q, int64_t ldq, const void* k, co
     CUtensorMap mq, mk, mv, mck, mcv;
     {
         uint64_t dims[3] = {(uint64_t)head_dim, (uint64_t)q_heads, (uint64_t)tq};
-        uint64_t strides[2] = {(uint64_t)head_dim * 2, (uint64_t)ldq * 2};
+        uint64_t strides[2] = {(uint64_t)hsq * 2, (uint64_t)ldq * 2};
         uint32_t box[3] = {64, (uint32_t)g, (uint32_t)(ROWS / g)};
         int rc = bg_make_tensor_map(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, q, dims, strides, box,
                                     CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc) return rc;
     }
-    int rc = kv_map(&mk, k, tk, kv_heads, head_dim, ldkv);
-    if (!rc) rc = kv_map(&mv, v, tk, kv_heads, head_dim, ldkv);
-    if (!rc && ck) rc = kv_map(&mck, ck, ts, kv_heads, head_dim, ldc);
-    if (!rc && cv) rc = kv_map(&mcv, cv, ts, kv_heads, head_dim, ldc);
+    int rc = kv_map(&mk, k, tk, kv_heads, head_dim, ldkv, hskv);
+    if (!rc) rc = kv_map(&mv, v, tk, kv_heads, head_dim, ldkv, hskv);
+    if (!rc && ck) rc = kv_map(&mck, ck, ts, kv_heads, head_dim, ldc, hsc);
+    if (!rc && cv) rc = kv_map(&mcv, cv, ts, kv_heads, head_dim, ldc, hsc);
     if (rc) return rc;
     if (!ck) { mck = mk; mcv = mv; }
 

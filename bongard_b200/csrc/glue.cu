@@ -120,13 +120,22 @@ __global__ void qk_norm_rope_kernel(__nv_bfloat16* __restrict__ q, int64_t ldq, 
                                     __nv_bfloat16* __restrict__ k, int64_t ldk, int k_heads,
                                     const __nv_bfloat16* __restrict__ qw, const __nv_bfloat16* __restrict__ kw,
                                     const int32_t* __restrict__ positions, const float* __restrict__ inv_freq,
-                                    int64_t tokens, float eps, int rotate) {
+                                    const __nv_bfloat16* __restrict__ cos_table,
+                                    const __nv_bfloat16* __restrict__ sin_table, int64_t tokens, float eps,
+                                    int rotate) {
     constexpr int E = D / 32;  // elements per lane
     const int lane = threadIdx.x & 31;
     const int64_t token = int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (token >= tokens) return;
     float cs[E], sn[E];
-    if (rotate) {
+    if (rotate && cos_table != nullptr) {
+        // caller-supplied tables [tokens, D] (the rotary module's cos/sin, cat(freqs, freqs))
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            cs[e] = __bfloat162float(cos_table[token * D + lane * E + e]);
+            sn[e] = __bfloat162float(sin_table[token * D + lane * E + e]);
+        }
+    } else if (rotate) {
         const float pos = float(positions[token]);
 #pragma unroll
         for (int e = 0; e < E; ++e) {
@@ -311,9 +320,10 @@ int bg_add_rmsnorm(const void* y, const void* w_post, void* resid, const void* w
     return check_launch("bg_add_rmsnorm");
 }
 
-int bg_qk_norm_rope(void* q, int64_t ldq, int q_heads, void* k, int64_t ldk, int k_heads, const void* q_weight,
-                    const void* k_weight, const int32_t* positions, const float* inv_freq, int64_t tokens,
-                    int head_dim, float eps, int rotate, void* stream) {
+static int qk_norm_rope_launch(void* q, int64_t ldq, int q_heads, void* k, int64_t ldk, int k_heads,
+                               const void* q_weight, const void* k_weight, const int32_t* positions,
+                               const float* inv_freq, const void* cos_table, const void* sin_table, int64_t tokens,
+                               int head_dim, float eps, int rotate, void* stream) {
     if (tokens < 0 || (head_dim != 64 && head_dim != 128 && head_dim != 256) || q_heads < 0 || k_heads < 0) {
         bg_set_error("bg_qk_norm_rope: head_dim must be 64, 128 or 256 (got %d)", head_dim);
         return BG_ERR_SHAPE;
@@ -330,17 +340,37 @@ int bg_qk_norm_rope(void* q, int64_t ldq, int q_heads, void* k, int64_t ldk, int
     auto* kp = static_cast<__nv_bfloat16*>(k);
     auto* qw = static_cast<const __nv_bfloat16*>(q_weight);
     auto* kw = static_cast<const __nv_bfloat16*>(k_weight);
+    auto* ct = static_cast<const __nv_bfloat16*>(cos_table);
+    auto* st = static_cast<const __nv_bfloat16*>(sin_table);
     if (qp == nullptr) q_heads = 0;
     if (head_dim == 64)
         qk_norm_rope_kernel<64><<<grid, warps * 32, 0, s>>>(qp, ldq, q_heads, kp, ldk, k_heads, qw, kw, positions,
-                                                             inv_freq, tokens, eps, rotate);
+                                                             inv_freq, ct, st, tokens, eps, rotate);
     else if (head_dim == 128)
         qk_norm_rope_kernel<128><<<grid, warps * 32, 0, s>>>(qp, ldq, q_heads, kp, ldk, k_heads, qw, kw, positions,
-                                                              inv_freq, tokens, eps, rotate);
+                                                              inv_freq, ct, st, tokens, eps, rotate);
     else
         qk_norm_rope_kernel<256><<<grid, warps * 32, 0, s>>>(qp, ldq, q_heads, kp, ldk, k_heads, qw, kw, positions,
-                                                              inv_freq, tokens, eps, rotate);
+                                                              inv_freq, ct, st, tokens, eps, rotate);
     return check_launch("bg_qk_norm_rope");
+}
+
+int bg_qk_norm_rope(void* q, int64_t ldq, int q_heads, void* k, int64_t ldk, int k_heads, const void* q_weight,
+                    const void* k_weight, const int32_t* positions, const float* inv_freq, int64_t tokens,
+                    int head_dim, float eps, int rotate, void* stream) {
+    return qk_norm_rope_launch(q, ldq, q_heads, k, ldk, k_heads, q_weight, k_weight, positions, inv_freq, nullptr,
+                               nullptr, tokens, head_dim, eps, rotate, stream);
+}
+
+int bg_qk_norm_rope_table(void* q, int64_t ldq, int q_heads, void* k, int64_t ldk, int k_heads,
+                          const void* q_weight, const void* k_weight, const void* cos_table, const void* sin_table,
+                          int64_t tokens, int head_dim, float eps, void* stream) {
+    if (cos_table == nullptr || sin_table == nullptr) {
+        bg_set_error("bg_qk_norm_rope_table: cos and sin tables are required");
+        return BG_ERR_SHAPE;
+    }
+    return qk_norm_rope_launch(q, ldq, q_heads, k, ldk, k_heads, q_weight, k_weight, nullptr, nullptr, cos_table,
+                               sin_table, tokens, head_dim, eps, 1, stream);
 }
 
 int bg_embed(const int64_t* ids, const void* table, const void* eoi_embedding, void* out, int64_t rows, int64_t h,

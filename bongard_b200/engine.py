@@ -32,10 +32,11 @@ BF16 = torch.bfloat16
 
 @dataclass
 class LayerWeights:
-    wqkv: torch.Tensor
-    wo: torch.Tensor
-    wgu: torch.Tensor
-    wdown: torch.Tensor
+    wqkv: object             # bf16 tensors, or ops.Fp8Weight under linears='fp8'
+    wkv: object              # the k|v rows of wqkv (decoder: projects the shared state)
+    wo: object
+    wgu: object
+    wdown: object
     pre_attn: torch.Tensor
     post_attn: torch.Tensor
     pre_ffn: torch.Tensor
@@ -44,13 +45,17 @@ class LayerWeights:
     k_norm: torch.Tensor
 
 
-def _stack_layer(w, prefix, device):
+def _stack_layer(w, prefix, device, fp8=False, state_kv=False):
     g = lambda name: w[prefix + name].to(device=device, dtype=BF16)   # noqa: E731
+    conv = ops.quantize_weight if fp8 else (lambda t: t)
+    wqkv = torch.cat([g('self_attn.q_proj.weight'), g('self_attn.k_proj.weight'), g('self_attn.v_proj.weight')]).contiguous()
+    q_rows = w[prefix + 'self_attn.q_proj.weight'].shape[0]
     return LayerWeights(
-        wqkv=torch.cat([g('self_attn.q_proj.weight'), g('self_attn.k_proj.weight'), g('self_attn.v_proj.weight')]).contiguous(),
-        wo=g('self_attn.o_proj.weight').contiguous(),
-        wgu=torch.cat([g('mlp.gate_proj.weight'), g('mlp.up_proj.weight')]).contiguous(),
-        wdown=g('mlp.down_proj.weight').contiguous(),
+        wqkv=conv(wqkv),
+        wkv=(conv(wqkv[q_rows:].contiguous()) if fp8 else wqkv[q_rows:]) if state_kv else None,
+        wo=conv(g('self_attn.o_proj.weight').contiguous()),
+        wgu=conv(torch.cat([g('mlp.gate_proj.weight'), g('mlp.up_proj.weight')]).contiguous()),
+        wdown=conv(g('mlp.down_proj.weight').contiguous()),
         pre_attn=g('pre_self_attn_layernorm.weight'), post_attn=g('post_self_attn_layernorm.weight'),
         pre_ffn=g('pre_feedforward_layernorm.weight'), post_ffn=g('post_feedforward_layernorm.weight'),
         q_norm=g('self_attn.q_norm.weight'), k_norm=g('self_attn.k_norm.weight'))
@@ -60,16 +65,19 @@ class JudgmentEngine:
     """A full replica of the judgment model on one GPU."""
 
     def __init__(self, weights, shape: ModelShape, device='cuda', *, encoder_pack_tokens=65536,
-                 decoder_pack_tokens=16384):
+                 decoder_pack_tokens=16384, linears='bf16'):
         ops.device_check()
+        if linears not in ('bf16', 'fp8'):
+            raise ValueError("linears must be 'bf16' or 'fp8'")
+        self.linears, fp8 = linears, linears == 'fp8'
         self.shape, self.device = shape, torch.device(device)
         self.encoder_pack_tokens, self.decoder_pack_tokens = encoder_pack_tokens, decoder_pack_tokens
         g = lambda name: weights[name].to(device=self.device, dtype=BF16).contiguous()   # noqa: E731
         self.table = g('encoder.text_model.embed_tokens.weight')
         self.eoi = g('encoder.text_model.embed_tokens.eoi_embedding')
         self.enc_norm, self.dec_norm = g('encoder.text_model.norm.weight'), g('decoder.norm.weight')
-        self.enc = [_stack_layer(weights, f'encoder.text_model.layers.{i}.', self.device) for i in range(shape.layers)]
-        self.dec = [_stack_layer(weights, f'decoder.layers.{i}.', self.device) for i in range(shape.layers)]
+        self.enc = [_stack_layer(weights, f'encoder.text_model.layers.{i}.', self.device, fp8) for i in range(shape.layers)]
+        self.dec = [_stack_layer(weights, f'decoder.layers.{i}.', self.device, fp8, True) for i in range(shape.layers)]
         self.head_w, self.head_c, self.head_g = g('head.w.weight'), g('head.candidate.weight'), g('head.global_readout.weight')
         self.embed_scale = embed_scale(shape, BF16)
         self.launches = 0          # kernels launched by this library (for reporting)
@@ -153,6 +161,12 @@ class JudgmentEngine:
     def _freqs(self, index):
         return ops.inv_freq(self.shape.head_dim, self.shape.layer_theta(index), self.device)
 
+    @staticmethod
+    def _lin(x, w, geglu=False):
+        if isinstance(w, ops.Fp8Weight):
+            return ops.linear_fp8(x, w, geglu=geglu)
+        return ops.linear_geglu(x, w) if geglu else ops.linear(x, w)
+
     def _stack(self, layers, final_norm, pack, cross=None):
         s = self.shape
         x = ops.embed(pack.ids, self.table, self.eoi, self.embed_scale, s.eoi_token)
@@ -161,17 +175,17 @@ class JudgmentEngine:
         qd, kd = s.q_dim, s.kv_dim
         self.launches += 2
         for index, lw in enumerate(layers):
-            qkv = ops.linear(n, lw.wqkv)
+            qkv = self._lin(n, lw.wqkv)
             q = qkv[:, :qd].view(t, s.q_heads, s.head_dim)
             k = qkv[:, qd:qd + kd].view(t, s.kv_heads, s.head_dim)
             v = qkv[:, qd + kd:].view(t, s.kv_heads, s.head_dim)
             ops.qk_norm_rope_(q, k, lw.q_norm, lw.k_norm, pack.positions, self._freqs(index), s.eps)
             a = ops.varlen_attention(q, k, v, pack.plans[pack.keys[index]], s.scale,
                                      None if cross is None else cross[index])
-            o = ops.linear(a, lw.wo)
+            o = self._lin(a, lw.wo)
             n2 = ops.add_rmsnorm_(o, lw.post_attn, x, lw.pre_ffn, s.eps)
-            h = ops.linear_geglu(n2, lw.wgu)
-            d = ops.linear(h, lw.wdown)
+            h = self._lin(n2, lw.wgu, geglu=True)
+            d = self._lin(h, lw.wdown)
             nxt = layers[index + 1].pre_attn if index + 1 < len(layers) else final_norm
             n = ops.add_rmsnorm_(d, lw.post_ffn, x, nxt, s.eps)
             self.launches += 8
@@ -183,7 +197,7 @@ class JudgmentEngine:
         s = self.shape
         out = []
         for lw in self.dec:
-            kv = ops.linear(state, lw.wqkv[s.q_dim:])
+            kv = self._lin(state, lw.wkv)
             k = kv[:, :s.kv_dim].view(-1, s.kv_heads, s.head_dim)
             v = kv[:, s.kv_dim:].view(-1, s.kv_heads, s.head_dim)
             ops.qk_norm_rope_(None, k, None, lw.k_norm, None, None, s.eps, rotate=False)

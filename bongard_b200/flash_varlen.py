@@ -1,0 +1,96 @@
+"""Packed varlen attention behind the reference's flash_varlen surface.
+
+Mirrors bongard/flash_varlen.py: `attention(q, k, v, layout, scale, window, cross=None)` with
+tensors in [1, heads, tokens, D] order.  Two differences, both extensions:
+  - an ACTIVE window is accepted (the reference raises ValueError and falls back to a Triton
+    kernel, bongard/flash_varlen.py:130-131);
+  - the decoder path never materialises per-question copies of the state K/V
+    (bongard/flash_varlen.py:61-63 `_prefix_keys`): the kernel streams the owner's state as a
+    key prefix.
+The two forward custom ops keep the reference's output contract
+(out shaped like q [T, Hq, D], lse [Hq, T] fp32; bongard/flash_varlen.py:25-27, 80-82).
+They are inference ops: no autograd formula is registered.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import ops
+
+
+def _plan_from_cu(cu_q, window, group, device, *, decoder=False, cu_k=None):
+    """Attention plan from cu_seqlens tensors (synchronises: the custom-op surface carries no host lengths)."""
+    lengths = (cu_q[1:] - cu_q[:-1]).tolist()
+    if not decoder:
+        return ops.make_plan(lengths, window, device, group=group)
+    key_lengths = (cu_k[1:] - cu_k[:-1]).tolist()
+    state_lengths = [k - n for k, n in zip(key_lengths, lengths)]
+    return ops.make_plan(lengths, window, device, group=group, owners=list(range(len(lengths))),
+                         state_lengths=state_lengths)
+
+
+def flash_packed_forward(q, k, v, cuq, cuk, scale, causal):
+    """Encoder form of the op `bongard::flash_packed_forward` (bongard/flash_varlen.py:13-22):
+    q [T,Hq,D], k/v [T,Hkv,D], non-causal attention inside each cu_seqlens segment."""
+    if causal:
+        raise ValueError('causal packed attention goes through flash_prefix_forward (state-prefix keys)')
+    plan = _plan_from_cu(cuq, None, q.shape[1] // k.shape[1], q.device)
+    out, lse = ops.varlen_attention(q, k, v, plan, scale, return_lse=True)
+    return out.view(q.shape), lse
+
+
+def flash_prefix_forward(q, k, v, ck, cv, indices, cuq, cuk, scale):
+    """Decoder form, op `bongard::flash_prefix_forward` (bongard/flash_varlen.py:66-77): keys of
+    question i are [state_i | own_i] with bottom-right causal alignment.  `indices` (the gather
+    the reference needs) is accepted and ignored; state segments are taken in question order,
+    i.e. ck/cv hold one state per question back to back, or the caller uses `attention` below
+    with a layout that knows the owners."""
+    plan = _plan_from_cu(cuq, None, q.shape[1] // k.shape[1], q.device, decoder=True, cu_k=cuk)
+    out, lse = ops.varlen_attention(q, k, v, plan, scale, (ck, cv), return_lse=True)
+    return out.view(q.shape), lse
+
+
+def _register():
+    """Expose the two forwards as torch custom ops under the reference's names when that
+    namespace is still free (the reference registers the same names if it is imported)."""
+    try:
+        torch.library.custom_op('bongard::flash_packed_forward', mutates_args=())(_packed_op)
+        torch.library.custom_op('bongard::flash_prefix_forward', mutates_args=())(_prefix_op)
+        return True
+    except Exception:   # already registered by the reference package
+        return False
+
+
+def _packed_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cuq: torch.Tensor, cuk: torch.Tensor,
+               scale: float, causal: bool) -> tuple[torch.Tensor, torch.Tensor]:
+    return flash_packed_forward(q, k, v, cuq, cuk, scale, causal)
+
+
+def _prefix_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ck: torch.Tensor, cv: torch.Tensor,
+               indices: torch.Tensor, cuq: torch.Tensor, cuk: torch.Tensor, scale: float
+               ) -> tuple[torch.Tensor, torch.Tensor]:
+    return flash_prefix_forward(q, k, v, ck, cv, indices, cuq, cuk, scale)
+
+
+REGISTERED = _register()
+
+
+def attention(q, k, v, layout, scale, window, cross=None):
+    """bongard/flash_varlen.py:129-139.  q [1,Hq,T,D], k/v [1,Hkv,T,D], cross (ck, cv) [1,Hkv,S,D];
+    returns [1,Hq,T,D].  The [heads, tokens, D] storage is read in place (the kernel takes
+    head and token strides), so nothing is transposed on the way in."""
+    if q.ndim != 4 or q.shape[0] != 1:
+        raise ValueError('packed attention expects [1, heads, tokens, head_dim] tensors')
+    q3, k3, v3 = (t[0].transpose(0, 1) for t in (q, k, v))
+    if k3.stride() != v3.stride():
+        k3, v3 = k[0].contiguous().transpose(0, 1), v[0].contiguous().transpose(0, 1)
+    cr = None
+    if cross is not None:
+        ck, cv = (t[0].transpose(0, 1) if t.ndim == 4 else t for t in cross)
+        if ck.stride() != cv.stride():
+            ck, cv = cross[0][0].contiguous().transpose(0, 1), cross[1][0].contiguous().transpose(0, 1)
+        cr = (ck, cv)
+    plan = layout.plan(window, q3.shape[1] // k3.shape[1])
+    out = ops.varlen_attention(q3, k3, v3, plan, scale, cr)
+    return out.view(q3.shape[0], q3.shape[1], q3.shape[2]).transpose(0, 1)[None]

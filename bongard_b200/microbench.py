@@ -84,6 +84,18 @@ def mlp(args, flush):
         out.append(dict(op=f'gemm_bf16_{name}', tokens=t, ms=ms, tflops=flops / ms / 1e9, min_bytes=nbytes))
     both = timed(lambda: ops.linear(ops.linear_geglu(x, wgu), wd), args.iters, args.warmup, flush)
     out.append(dict(op='geglu_mlp', tokens=t, ms=both, tflops=6 * t * h * i / both / 1e9))
+    if args.fp8:
+        qgu, qd = ops.quantize_weight(wgu), ops.quantize_weight(wd)
+        xq, xs = ops.quantize_rows(x)
+        hq, hs = ops.quantize_rows(hidden)
+        for name, fn, flops in (
+                ('quantize_rows_x', lambda: ops.quantize_rows(x), 0),
+                ('gemm_fp8_gate_up_geglu', lambda: ops.gemm_fp8(xq, xs, qgu, geglu=True), 4 * t * h * i),
+                ('gemm_fp8_down', lambda: ops.gemm_fp8(hq, hs, qd), 2 * t * h * i),
+                ('geglu_mlp_fp8_with_quantisation',
+                 lambda: ops.linear_fp8(ops.linear_fp8(x, qgu, geglu=True), qd), 6 * t * h * i)):
+            ms = timed(fn, args.iters, args.warmup, flush)
+            out.append(dict(op=name, tokens=t, ms=ms, tflops=flops / ms / 1e9))
     return out
 
 
@@ -124,6 +136,7 @@ def main():
     ap.add_argument('--tokens', type=int, default=32768)
     ap.add_argument('--iters', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--fp8', action='store_true', help='mlp: also time the E4M3 block-scaled path')
     ap.add_argument('--flush', action='store_true', help='write a 256 MB buffer between launches')
     args = ap.parse_args()
     ops.device_check()

@@ -131,6 +131,23 @@ def qk_norm_rope_(q, k, q_weight, k_weight, positions, freqs, eps=1e-6, rotate=T
         tokens, head_dim, eps, 1 if rotate else 0, _stream()), 'bg_qk_norm_rope')
 
 
+def qk_norm_rope_table_(q, k, q_weight, k_weight, cos, sin, eps=1e-6):
+    """In place on q [T,Hq,D], k [T,Hkv,D] with bf16 cos / sin tables [T, D]."""
+    lib = _lib.load()
+    tokens, head_dim = q.shape[0], q.shape[-1]
+    for t, name in ((q, 'q'), (k, 'k')):
+        _need(t, name)
+        if t.stride(-1) != 1 or t.stride(1) != head_dim:
+            raise ValueError(f'{name} heads must be contiguous [T, heads, D]')
+    cos, sin = _need(cos, 'cos').contiguous(), _need(sin, 'sin').contiguous()
+    if cos.shape != (tokens, head_dim) or sin.shape != (tokens, head_dim):
+        raise ValueError(f'cos/sin must be [{tokens}, {head_dim}]')
+    _lib.check(lib.bg_qk_norm_rope_table(_ptr(q), q.stride(0), q.shape[1], _ptr(k), k.stride(0), k.shape[1],
+                                         _ptr(_need(q_weight, 'q_weight')), _ptr(_need(k_weight, 'k_weight')),
+                                         _ptr(cos), _ptr(sin), tokens, head_dim, eps, _stream()),
+               'bg_qk_norm_rope_table')
+
+
 def embed(ids, table, eoi_embedding, scale, eoi_token=256_000):
     lib = _lib.load()
     _need(ids, 'ids', torch.int64), _need(table, 'table')
@@ -296,29 +313,29 @@ def varlen_attention(q, k, v, plan, scale, cross=None, return_lse=False):
     lib = _lib.load()
     for t, name in ((q, 'q'), (k, 'k'), (v, 'v')):
         _need(t, name)
-        if t.ndim != 3 or t.stride(2) != 1 or t.stride(1) != t.shape[2]:
-            raise ValueError(f'{name} must be [T, heads, D] with contiguous heads')
-    if k.stride(0) != v.stride(0) or k.shape != v.shape:
-        raise ValueError('k and v must share shape and token stride')
+        if t.ndim != 3 or t.stride(2) != 1:
+            raise ValueError(f'{name} must be [T, heads, D] with a contiguous last dimension')
+    if k.stride() != v.stride() or k.shape != v.shape:
+        raise ValueError('k and v must share shape and strides')
     tq, hq, d = q.shape
     tk, hkv = k.shape[0], k.shape[1]
     if plan.tokens != tq:
         raise ValueError(f'plan was built for {plan.tokens} tokens, q has {tq}')
     ck = cv = None
-    ts = ldc = 0
+    ts = ldc = hsc = 0
     if cross is not None:
         ck, cv = cross
         _need(ck, 'cross keys'), _need(cv, 'cross values')
-        if ck.shape != cv.shape or ck.stride(0) != cv.stride(0) or ck.shape[1:] != k.shape[1:] \
-                or ck.stride(2) != 1 or ck.stride(1) != d:
-            raise ValueError('cross keys/values must be [S, kv_heads, D] with one token stride')
-        ts, ldc = ck.shape[0], ck.stride(0)
+        if ck.shape != cv.shape or ck.stride() != cv.stride() or ck.shape[1:] != k.shape[1:] or ck.stride(2) != 1:
+            raise ValueError('cross keys/values must be [S, kv_heads, D] with equal strides')
+        ts, ldc, hsc = ck.shape[0], ck.stride(0), ck.stride(1)
     out = torch.empty((tq, hq * d), device=q.device, dtype=BF16)
     lse = torch.empty((hq, tq), device=q.device, dtype=torch.float32) if return_lse else None
     timer = ATTN_TIMER
     begin = timer.start() if timer is not None else None
     _lib.check(lib.bg_varlen_attention(
-        _ptr(q), q.stride(0), _ptr(k), _ptr(v), k.stride(0), _ptr(ck), _ptr(cv), ldc, _ptr(out), _ptr(lse),
+        _ptr(q), q.stride(0), q.stride(1), _ptr(k), _ptr(v), k.stride(0), k.stride(1), _ptr(ck), _ptr(cv), ldc, hsc,
+        _ptr(out), _ptr(lse),
         _ptr(plan.tiles), plan.n_tiles, _ptr(plan.row_lo), _ptr(plan.row_hi), tq, tk, ts, hq, hkv, d,
         float(scale), _stream()), 'bg_varlen_attention')
     if timer is not None:
@@ -353,3 +370,86 @@ def candidate_softmax(logits, offsets, temperature=1.0):
     _lib.check(lib.bg_candidate_softmax(_ptr(logits), _ptr(offsets), _ptr(probs), offsets.numel() - 1,
                                         float(temperature), _stream()), 'bg_candidate_softmax')
     return probs
+
+
+# --------------------------------------------------------------------------------------
+# FP8 E4M3 with per-128 block scales
+# --------------------------------------------------------------------------------------
+
+@dataclass
+class Fp8Weight:
+    """A weight quantised once: E4M3 values [N, K] (uint8 storage) and inverse scales per 128 x 128 tile."""
+
+    q: torch.Tensor
+    inv_scale: torch.Tensor
+    shape: tuple
+
+
+def quantize_rows(x):
+    """1 x 128 dynamic quantisation of x [M, K] -> (q uint8 [M, K], inverse scales fp32 [K/128, M])."""
+    lib = _lib.load()
+    flat, m, k, ldx = _rows(x, 'x')
+    q = torch.empty((m, k), device=x.device, dtype=torch.uint8)
+    inv = torch.empty((k // 128, m), device=x.device, dtype=torch.float32)
+    _lib.check(lib.bg_quantize_e4m3_rows(_ptr(flat), ldx, _ptr(q), k, _ptr(inv), m, k, _stream()),
+               'bg_quantize_e4m3_rows')
+    return q, inv
+
+
+def quantize_weight(weight):
+    """128 x 128 dynamic quantisation of a [N, K] weight."""
+    lib = _lib.load()
+    _need(weight, 'weight')
+    if weight.ndim != 2 or weight.stride(1) != 1:
+        raise ValueError('weight must be [N, K] with contiguous rows')
+    n, k = weight.shape
+    q = torch.empty((n, k), device=weight.device, dtype=torch.uint8)
+    inv = torch.empty(((n + 127) // 128, k // 128), device=weight.device, dtype=torch.float32)
+    _lib.check(lib.bg_quantize_e4m3_tiles(_ptr(weight), weight.stride(0), _ptr(q), k, _ptr(inv), n, k, _stream()),
+               'bg_quantize_e4m3_tiles')
+    return Fp8Weight(q, inv, (n, k))
+
+
+_WORKSPACE = {}
+
+
+def _workspace(device, nbytes):
+    """A grow-only scratch buffer per device for the quantised activations of bg_linear_fp8."""
+    buf = _WORKSPACE.get(device)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), device=device, dtype=torch.uint8)
+        _WORKSPACE[device] = buf
+    return buf
+
+
+def linear_fp8(x, weight: Fp8Weight, *, geglu=False):
+    """bf16 x [..., K] times an Fp8Weight: dynamic 1 x 128 activation scales, E4M3 tensor-core
+    contraction, fp32 accumulation, bf16 result.  geglu=True treats the weight as [gate; up]."""
+    lib = _lib.load()
+    flat, m, k, ldx = _rows(x, 'x')
+    rows, wk = weight.shape
+    if wk != k:
+        raise ValueError(f'weight has K={wk}, input has {k}')
+    n = rows // 2 if geglu else rows
+    out = torch.empty((m, n), device=x.device, dtype=BF16)
+    need = lib.bg_linear_fp8_workspace_bytes(m, k)
+    ws = _workspace(x.device, need)
+    timer = GEMM_TIMER
+    begin = timer.start() if timer is not None else None
+    _lib.check(lib.bg_linear_fp8(_ptr(flat), ldx, _ptr(weight.q), k, _ptr(weight.inv_scale), _ptr(out), n, m, n, k,
+                                 1 if geglu else 0, _ptr(ws), ws.numel(), _stream()), 'bg_linear_fp8')
+    if timer is not None:
+        timer.stop(begin, (4 if geglu else 2) * m * n * k)
+    return out.view(*x.shape[:-1], n)
+
+
+def gemm_fp8(aq, a_inv_t, weight: Fp8Weight, *, geglu=False):
+    """Pre-quantised activations (from quantize_rows) times an Fp8Weight."""
+    lib = _lib.load()
+    m, k = aq.shape
+    rows = weight.shape[0]
+    n = rows // 2 if geglu else rows
+    out = torch.empty((m, n), device=aq.device, dtype=BF16)
+    _lib.check(lib.bg_gemm_fp8_block128(_ptr(aq), k, _ptr(a_inv_t), _ptr(weight.q), k, _ptr(weight.inv_scale),
+                                        _ptr(out), n, m, n, k, 1 if geglu else 0, _stream()), 'bg_gemm_fp8_block128')
+    return out

@@ -1,0 +1,122 @@
+"""Packed layouts and the per-layer attention wrappers, with the reference's call surfaces.
+
+Mirrors bongard/packing.py: `PackedLayout`, `packed_layout`, `layout_attention`,
+`encoder_attention`, `decoder_attention` keep their names, argument meaning and error
+behaviour, so the reference's own `forward_packed` (bongard/packing.py:228-318) and its
+attention modules can call them unchanged with `backend='b200'`.  What changes is what sits
+behind them: every window - active or not - is served by one CUDA kernel, so a layout never
+carries dense masks, FlexAttention block masks, short/long partitions or gathered key indices.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from itertools import accumulate
+
+import torch
+
+from . import ops
+
+
+@dataclass
+class PackedLayout:
+    """Same fields as the reference's PackedLayout (bongard/packing.py:42-51); `masks`,
+    `key_indices` and `partitions` stay empty because the kernel needs none of them."""
+
+    positions: torch.Tensor                      # int64 [1, T], restarting at every segment
+    masks: dict = field(default_factory=dict)
+    backend: str = 'b200'
+    cu_seqlens: torch.Tensor | None = None       # int32 [n + 1]
+    key_seqlens: torch.Tensor | None = None      # int32 [n + 1], decoder: state + own keys per question
+    key_indices: torch.Tensor | None = None
+    flash_windows: frozenset = frozenset()
+    partitions: dict = field(default_factory=dict)
+    # host-side description the attention plans are built from
+    lengths: tuple = ()
+    owners: tuple | None = None
+    state_lengths: tuple | None = None
+    positions32: torch.Tensor | None = None      # int32 [T]
+    plans: dict = field(default_factory=dict)    # (window, group) -> ops.AttentionPlan
+
+    @property
+    def decoder(self):
+        return self.owners is not None
+
+    def effective_window(self, window):
+        """None when the window covers every segment (the reference's own test for routing a
+        layer to its dense kernel, bongard/packing.py:84-85)."""
+        if window is None or not self.lengths:
+            return None
+        reach = window if self.decoder else (window + 1) // 2
+        return None if max(self.lengths) <= reach else window
+
+    def plan(self, window, group):
+        key = (self.effective_window(window), group)
+        if key not in self.plans:
+            self.plans[key] = ops.make_plan(self.lengths, key[0], self.positions.device, group=group,
+                                            owners=self.owners, state_lengths=self.state_lengths)
+        return self.plans[key]
+
+
+def packed_layout(lengths, windows, device, *, owners=None, state_lengths=None, backend='b200'):
+    """Build once per pack; every layer shares it (bongard/packing.py:54-151).
+
+    `windows` is accepted for signature compatibility: plans are built lazily per window."""
+    if backend != 'b200':
+        raise ValueError(f"bongard_b200 serves backend 'b200' only, got {backend!r}")
+    lengths = tuple(int(n) for n in lengths)
+    if owners is not None and state_lengths is None:
+        raise ValueError('decoder layouts need state_lengths')
+    device = torch.device(device)
+    positions = torch.cat([torch.arange(n) for n in lengths]) if lengths else torch.zeros(0, dtype=torch.long)
+    cu = torch.tensor(list(accumulate(lengths, initial=0)), dtype=torch.int32)
+    key_cu = None
+    if owners is not None:
+        key_cu = torch.tensor(list(accumulate((state_lengths[o] + n for o, n in zip(owners, lengths)), initial=0)),
+                              dtype=torch.int32).to(device)
+    positions = positions.to(device)
+    return PackedLayout(positions[None], {}, backend, cu.to(device), key_cu, None,
+                        frozenset(set(windows)), {}, lengths,
+                        None if owners is None else tuple(int(o) for o in owners),
+                        None if state_lengths is None else tuple(int(s) for s in state_lengths),
+                        positions.to(torch.int32))
+
+
+def layout_attention(q, k, v, layout, scale, window, cross=None, dropout=0.0):
+    """bongard/packing.py:178-198.  q [1,Hq,T,D]; k, v [1,Hkv,T,D]; cross = (ck, cv) [1,Hkv,S,D]."""
+    from .flash_varlen import attention
+
+    if dropout:
+        raise ValueError('Packed CUDA attention requires zero attention dropout')
+    return attention(q, k, v, layout, scale, window, cross)
+
+
+def _project(module, hidden_states, layout_positions, position_embeddings):
+    """q, k (normalised and rotated) and v as [T, heads, D] views of one projection buffer."""
+    from .attention import fused_qkv
+
+    return fused_qkv(module, hidden_states, positions=layout_positions, position_embeddings=position_embeddings)
+
+
+def encoder_attention(module, hidden_states, position_embeddings, layout):
+    """bongard/packing.py:201-210: projections, QK-norm + RoPE, packed attention, o_proj."""
+    q, k, v = _project(module, hidden_states, layout.positions32, position_embeddings)
+    group = q.shape[1] // k.shape[1]
+    out = ops.varlen_attention(q, k, v, layout.plan(module.sliding_window, group), module.scaling)
+    from .attention import project_out
+
+    return project_out(module, out, hidden_states.shape), None
+
+
+def decoder_attention(module, hidden_states, position_embeddings, cache, layout, packed_cross=None):
+    """bongard/packing.py:213-225: as above with the owner's state K/V as key prefix."""
+    from .attention import as_token_major, project_out
+
+    q, k, v = _project(module, hidden_states, layout.positions32, position_embeddings)
+    if packed_cross is None:
+        cross = cache.cross_attention_cache.layers[module.layer_idx]
+        packed_cross = (cross.keys, cross.values)
+    ck, cv = as_token_major(packed_cross[0]), as_token_major(packed_cross[1])
+    group = q.shape[1] // k.shape[1]
+    out = ops.varlen_attention(q, k, v, layout.plan(module.sliding_window, group), module.scaling, (ck, cv))
+    return project_out(module, out, hidden_states.shape), None, None

@@ -65,6 +65,14 @@ int bg_qk_norm_rope(void* q, int64_t ldq, int q_heads, void* k, int64_t ldk, int
                     const void* k_weight, const int32_t* positions, const float* inv_freq, int64_t tokens,
                     int head_dim, float eps, int rotate, void* stream);
 
+/* The same in-place norm + rotation with caller-supplied bf16 cos / sin tables [tokens, D]
+ * (cat(freqs, freqs) layout, as the rotary module returns them).
+ * Replaces the (q, k, q_norm, k_norm, position_embeddings) surface of
+ * bongard/flash_attention.py:76-125 metal_qk_norm_rope and bongard/attention.py:172-180 project_qk. */
+int bg_qk_norm_rope_table(void* q, int64_t ldq, int q_heads, void* k, int64_t ldk, int k_heads,
+                          const void* q_weight, const void* k_weight, const void* cos_table, const void* sin_table,
+                          int64_t tokens, int head_dim, float eps, void* stream);
+
 /* out[r, :] = table[ids[r], :] * scale, or eoi_embedding where ids[r] == eoi_token.  ids int64.
  * Replaces HF:644-647 T5Gemma2TextScaledWordEmbedding.forward. */
 int bg_embed(const int64_t* ids, const void* table, const void* eoi_embedding, void* out, int64_t rows, int64_t h,
@@ -79,9 +87,39 @@ int bg_embed(const int64_t* ids, const void* table, const void* eoi_embedding, v
 int bg_gemm_bf16(const void* a, int64_t lda, const void* w, int64_t ldw, void* out, int64_t ldo, int64_t m,
                  int64_t n, int64_t k, int epilogue, void* stream);
 
+/* E4M3 quantisation with dynamic per-block scales: scale = 448 / max(amax, 1e-12), values clamped
+ * to +-448 and rounded to nearest; the INVERSE scales are stored as fp32.
+ *   rows : 1 x 128 blocks of x [m, k] -> q (uint8 [m, k], row stride ldq bytes), inv_scale_t [k/128, m].
+ *   tiles: 128 x 128 blocks of w [n, k] -> q, inv_scale [ceil(n/128), k/128].
+ * Replaces the per-call dynamic scaling of the reference's FP8 linears
+ * (bongard/float8_training.py:35-44; torchao Float8Linear casts) at 128-element granularity. */
+int bg_quantize_e4m3_rows(const void* x, int64_t ldx, void* q, int64_t ldq, float* inv_scale_t, int64_t m, int64_t k,
+                          void* stream);
+int bg_quantize_e4m3_tiles(const void* w, int64_t ldw, void* q, int64_t ldq, float* inv_scale, int64_t n, int64_t k,
+                           void* stream);
+
+/* out[m, n] = sum over 128-deep K blocks of a_inv_t[kb, m] * w_inv[n/128, kb] * (aq . wq^T), E4M3
+ * operands on tcgen05 (kind::f8f6f4), fp32 accumulate, bf16 out.  Epilogues as bg_gemm_bf16.
+ * Replaces the scaled GEMM behind bongard/float8_training.py:12-24 TrainingLinear.forward
+ * (torch._scaled_mm) and the `fp8` recipe of bongard/te_linear.py:32-39 / bongard/fused_mlp.py:21-79. */
+int bg_gemm_fp8_block128(const void* aq, int64_t lda, const float* a_inv_t, const void* wq, int64_t ldw,
+                         const float* w_inv, void* out, int64_t ldo, int64_t m, int64_t n, int64_t k, int epilogue,
+                         void* stream);
+
+/* bf16 activation in, FP8 contraction: x is quantised (1 x 128 blocks) into `workspace`, then
+ * multiplied with pre-quantised weights.  bg_linear_fp8_workspace_bytes(m, k) gives the scratch
+ * size; the workspace must be 256-byte aligned and is owned by the caller.
+ * Replaces bongard/float8_training.py:17-22 / bongard/te_linear.py:59-77 forward in FP8 mode. */
+int64_t bg_linear_fp8_workspace_bytes(int64_t m, int64_t k);
+int bg_linear_fp8(const void* x, int64_t ldx, const void* wq, int64_t ldw, const float* w_inv, void* out,
+                  int64_t ldo, int64_t m, int64_t n, int64_t k, int epilogue, void* workspace,
+                  int64_t workspace_bytes, void* stream);
+
 /* Packed variable-length attention, one softmax over [prefix keys | own keys].
- *   q [tq, q_heads, D] (token stride ldq); k, v [tk, kv_heads, D] (stride ldkv);
- *   ck, cv [ts, kv_heads, D] (stride ldc) or NULL; out [tq, q_heads * D] contiguous;
+ *   q [tq, q_heads, D] (token stride ldq, head stride hsq); k, v [tk, kv_heads, D] (strides ldkv,
+ *   hskv); ck, cv [ts, kv_heads, D] (strides ldc, hsc) or NULL - any token/head strides that are
+ *   multiples of 8 elements, so both [T, H, D] and [H, T, D] storage work without a copy;
+ *   out [tq, q_heads * D] contiguous;
  *   lse fp32 [q_heads, tq] (natural log) or NULL.
  *   tiles int32 [n_tiles, 8] = {q_start, q_count, own_lo, own_hi, lo_max, hi_min, prefix_start,
  *   prefix_len}: q_count <= 128 / (q_heads / kv_heads) consecutive query tokens; [own_lo, own_hi)
@@ -91,8 +129,9 @@ int bg_gemm_bf16(const void* a, int64_t lda, const void* w, int64_t ldw, void* o
  * 61-77 _prefix (op bongard::flash_prefix_forward, without materialising the gathered keys), the
  * windowed layers bongard/packing.py:154-175 packed_attention serves, and the two-partition
  * serving path bongard/attention.py:122-169. */
-int bg_varlen_attention(const void* q, int64_t ldq, const void* k, const void* v, int64_t ldkv, const void* ck,
-                        const void* cv, int64_t ldc, void* out, float* lse, const int32_t* tiles,
+int bg_varlen_attention(const void* q, int64_t ldq, int64_t hsq, const void* k, const void* v, int64_t ldkv,
+                        int64_t hskv, const void* ck, const void* cv, int64_t ldc, int64_t hsc, void* out,
+                        float* lse, const int32_t* tiles,
                         int32_t n_tiles, const int32_t* row_lo, const int32_t* row_hi, int64_t tq, int64_t tk,
                         int64_t ts, int q_heads, int kv_heads, int head_dim, float scale, void* stream);
 

@@ -191,10 +191,11 @@ def quantize_e4m3_block(x, block_rows, block_cols):
     br, bc = xf.shape[0] // block_rows, xf.shape[1] // block_cols
     tiles = xf.reshape(br, block_rows, bc, block_cols)
     amax = tiles.abs().amax(dim=(1, 3))
-    scale = E4M3_MAX / amax.clamp_min(1e-12)
+    # tensor / tensor is an IEEE division (a python scalar divided by a tensor is reciprocal-multiply)
+    scale = torch.full_like(amax, E4M3_MAX) / amax.clamp_min(1e-12)
     q = (tiles * scale[:, None, :, None]).clamp(-E4M3_MAX, E4M3_MAX)
     q = q.reshape(xf.shape)[:rows, :cols].to(torch.float8_e4m3fn)
-    return q, (1.0 / scale).float()
+    return q, (torch.ones_like(scale) / scale).float()
 
 
 def dequantize_block(q, inv_scale, block_rows, block_cols):

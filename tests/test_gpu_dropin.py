@@ -1,0 +1,160 @@
+"""The reference-shaped call surfaces: module substitution into the Hugging Face backbone and
+the function-level entry points (flash_varlen.attention, project_qk, enable_* installers)."""
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from bongard_b200 import flash_varlen, ops, packing, workload as wl  # noqa: E402
+from bongard_b200 import attention as b200_attention  # noqa: E402
+from bongard_b200.engine import JudgmentEngine  # noqa: E402
+from bongard_b200.float8_training import enable_float8  # noqa: E402
+from bongard_b200.fused_mlp import B200FusedMLP, enable_fused_mlp  # noqa: E402
+from bongard_b200.hf import PackedJudge, build_backbone  # noqa: E402
+from bongard_b200.install import install_b200_inference  # noqa: E402
+from bongard_b200.te_linear import B200Linear, B200MLP, enable_te_linear  # noqa: E402
+from oracle import reference_math as om  # noqa: E402
+
+DEV = 'cuda'
+
+
+def probs_of(result):
+    return torch.cat([om.probabilities(v['logits'].float()) for a in result for v in a.values()])
+
+
+@pytest.fixture(scope='module')
+def tiny():
+    weights = wl.make_weights(wl.TINY, 1)
+    return weights, wl.tiny_requests(1)
+
+
+def test_module_substitution_matches_reference_fixture(golden_dir, tiny):
+    weights, requests = tiny
+    gold = np.load(golden_dir / 'tiny_config1.npz')
+    backbone = build_backbone(wl.TINY, weights)
+    counts = install_b200_inference(backbone)
+    assert counts == dict(encoder_attention=2, decoder_attention=2, mlp=4, norms=2 * 2 * 6 + 2)
+    names = set(backbone.state_dict())
+    assert 'encoder.text_model.layers.0.self_attn.q_proj.weight' in names       # HF-shaped keys survive
+    result = PackedJudge(backbone, weights).forward_packed(requests, 8)
+    probs = probs_of(result)
+    spread = float(np.abs(gold['probs_packed_fp32'] - gold['probs_packed_bf16']).max())
+    err = float((probs - torch.from_numpy(gold['probs_packed_fp32'])).abs().max())
+    assert err <= max(spread, 1e-3) * 1.25, (err, spread)
+    engine = probs_of(JudgmentEngine(weights, wl.TINY).forward_packed(requests, 8))
+    assert float((probs - engine).abs().max()) < 2e-3
+
+
+def test_padded_question_batch_matches_packed(tiny):
+    """The serving path's padded decoder batch (QuestionLayout) and the packed path agree."""
+    weights, requests = tiny
+    backbone = build_backbone(wl.TINY, weights)
+    install_b200_inference(backbone)
+    judge = PackedJudge(backbone, weights)
+    request = requests[0]
+    with torch.inference_mode():
+        state = judge.encode([request.state])
+        cross = judge.state_kv(state)
+        rows = [q.tokens for q in request.questions.values()]
+        packed = judge.decode(rows, [0] * len(rows), [len(request.state)], state, cross)
+        width = max(map(len, rows))
+        ids = torch.tensor([list(r) + [0] * (width - len(r)) for r in rows], device=DEV)
+        valid = torch.arange(width, device=DEV)[None, :] < torch.tensor([len(r) for r in rows], device=DEV)[:, None]
+        positions = (valid.long().cumsum(-1) - 1).clamp_min(0)
+        layout = b200_attention.QuestionLayout(valid, positions)
+        decoder = backbone.decoder
+        hidden = decoder.embed_tokens(ids)
+        emb = {t: decoder.rotary_emb(hidden, positions, t) for t in set(decoder.config.layer_types)}
+        empty = torch.empty(0, device=DEV)
+        for index, layer in enumerate(decoder.layers):
+            hidden = layer(hidden, emb[decoder.config.layer_types[index]], empty, positions, None, False, state,
+                           question_layout=layout, packed_cross=cross[index])
+        hidden = decoder.norm(hidden)
+    offset = 0
+    for i, r in enumerate(rows):
+        a, b = hidden[i, :len(r)].float(), packed[offset:offset + len(r)].float()
+        assert float((a - b).abs().max()) <= 2e-2 + 1e-2 * float(b.abs().max())
+        offset += len(r)
+
+
+@pytest.mark.parametrize('window', [None, 4, 16])
+def test_flash_varlen_attention_surface(golden_dir, window):
+    """bongard.flash_varlen.attention's signature, [1,H,T,D] tensors, incl. an ACTIVE window."""
+    g = {k: torch.from_numpy(v) for k, v in np.load(golden_dir / 'ops.npz').items() if k.startswith('att_')}
+    to = lambda t: t.bfloat16().to(DEV).transpose(0, 1)[None].contiguous()   # noqa: E731  [T,H,D] -> [1,H,T,D]
+    q, k, v, ck, cv = (to(g[n]) for n in ('att_q', 'att_k', 'att_v', 'att_ck', 'att_cv'))
+    lengths = g['att_lengths'].tolist()
+    layout = packing.packed_layout(lengths, [window], DEV)
+    out = flash_varlen.attention(q, k, v, layout, 0.125, window)
+    assert out.shape == q.shape
+    want = g[f'att_enc_w{window}']
+    assert float((out[0].transpose(0, 1).float().cpu() - want).abs().max()) < 4e-2
+    layout = packing.packed_layout(lengths, [window], DEV, owners=g['att_owners'].tolist(),
+                                   state_lengths=g['att_state_lengths'].tolist())
+    out = packing.layout_attention(q, k, v, layout, 0.125, window, (ck, cv))
+    want = g[f'att_dec_w{window}']
+    assert float((out[0].transpose(0, 1).float().cpu() - want).abs().max()) < 4e-2
+    with pytest.raises(ValueError):
+        packing.layout_attention(q, k, v, layout, 0.125, window, (ck, cv), dropout=0.1)
+    with pytest.raises(ValueError):
+        packing.packed_layout(lengths, [window], DEV, backend='triton')
+
+
+def test_custom_ops_keep_the_reference_contract():
+    t, hq, hkv, d = 50, 4, 2, 64
+    g = torch.Generator().manual_seed(0)
+    q, k, v = (torch.randn(t, h, d, generator=g).bfloat16().to(DEV) for h in (hq, hkv, hkv))
+    cu = torch.tensor([0, 20, 50], dtype=torch.int32, device=DEV)
+    out, lse = flash_varlen.flash_packed_forward(q, k, v, cu, cu, 0.125, False)
+    assert out.shape == q.shape and lse.shape == (hq, t) and lse.dtype == torch.float32
+    want, want_lse = om.varlen_attention(q.float().cpu(), k.float().cpu(), v.float().cpu(), [20, 30], 0.125, None)
+    assert float((out.float().cpu() - want).abs().max()) < 2e-2
+    assert float((lse.cpu() - want_lse).abs().max()) < 2e-2
+    if flash_varlen.REGISTERED:
+        out2, _ = torch.ops.bongard.flash_packed_forward(q, k, v, cu, cu, 0.125, False)
+        assert torch.equal(out2, out)
+
+
+def test_project_qk_surface(golden_dir, tiny):
+    weights, _ = tiny
+    g = {k: torch.from_numpy(v) for k, v in np.load(golden_dir / 'ops.npz').items() if k.startswith(('qk_', 'state_'))}
+    backbone = build_backbone(wl.TINY, weights)
+    attn = backbone.encoder.text_model.layers[0].self_attn
+    with torch.no_grad():
+        attn.q_proj.weight.copy_(g['qk_wq']); attn.k_proj.weight.copy_(g['qk_wk'])      # noqa: E702
+        attn.q_norm.weight.copy_(g['qk_qnorm']); attn.k_norm.weight.copy_(g['qk_knorm'])  # noqa: E702
+    hidden = g['qk_hidden'].bfloat16().to(DEV)[None]
+    pe = (g['qk_cos'].bfloat16().to(DEV)[None], g['qk_sin'].bfloat16().to(DEV)[None])
+    q, k = b200_attention.project_qk(attn, hidden, pe, 'b200')
+    assert q.shape == (1, 4, hidden.shape[1], 64) and k.shape == (1, 2, hidden.shape[1], 64)
+    assert float((q[0].transpose(0, 1).float().cpu() - g['qk_q']).abs().max()) < 6e-2
+    assert float((k[0].transpose(0, 1).float().cpu() - g['qk_k']).abs().max()) < 6e-2
+
+
+def test_enable_surfaces_and_fp8_end_to_end(tiny):
+    weights, requests = tiny
+    backbone = build_backbone(wl.TINY, weights)
+    assert enable_fused_mlp(backbone, 'bf16') == 4
+    assert isinstance(backbone.decoder.layers[0].mlp, B200FusedMLP)
+    assert isinstance(backbone.decoder.layers[0].pre_feedforward_layernorm, torch.nn.Identity)
+    with pytest.raises(ValueError):
+        enable_fused_mlp(backbone, 'nvfp4')
+    backbone = build_backbone(wl.TINY, weights)
+    assert enable_te_linear(backbone, mlp='bf16', attention='bf16') == {'mlp': 4, 'attention': 16}
+    assert isinstance(backbone.encoder.text_model.layers[0].mlp, B200MLP)
+    assert isinstance(backbone.encoder.text_model.layers[0].self_attn.o_proj, B200Linear)
+    with pytest.raises(ValueError):
+        enable_te_linear(backbone)
+    # FP8 everywhere: module path and engine agree with each other and stay near the bf16 result
+    backbone = build_backbone(wl.TINY, weights)
+    assert enable_float8(backbone, 'block128') == 2 * 2 * 7
+    install_b200_inference(backbone, linears='fp8')
+    p_mod = probs_of(PackedJudge(backbone, weights).forward_packed(requests, 8))
+    p_eng = probs_of(JudgmentEngine(weights, wl.TINY, linears='fp8').forward_packed(requests, 8))
+    p_bf16 = probs_of(JudgmentEngine(weights, wl.TINY).forward_packed(requests, 8))
+    assert float((p_mod - p_eng).abs().max()) < 5e-3
+    assert float((p_eng - p_bf16).abs().max()) < 3e-2
+    with pytest.raises(ValueError):
+        enable_float8(backbone, 'tensorwise')
