@@ -29,7 +29,6 @@ constexpr int B_BYTES = BN * BK * 2;        // 32 KB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 constexpr int THREADS = 192;
-constexpr int GROUP_M = 16;       // tile rasterisation: 16 row-tiles share each column panel in L2
 
 struct GemmParams {
     int m, n, k;                  // n = output columns
@@ -37,14 +36,15 @@ struct GemmParams {
     int64_t ldo;
     __nv_bfloat16* out;
     int tiles_m, tiles_n;
+    int group_m;                  // raster: this many row-tiles share each weight panel while it is in L2
     int32_t* status;
 };
 
-__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
-    int per_group = GROUP_M * tiles_n;
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
+    int per_group = group_m * tiles_n;
     int group = tile / per_group;
-    int first_m = group * GROUP_M;
-    int rows = min(GROUP_M, tiles_m - first_m);
+    int first_m = group * group_m;
+    int rows = min(group_m, tiles_m - first_m);
     int in_group = tile - group * per_group;
     tm = first_m + in_group % rows;
     tn = in_group / rows;
@@ -100,7 +100,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             uint32_t phase = 0;
             for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
                 int tm, tn;
-                tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+                tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
                 const int row0 = tm * BM;
                 // W rows: plain -> 256 consecutive output columns; GeGLU -> 128 gate rows + 128 up rows.
                 const int w0 = p.epilogue == 1 ? tn * 128 : tn * BN;
@@ -154,7 +154,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         int local = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
             int tm, tn;
-            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+            tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
             const int buf = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
             if (!mbar_wait(&acc_full[buf], acc_phase, ab, 104)) break;
@@ -234,6 +234,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
 }  // namespace
 
+int bg_gemm_bf16_pair_launch(const CUtensorMap& map_a, const CUtensorMap& map_w, void* out, int64_t ldo, int64_t m,
+                             int64_t n, int64_t k, int epilogue, cudaStream_t stream);
+
 extern "C" int bg_gemm_bf16(const void* a, int64_t lda, const void* w, int64_t ldw, void* out, int64_t ldo,
                             int64_t m, int64_t n, int64_t k, int epilogue, void* stream) {
     if (m < 0 || n <= 0 || k <= 0 || (epilogue != 0 && epilogue != 1)) {
@@ -262,11 +265,21 @@ extern "C" int bg_gemm_bf16(const void* a, int64_t lda, const void* w, int64_t l
                             CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
 
+    // More than one row tile: CTA pairs (256 x 256 tiles, a third less L2-to-SM traffic per FLOP).
+    if (m > BM) return bg_gemm_bf16_pair_launch(map_a, map_w, out, ldo, m, n, k, epilogue, static_cast<cudaStream_t>(stream));
+
     GemmParams p;
     p.m = (int)m; p.n = (int)n; p.k = (int)k; p.epilogue = epilogue; p.ldo = ldo;
     p.out = static_cast<__nv_bfloat16*>(out);
     p.tiles_m = (int)((m + BM - 1) / BM);
     p.tiles_n = epilogue == 1 ? (int)(n / 128) : (int)((n + BN - 1) / BN);
+    // Keep one group's activation rows (group_m x 128 x K bf16) at about a third of the 126 MB L2, so
+    // that every weight panel is fetched from DRAM once per group instead of once per 16 row-tiles.
+    {
+        const int64_t panel = int64_t(BM) * k * 2;
+        int64_t g = (40ll << 20) / (panel > 0 ? panel : 1);
+        p.group_m = (int)(g < 8 ? 8 : (g > 64 ? 64 : g));
+    }
     p.status = bg_status_word();
     if (!p.status) return BG_ERR_DRIVER;
 

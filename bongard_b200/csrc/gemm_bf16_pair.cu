@@ -1,0 +1,293 @@
+// BF16 contraction on CTA PAIRS (thread-block cluster of 2, tcgen05 cta_group::2).
+//
+//   out[M, N] = A[M, K] . W[N, K]^T, output tile 256 x 256 per pair.
+//
+// Why pairs: a single-CTA 128 x 256 tile has to pull 48 KB (A 16 KB + W 32 KB) from L2 into its
+// SM for every 512 tensor-core clocks, and that L2-to-SM stream, not the tensor pipe, is what
+// limits the single-CTA kernel.  In a pair each CTA loads its own 128 rows of A and only HALF
+// of the weight panel (128 of the 256 rows); one tcgen05.mma.cta_group::2 instruction issued
+// by the leader CTA drives both tensor cores with M = 256 and reads the two weight halves
+// from both CTAs' shared memory.  Per CTA that is 32 KB per 512 clocks - a third less - and
+// the smaller stages allow a 6-deep ring.
+//
+// Synchronisation between the two CTAs (all barriers sit at the same shared-memory offset in
+// both CTAs; nothing uses a multi-destination form):
+//   full[s]       leader only.  Both CTAs' TMA loads credit their bytes to the leader's barrier.
+//   empty[s]      one per CTA.  The leader commits twice: to its own barrier and to the peer's.
+//   acc_full[b]   one per CTA, same double commit.
+//   acc_empty[b]  leader only, 8 arrivals: 4 epilogue warps of each CTA (the peer arrives remotely).
+// Roles per CTA: warp 0 TMA producer, warp 1 MMA issuer (leader only), warps 2-5 epilogue.
+#include "common.cuh"
+
+namespace {
+
+using namespace bg;
+
+constexpr int BM = 128;           // rows per CTA (256 per pair)
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 6;
+constexpr int A_BYTES = BM * BK * 2;        // 16 KB
+constexpr int B_BYTES = (BN / 2) * BK * 2;  // 16 KB: this CTA's half of the weight panel
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int THREADS = 192;
+
+struct PairParams {
+    int m, n, k, epilogue;
+    int64_t ldo;
+    __nv_bfloat16* out;
+    int tiles_m, tiles_n;         // in units of 256-row pair tiles
+    int group_m;
+    int32_t* status;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
+    int per_group = group_m * tiles_n;
+    int group = tile / per_group;
+    int first_m = group * group_m;
+    int rows = min(group_m, tiles_m - first_m);
+    int in_group = tile - group * per_group;
+    tm = first_m + in_group % rows;
+    tn = in_group / rows;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                      const PairParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    uint64_t* full = bars;                        // [STAGES]
+    uint64_t* empty = bars + STAGES;              // [STAGES]
+    uint64_t* acc_full = bars + 2 * STAGES;       // [2]
+    uint64_t* acc_empty = bars + 2 * STAGES + 2;  // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const Abort ab{abort_flag, p.status};
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 8);
+        }
+        mbar_fence_init();
+        tma_prefetch_desc(&map_a);
+        tma_prefetch_desc(&map_w);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, 512);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();               // both CTAs' barriers are initialised before anyone signals across
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int pairs = gridDim.x >> 1, pair = blockIdx.x >> 1;
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int kblocks = (p.k + BK - 1) / BK;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int tile = pair; tile < num_tiles; tile += pairs) {
+                int tm, tn;
+                tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+                const int row0 = tm * 2 * BM + rank * BM;
+                // this CTA's half of the weight panel: plain -> columns [256 tn + 128 rank, +128);
+                // GeGLU -> rank 0 loads 128 gate rows, rank 1 the matching 128 up rows.
+                const int w0 = p.epilogue == 1 ? (rank == 0 ? tn * 128 : p.n + tn * 128) : tn * BN + rank * 128;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (!mbar_wait(&empty[stage], phase ^ 1, ab, 111)) break;
+                    uint8_t* sa = smem + stage * STAGE_BYTES;
+                    const uint32_t leader_full = map_to_cta(smem_u32(&full[stage]), 0);
+                    if (leader) mbar_expect_tx(&full[stage], 2 * STAGE_BYTES);
+                    tma_load_2d_pair(sa, &map_a, leader_full, kb * BK, row0);
+                    tma_load_2d_pair(sa + A_BYTES, &map_w, leader_full, kb * BK, w0);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = instr_desc(2 * BM, BN, 1, 1, 0, 0);
+            int stage = 0;
+            uint32_t phase = 0;
+            int local = 0;
+            for (int tile = pair; tile < num_tiles; tile += pairs, ++local) {
+                const int buf = local & 1;
+                if (!mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, ab, 112)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (!mbar_wait(&full[stage], phase, ab, 113)) break;
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+                    const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < BK / 16; ++kk) {
+                        uint64_t da = smem_desc_sw128(sa + kk * 32, 16, 1024);
+                        uint64_t db = smem_desc_sw128(sb + kk * 32, 16, 1024);
+                        mma_bf16_ss_pair(d_tmem, da, db, idesc, (kb | kk) != 0);
+                    }
+                    const uint32_t e = smem_u32(&empty[stage]);
+                    mma_commit_pair(map_to_cta(e, 0));
+                    mma_commit_pair(map_to_cta(e, 1));
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                const uint32_t f = smem_u32(&acc_full[buf]);
+                mma_commit_pair(map_to_cta(f, 0));
+                mma_commit_pair(map_to_cta(f, 1));
+            }
+        }
+    } else {
+        const int part = warp & 3;
+        const int row_in_tile = part * 32 + lane;
+        int local = 0;
+        for (int tile = pair; tile < num_tiles; tile += pairs, ++local) {
+            int tm, tn;
+            tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+            const int buf = local & 1;
+            if (!mbar_wait(&acc_full[buf], (local >> 1) & 1, ab, 114)) break;
+            tc_fence_after();
+            const int row = tm * 2 * BM + rank * BM + row_in_tile;
+            const uint32_t taddr = tmem_base + (uint32_t(part * 32) << 16) + buf * BN;
+            if (p.epilogue == 0) {
+                const int col0 = tn * BN;
+                __nv_bfloat16* dst = p.out + int64_t(row) * p.ldo + col0;
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(taddr + c, r);
+                    tmem_wait_ld();
+                    if (row < p.m) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            if (col0 + c + v * 8 < p.n) {
+                                uint4 o;
+                                o.x = pack_bf16(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+                                o.y = pack_bf16(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+                                o.z = pack_bf16(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+                                o.w = pack_bf16(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+                                *reinterpret_cast<uint4*>(dst + c + v * 8) = o;
+                            }
+                        }
+                    }
+                }
+            } else {
+                const int col0 = tn * 128;
+                __nv_bfloat16* dst = p.out + int64_t(row) * p.ldo + col0;
+#pragma unroll 1
+                for (int c = 0; c < 128; c += 32) {
+                    uint32_t g[32], u[32];
+                    tmem_ld32(taddr + c, g);
+                    tmem_ld32(taddr + 128 + c, u);
+                    tmem_wait_ld();
+                    if (row < p.m) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            float h[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e)
+                                h[e] = gelu_tanh(__uint_as_float(g[v * 8 + e])) * __uint_as_float(u[v * 8 + e]);
+                            uint4 o;
+                            o.x = pack_bf16(h[0], h[1]);
+                            o.y = pack_bf16(h[2], h[3]);
+                            o.z = pack_bf16(h[4], h[5]);
+                            o.w = pack_bf16(h[6], h[7]);
+                            *reinterpret_cast<uint4*>(dst + c + v * 8) = o;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
+        }
+    }
+
+    // Neither CTA may leave while the other can still signal its barriers or read its shared memory.
+    tc_fence_before();
+    __syncthreads();
+    if (ab.raised()) {
+        uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) __nanosleep(1000);
+        __syncthreads();
+    }
+    cluster_sync();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, 512);
+    }
+}
+
+}  // namespace
+
+// Launcher used by bg_gemm_bf16 for every problem with more than 128 rows.
+int bg_gemm_bf16_pair_launch(const CUtensorMap& map_a, const CUtensorMap& map_w, void* out, int64_t ldo, int64_t m,
+                             int64_t n, int64_t k, int epilogue, cudaStream_t stream) {
+    PairParams p;
+    p.m = (int)m; p.n = (int)n; p.k = (int)k; p.epilogue = epilogue; p.ldo = ldo;
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.tiles_m = (int)((m + 2 * BM - 1) / (2 * BM));
+    p.tiles_n = epilogue == 1 ? (int)(n / 128) : (int)((n + BN - 1) / BN);
+    {
+        const int64_t panel = int64_t(2 * BM) * k * 2;
+        int64_t g = (40ll << 20) / (panel > 0 ? panel : 1);
+        p.group_m = (int)(g < 4 ? 4 : (g > 32 ? 32 : g));
+    }
+    p.status = bg_status_word();
+    if (!p.status) return BG_ERR_DRIVER;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) {
+            bg_set_error("bg_gemm_bf16: cudaFuncSetAttribute(pair): %s", cudaGetErrorString(e));
+            return BG_ERR_LAUNCH;
+        }
+        configured = true;
+    }
+    // Number of CTA pairs that can be resident at once (pairs must sit inside one GPC, so it can be
+    // fewer than SMs / 2); the persistent grid is sized to it so that every pair starts immediately.
+    static int max_pairs = 0;
+    if (!max_pairs) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * (bg_num_sms() / 2));
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = SMEM_BYTES;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_pair_kernel, &cfg) != cudaSuccess || n <= 0) {
+            cudaGetLastError();
+            n = bg_num_sms() / 2;
+        }
+        max_pairs = n < bg_num_sms() / 2 ? n : bg_num_sms() / 2;
+    }
+    const int tiles = p.tiles_m * p.tiles_n;
+    const int pairs = tiles < max_pairs ? tiles : max_pairs;
+    gemm_bf16_pair_kernel<<<2 * pairs, THREADS, SMEM_BYTES, stream>>>(map_a, map_w, p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        bg_set_error("bg_gemm_bf16: launch(pair): %s", cudaGetErrorString(e));
+        return BG_ERR_LAUNCH;
+    }
+    return BG_OK;
+}
