@@ -444,4 +444,64 @@ int bg_linear_fp8(const void* x, int64_t ldx, const void* wq, int64_t ldw, const
     return bg_gemm_fp8_block128(q, k, inv, wq, ldw, w_inv, out, ldo, m, n, k, epilogue, stream);
 }
 
+// ---------------------------------------------------------------------------- allocation-free variant
+//
+// Some callers are not in a position to hand over scratch memory: a plugin invoked by a host
+// runtime that has already reserved the device's memory for its own pools, a callback that runs
+// where calling into the allocator is forbidden or would stall the device, an integration that
+// simply has no allocator of its own.  For them the scratch of the FP8 linear lives inside the
+// library, in a fixed file-scope device array.  Every GPU that loads the library carries these
+// BG_FP8_STATIC_SCRATCH_BYTES until the process exits, so the limit is kept modest.
+//
+// The array's name is only a host-side handle: the kernels need its device address, which is
+// looked up once per device (with that device current) by cudaGetSymbolAddress on the first call
+// there.  Do that first call before starting any stream capture.
+//
+// All calls on a device share the one array and it keeps whatever the last call left in it.
+// Nothing in it has to start at zero (each call overwrites exactly the part it then reads), but
+// two calls whose kernels overlap on the GPU - different streams, no ordering between them -
+// would overwrite each other's quantised activations: order them on one stream or with events.
+constexpr int64_t kStaticScratchBytes = 9ll << 20;     // 8 Mi activation elements + their block scales
+constexpr int kMaxDevices = 64;
+static __device__ __align__(256) uint8_t g_fp8_static_scratch[kStaticScratchBytes];
+
+int64_t bg_linear_fp8_static_max_bytes(void) { return kStaticScratchBytes; }
+
+int bg_linear_fp8_static(const void* x, int64_t ldx, const void* wq, int64_t ldw, const float* w_inv, void* out,
+                         int64_t ldo, int64_t m, int64_t n, int64_t k, int epilogue, void* stream) {
+    if (m == 0) return BG_OK;
+    if (m < 0 || k <= 0 || k % 128) {
+        bg_set_error("bg_linear_fp8_static: k must be a positive multiple of 128 (got %lld)", (long long)k);
+        return BG_ERR_ALIGN;
+    }
+    const int64_t need = bg_linear_fp8_workspace_bytes(m, k);
+    if (need > kStaticScratchBytes) {
+        bg_set_error("bg_linear_fp8_static: an activation of %lld x %lld needs %lld bytes of scratch, the built-in "
+                     "buffer holds %lld; split the rows or use bg_linear_fp8 with a caller-owned workspace",
+                     (long long)m, (long long)k, (long long)need, (long long)kStaticScratchBytes);
+        return BG_ERR_WORKSPACE;
+    }
+    static void* device_address[kMaxDevices] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        bg_set_error("bg_linear_fp8_static: cannot identify the current device (%s)", cudaGetErrorString(e));
+        return BG_ERR_DRIVER;
+    }
+    if (device_address[dev] == nullptr) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_fp8_static_scratch);
+        if (e != cudaSuccess || ptr == nullptr) {
+            bg_set_error("bg_linear_fp8_static: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+            return BG_ERR_DRIVER;
+        }
+        device_address[dev] = ptr;
+    }
+    uint8_t* q = static_cast<uint8_t*>(device_address[dev]);
+    float* inv = reinterpret_cast<float*>(q + ((m * k + 255) / 256) * 256);
+    int rc = bg_quantize_e4m3_rows(x, ldx, q, k, inv, m, k, stream);
+    if (rc) return rc;
+    return bg_gemm_fp8_block128(q, k, inv, wq, ldw, w_inv, out, ldo, m, n, k, epilogue, stream);
+}
+
 }  // extern "C"

@@ -453,3 +453,19 @@ def gemm_fp8(aq, a_inv_t, weight: Fp8Weight, *, geglu=False):
     _lib.check(lib.bg_gemm_fp8_block128(_ptr(aq), k, _ptr(a_inv_t), _ptr(weight.q), k, _ptr(weight.inv_scale),
                                         _ptr(out), n, m, n, k, 1 if geglu else 0, _stream()), 'bg_gemm_fp8_block128')
     return out
+
+
+def linear_fp8_static(x, weight: Fp8Weight, *, geglu=False):
+    """linear_fp8 without any scratch allocation: the quantised activations live in a fixed
+    buffer inside the library (see bg_linear_fp8_static).  Raises B200Error when the activation
+    does not fit that buffer."""
+    lib = _lib.load()
+    flat, m, k, ldx = _rows(x, 'x')
+    rows, wk = weight.shape
+    if wk != k:
+        raise ValueError(f'weight has K={wk}, input has {k}')
+    n = rows // 2 if geglu else rows
+    out = torch.empty((m, n), device=x.device, dtype=BF16)
+    _lib.check(lib.bg_linear_fp8_static(_ptr(flat), ldx, _ptr(weight.q), k, _ptr(weight.inv_scale), _ptr(out), n, m, n,
+                                        k, 1 if geglu else 0, _stream()), 'bg_linear_fp8_static')
+    return out.view(*x.shape[:-1], n)

@@ -115,6 +115,18 @@ int bg_linear_fp8(const void* x, int64_t ldx, const void* wq, int64_t ldw, const
                   int64_t ldo, int64_t m, int64_t n, int64_t k, int epilogue, void* workspace,
                   int64_t workspace_bytes, void* stream);
 
+/* bg_linear_fp8 for callers that cannot supply scratch memory.  (No counterpart in the reference.)
+ * The quantised activations go to a fixed buffer inside the library instead of a caller-owned
+ * workspace, so the call allocates nothing; in exchange the activation is limited to
+ * bg_linear_fp8_static_max_bytes() of scratch (9 MiB: about 8 Mi elements, e.g. 3 276 rows of 2 560),
+ * larger ones are refused with BG_ERR_WORKSPACE.  Every GPU that loads the library holds the buffer
+ * until exit.  The first call on each device looks up the buffer's device address: make it before
+ * any stream capture.  All calls on a device share the buffer, so calls that may overlap on the GPU
+ * must be ordered by the caller.  Same arguments and results as bg_linear_fp8 otherwise. */
+int64_t bg_linear_fp8_static_max_bytes(void);
+int bg_linear_fp8_static(const void* x, int64_t ldx, const void* wq, int64_t ldw, const float* w_inv, void* out,
+                         int64_t ldo, int64_t m, int64_t n, int64_t k, int epilogue, void* stream);
+
 /* Packed variable-length attention, one softmax over [prefix keys | own keys].
  *   q [tq, q_heads, D] (token stride ldq, head stride hsq); k, v [tk, kv_heads, D] (strides ldkv,
  *   hskv); ck, cv [ts, kv_heads, D] (strides ldc, hsc) or NULL - any token/head strides that are
