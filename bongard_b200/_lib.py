@@ -31,6 +31,7 @@ SIGNATURES = {
     'bg_linear_fp8': ([P, I64, P, I64, P, P, I64, I64, I64, I64, INT, P, I64, P], INT),
     'bg_linear_fp8_static_max_bytes': ([], I64),
     'bg_linear_fp8_static': ([P, I64, P, I64, P, P, I64, I64, I64, I64, INT, P], INT),
+    'bg_attention_tile_rows': ([INT], INT),
     'bg_varlen_attention': ([P, I64, I64, P, P, I64, I64, P, P, I64, I64, P, P, P, I32, P, P, I64, I64, I64, INT, INT, INT,
                              F32, P], INT),
     'bg_judgment_head': ([P, I64, P, P, P, P, P, P, I64, I64, INT, P], INT),

@@ -17,21 +17,16 @@
 //                           its own question                       (bongard/flash_varlen.py:1-8, 61-77)
 // A tile whose rows belong to several questions of one owner streams the owner's state once.
 //
-// Operand placement.  The query tile lives in TENSOR MEMORY for the whole CTA: the softmax
-// threads load their rows from global memory once and store them with tcgen05.st, and
-// S = Q K^T is issued in the TS form (A from TMEM, B = K tile in shared memory).  An SS-form
-// M128 N128 K16 instruction reads 8 KB of shared memory per 64 clocks, which is the
-// shared-memory ceiling; taking Q out of shared memory halves that, and the 64 KB it frees
-// hold a second K slot so the next K tile streams in during the current contraction.
-// O += P V is SS form (P written back to shared memory as bf16, V as an MN-major operand).
-// TMEM columns: Q [0, D/2), S [128, 256), O [256, 256 + D).
-//
-// Roles: warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-9 = softmax: two threads per row
-// (one per 64-column half of the score tile, in different warps of the same TMEM lane quarter,
-// so every SM sub-partition has two softmax warps to interleave); the halves exchange their
-// row maxima through shared memory.  O is only rescaled when a row's running maximum grows by
-// more than 2^8 (lazy rescale).  Issue order on the tensor pipe is S(j+1), P.V(j): the single S
-// buffer is free again as soon as the softmax threads have copied S(j) to registers.
+// Roles: warp 0 = TMA producer, warp 1 = MMA issuer (S = Q K^T, O += P V), warps 2-5 = softmax
+// (thread = row).  S is double-buffered in TMEM (2 x 128 columns), O lives in TMEM (D columns).
+// The probabilities never leave tensor memory: a softmax thread overwrites the first 64 columns
+// of the S buffer it has just read with its row of P as packed bf16 (tcgen05.st), and O += P V is
+// issued in the TS form (A = P from TMEM, B = V tile in shared memory, MN-major).  Each iteration
+// of this kernel is a latency chain (S ready -> softmax -> P ready -> P.V), and keeping P out of
+// shared memory removes the stores, their bank conflicts and the generic-to-async proxy fence
+// from that chain.  S(j+1) reuses the buffer that held P(j-1); since
+// consecutive MMAs overlap in the tensor pipe, the issuer waits for P.V(j-1) to complete first.
+// O is only rescaled when a row's running maximum grows by more than 2^8 (lazy rescale).
 #include "common.cuh"
 
 namespace {
@@ -40,7 +35,7 @@ using namespace bg;
 
 constexpr int ROWS = 128;         // query rows per tile (tokens x GQA group)
 constexpr int KEYS = 128;         // keys per tile
-constexpr int THREADS = 320;
+constexpr int THREADS = 192;
 constexpr int SLAB = 16384;       // 128 rows x 128 B
 constexpr float LAZY_LOG2 = 8.f;  // rescale threshold in log2 units
 
@@ -48,8 +43,6 @@ struct AttnParams {
     const int32_t* tiles;    // [n_tiles][8]: q_start q_count own_lo own_hi lo_max hi_min prefix_start prefix_len
     const int32_t* row_lo;   // [Tq]
     const int32_t* row_hi;   // [Tq]
-    const __nv_bfloat16* q;  // [Tq, Hq, D] with token stride ldq and head stride hsq
-    int64_t ldq, hsq;
     __nv_bfloat16* out;      // [Tq, Hq * D]
     float* lse;              // [Hq, Tq] or null
     int64_t tq;
@@ -61,40 +54,32 @@ struct AttnParams {
 template <int D>
 struct Smem {
     static constexpr int SLABS = D / 64;
-    static constexpr int TILE = SLABS * SLAB;         // one K or V tile: 128 keys x D bf16
-    static constexpr int K = 0;                       // two K slots
-    static constexpr int V = K + 2 * TILE;
-    static constexpr int P = V + TILE;
-    static constexpr int BARS = P + 2 * SLAB;
-    static constexpr int XCH = BARS + 256;            // row-max / row-sum exchange: 2 x 2 x 128 floats
-    static constexpr int TOTAL = XCH + 2 * 2 * 128 * 4;   // 231 680 B for D = 256: no room for alignment slack
+    static constexpr int Q = 0;
+    static constexpr int K = Q + SLABS * SLAB;
+    static constexpr int V = K + SLABS * SLAB;
+    static constexpr int BARS = V + SLABS * SLAB;
+    static constexpr int TOTAL = BARS + 256 + 1024;
 };
 
 template <int D>
 __global__ void __launch_bounds__(THREADS, 1)
-varlen_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                        const __grid_constant__ CUtensorMap map_ck, const __grid_constant__ CUtensorMap map_cv,
-                        const AttnParams p) {
+varlen_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_ck,
+                        const __grid_constant__ CUtensorMap map_cv, const AttnParams p) {
     using L = Smem<D>;
     constexpr int SLABS = L::SLABS;
-    // The swizzled tiles need a 1024-byte aligned base.  The kernel has no static shared memory, so
-    // the dynamic window starts aligned; a misaligned base is reported instead of being padded for.
-    extern __shared__ __align__(1024) uint8_t smem[];
-    if (smem_u32(smem) & 1023) {
-        if (threadIdx.x == 0) atomicCAS(p.status, 0, 299);
-        return;
-    }
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BARS);
-    uint64_t* q_ready = bars + 0;   // 256 arrivals: the query tile is in TMEM
-    uint64_t* k_full = bars + 1;    // [2]
-    uint64_t* k_empty = bars + 3;   // [2]
-    uint64_t* v_full = bars + 5;
-    uint64_t* v_empty = bars + 6;
-    uint64_t* s_full = bars + 7;
-    uint64_t* s_empty = bars + 8;   // 8 arrivals (one per softmax warp): S has been copied to registers
-    uint64_t* p_full = bars + 9;    // 256 arrivals
-    uint64_t* pv_done = bars + 10;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+    uint64_t* q_full = bars + 0;
+    uint64_t* k_full = bars + 1;
+    uint64_t* k_empty = bars + 2;
+    uint64_t* v_full = bars + 3;
+    uint64_t* v_empty = bars + 4;
+    uint64_t* s_full = bars + 5;    // [2]
+    uint64_t* p_full = bars + 7;    // 4 warp arrivals: P(j) is in tensor memory
+    uint64_t* pv_done = bars + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -112,18 +97,16 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
-        mbar_init(q_ready, 256);
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(&k_full[i], 1);
-            mbar_init(&k_empty[i], 1);
-        }
+        mbar_init(q_full, 1);
+        mbar_init(k_full, 1);
+        mbar_init(k_empty, 1);
         mbar_init(v_full, 1);
         mbar_init(v_empty, 1);
-        mbar_init(s_full, 1);
-        mbar_init(s_empty, 8);
-        mbar_init(p_full, 256);
+        for (int b = 0; b < 2; ++b) mbar_init(&s_full[b], 1);
+        mbar_init(p_full, 4);
         mbar_init(pv_done, 1);
         mbar_fence_init();
+        tma_prefetch_desc(&map_q);
         tma_prefetch_desc(&map_k);
         tma_prefetch_desc(&map_v);
     }
@@ -135,33 +118,36 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_q = tmem_base, tmem_s = tmem_base + 128, tmem_o = tmem_base + 256;
+    const uint32_t tmem_o = tmem_base + 256;
 
     if (n_tiles > 0) {
         if (warp == 0) {
             // ------------------------------------------------------------ TMA producer
             if (lane == 0) {
-                auto key_start = [&](int j) { return j < n_pre ? pre_start + j * KEYS : own_lo + (j - n_pre) * KEYS; };
+                mbar_expect_tx(q_full, SLABS * SLAB);
+                for (int s = 0; s < SLABS; ++s)
+                    tma_load_3d(smem + L::Q + s * SLAB, &map_q, q_full, s * 64, kvh * G, q_start);
                 auto load_k = [&](int j) {
-                    const int slot = j & 1;
-                    if (!mbar_wait(&k_empty[slot], ((j >> 1) & 1) ^ 1, ab, 201)) return;
-                    mbar_expect_tx(&k_full[slot], L::TILE);
+                    if (!mbar_wait(k_empty, (j & 1) ^ 1, ab, 201)) return;
+                    const bool pre = j < n_pre;
+                    const int key0 = pre ? pre_start + j * KEYS : own_lo + (j - n_pre) * KEYS;
+                    mbar_expect_tx(k_full, SLABS * SLAB);
                     for (int s = 0; s < SLABS; ++s)
-                        tma_load_3d(smem + L::K + slot * L::TILE + s * SLAB, j < n_pre ? &map_ck : &map_k,
-                                    &k_full[slot], s * 64, kvh, key_start(j));
+                        tma_load_3d(smem + L::K + s * SLAB, pre ? &map_ck : &map_k, k_full, s * 64, kvh, key0);
                 };
                 auto load_v = [&](int j) {
                     if (!mbar_wait(v_empty, (j & 1) ^ 1, ab, 202)) return;
-                    mbar_expect_tx(v_full, L::TILE);
+                    const bool pre = j < n_pre;
+                    const int key0 = pre ? pre_start + j * KEYS : own_lo + (j - n_pre) * KEYS;
+                    mbar_expect_tx(v_full, SLABS * SLAB);
                     for (int s = 0; s < SLABS; ++s)
-                        tma_load_3d(smem + L::V + s * SLAB, j < n_pre ? &map_cv : &map_v, v_full, s * 64, kvh,
-                                    key_start(j));
+                        tma_load_3d(smem + L::V + s * SLAB, pre ? &map_cv : &map_v, v_full, s * 64, kvh, key0);
                 };
-                // Issue order = the order in which slots drain on the tensor pipe
-                // (S(0), S(1), P.V(0), S(2), P.V(1), ...): K(j+1) frees with S(j-1), V(j) with P.V(j-1).
+                // Issue order follows the order in which the slots drain: S(j) completes before
+                // P.V(j-1), so K(j+1) is requested before V(j).
                 load_k(0);
-                if (n_tiles > 1) load_k(1);
                 load_v(0);
+                if (n_tiles > 1) load_k(1);
                 for (int j = 1; j < n_tiles; ++j) {
                     if (j + 1 < n_tiles) load_k(j + 1);
                     load_v(j);
@@ -172,22 +158,27 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             if (lane == 0) {
                 constexpr uint32_t idesc_s = instr_desc(ROWS, KEYS, 1, 1, 0, 0);
                 constexpr uint32_t idesc_o = instr_desc(ROWS, D, 1, 1, 0, 1);   // V is MN-major
-                const uint32_t sk = smem_u32(smem + L::K), sv = smem_u32(smem + L::V), sp = smem_u32(smem + L::P);
+                const uint32_t sq = smem_u32(smem + L::Q), sk = smem_u32(smem + L::K);
+                const uint32_t sv = smem_u32(smem + L::V);
                 auto issue_s = [&](int j) {
-                    const int slot = j & 1;
-                    if (!mbar_wait(&k_full[slot], (j >> 1) & 1, ab, 203)) return;
-                    if (!mbar_wait(s_empty, (j & 1) ^ 1, ab, 204)) return;
+                    const int b = j & 1;
+                    if (!mbar_wait(k_full, j & 1, ab, 203)) return;
+                    // Buffer b still holds P(j-2) as the A operand of P.V(j-2).  Consecutive MMAs overlap in
+                    // the tensor pipe, so issue order alone does not protect it: wait for that P.V to finish.
+                    if (j >= 2 && !mbar_wait(pv_done, j & 1, ab, 204)) return;
                     tc_fence_after();
 #pragma unroll
-                    for (int kk = 0; kk < D / 16; ++kk) {      // 16 bf16 of K per instruction = 8 TMEM columns of Q
-                        uint64_t db = smem_desc_sw128(sk + slot * L::TILE + (kk >> 2) * SLAB + (kk & 3) * 32, 16, 1024);
-                        mma_bf16_ts(tmem_s, tmem_q + kk * 8, db, idesc_s, kk != 0);
-                    }
-                    mma_commit(s_full);
-                    mma_commit(&k_empty[slot]);
+                    for (int s = 0; s < SLABS; ++s)
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {
+                            uint64_t da = smem_desc_sw128(sq + s * SLAB + kk * 32, 16, 1024);
+                            uint64_t db = smem_desc_sw128(sk + s * SLAB + kk * 32, 16, 1024);
+                            mma_bf16_ss(tmem_base + b * KEYS, da, db, idesc_s, (s | kk) != 0);
+                        }
+                    mma_commit(&s_full[b]);
+                    mma_commit(k_empty);
                 };
-                if (mbar_wait(q_ready, 0, ab, 205)) {
-                    tc_fence_after();
+                if (mbar_wait(q_full, 0, ab, 205)) {
                     issue_s(0);
                     for (int j = 0; j < n_tiles; ++j) {
                         if (j + 1 < n_tiles) issue_s(j + 1);
@@ -196,9 +187,8 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         tc_fence_after();
 #pragma unroll
                         for (int kk = 0; kk < KEYS / 16; ++kk) {
-                            uint64_t da = smem_desc_sw128(sp + (kk >> 2) * SLAB + (kk & 3) * 32, 16, 1024);
                             uint64_t db = smem_desc_sw128(sv + kk * 2048, SLAB, 1024);
-                            mma_bf16_ss(tmem_o, da, db, idesc_o, (j | kk) != 0);
+                            mma_bf16_ts(tmem_o, tmem_base + (j & 1) * KEYS + kk * 8, db, idesc_o, (j | kk) != 0);
                         }
                         mma_commit(pv_done);
                         mma_commit(v_empty);
@@ -206,9 +196,8 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 }
             }
         } else {
-            // ------------------------------------------------------------ softmax + epilogue (warps 2..9)
-            const int part = warp & 3;                 // TMEM lane quarter of this warp
-            const int half = (warp - 2) >> 2;          // which 64 score columns of the 128-key tile
+            // ------------------------------------------------------------ softmax + epilogue (warps 2..5)
+            const int part = warp & 3;
             const int row = part * 32 + lane;
             const int tok_local = row / G;
             const int head = kvh * G + row % G;
@@ -220,75 +209,33 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             const float c = p.scale_log2;
             const float lazy = LAZY_LOG2 / c;
             float m_ref = -INFINITY, l = 0.f;
-            uint8_t* prow = smem + L::P + half * SLAB + row * 128;
-            const int sw = row & 7;
-            float* xch = reinterpret_cast<float*>(smem + L::XCH);     // [2][2][128]
-            constexpr int HK = KEYS / 2;               // score columns per thread
-            constexpr int OC = D / 2;                  // accumulator columns per thread
-
-            // Query rows -> tensor memory, packed bf16 pairs: column w of lane r holds q[r][2w], q[r][2w+1].
-            {
-                constexpr int QW = (D == 64) ? 32 : D / 4;      // 32-bit words this thread stores
-                const bool writer = (D != 64) || half == 0;     // warp-uniform
-                if (writer) {
-                    const int word0 = (D == 64) ? 0 : half * QW;
-                    const __nv_bfloat16* src = p.q + token * p.ldq + int64_t(head) * p.hsq + word0 * 2;
-#pragma unroll
-                    for (int w0 = 0; w0 < QW; w0 += 32) {
-                        uint32_t w[32];
-#pragma unroll
-                        for (int v4 = 0; v4 < 8; ++v4) {
-                            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                            if (row_valid) v = *reinterpret_cast<const uint4*>(src + (w0 + v4 * 4) * 2);
-                            w[v4 * 4 + 0] = v.x;
-                            w[v4 * 4 + 1] = v.y;
-                            w[v4 * 4 + 2] = v.z;
-                            w[v4 * 4 + 3] = v.w;
-                        }
-                        tmem_st32(tmem_q + lane_addr + word0 + w0, w);
-                    }
-                    tmem_wait_st();
-                }
-                tc_fence_before();
-                mbar_arrive(q_ready);
-            }
 
             for (int j = 0; j < n_tiles; ++j) {
-                // After an abort every wait returns at once; the loop keeps its shape so that the two
-                // warps of a row still meet at their named barrier.
-                mbar_wait(s_full, j & 1, ab, 208);
+                const int b = j & 1;
+                if (!mbar_wait(&s_full[b], (j >> 1) & 1, ab, 208)) break;
                 tc_fence_after();
-                float s[HK];
+                float s[KEYS];
 #pragma unroll
-                for (int cc = 0; cc < HK; cc += 32)
-                    tmem_ld32(tmem_s + lane_addr + half * HK + cc, reinterpret_cast<uint32_t*>(s + cc));
+                for (int cc = 0; cc < KEYS; cc += 32)
+                    tmem_ld32(tmem_base + lane_addr + b * KEYS + cc, reinterpret_cast<uint32_t*>(s + cc));
                 tmem_wait_ld();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(s_empty);
 
                 const bool pre = j < n_pre;
-                const int key0 = (pre ? pre_start + j * KEYS : own_lo + (j - n_pre) * KEYS);
+                const int key0 = pre ? pre_start + j * KEYS : own_lo + (j - n_pre) * KEYS;
                 const int lo = pre ? pre_start : rlo;
                 const int hi = pre ? (row_valid ? pre_start + pre_len : pre_start) : rhi;
                 const bool need_mask = pre ? (key0 + KEYS > pre_start + pre_len) || !row_valid
                                            : !(key0 >= lo_max && key0 + KEYS <= hi_min) || !row_valid;
                 if (need_mask) {
 #pragma unroll
-                    for (int i = 0; i < HK; ++i) {
-                        const int key = key0 + half * HK + i;
+                    for (int i = 0; i < KEYS; ++i) {
+                        const int key = key0 + i;
                         if (key < lo || key >= hi) s[i] = -INFINITY;
                     }
                 }
                 float mx = s[0];
 #pragma unroll
-                for (int i = 1; i < HK; ++i) mx = fmaxf(mx, s[i]);
-                // row maximum over both halves (double-buffered slot: no second barrier needed)
-                float* slot = xch + (j & 1) * 256;
-                slot[half * 128 + row] = mx;
-                named_barrier(1 + part, 64);
-                mx = fmaxf(mx, slot[(half ^ 1) * 128 + row]);
-
+                for (int i = 1; i < KEYS; ++i) mx = fmaxf(mx, s[i]);
                 const bool grow = mx > m_ref + lazy;   // false while both are -inf
                 float alpha = 1.f;
                 if (grow) {
@@ -299,56 +246,54 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 const float shift = (m_ref == -INFINITY) ? 0.f : m_ref * c;
                 float sum = 0.f;
 #pragma unroll
-                for (int i = 0; i < HK; ++i) {
+                for (int i = 0; i < KEYS; ++i) {
                     s[i] = fast_exp2(fmaf(s[i], c, -shift));
                     sum += s[i];
                 }
                 l += sum;
 
-                // P(j-1) has been consumed and O is stable once P.V(j-1) has completed.
+                // P(j) may only be stored once P.V(j-1) has completed: a tcgen05.st into tensor memory while a
+                // TS-form MMA is still reading its A operand from tensor memory corrupted results on B200, even
+                // though the two touch different columns.  The same wait makes O stable for a rescale.
                 if (j > 0) {
                     mbar_wait(pv_done, (j - 1) & 1, ab, 209);
                     tc_fence_after();
                     if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll 1
-                        for (int cc = 0; cc < OC; cc += 32) {
+                        for (int cc = 0; cc < D; cc += 32) {
                             uint32_t o[32];
-                            tmem_ld32(tmem_o + lane_addr + half * OC + cc, o);
+                            tmem_ld32(tmem_o + lane_addr + cc, o);
                             tmem_wait_ld();
 #pragma unroll
                             for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                            tmem_st32(tmem_o + lane_addr + half * OC + cc, o);
+                            tmem_st32(tmem_o + lane_addr + cc, o);
                         }
                         tmem_wait_st();
                     }
                 }
+                // P(j) as packed bf16 over the first 64 columns of the S buffer this thread has just read.
 #pragma unroll
-                for (int ch = 0; ch < HK / 8; ++ch) {
-                    uint4 v;
-                    v.x = pack_bf16(s[ch * 8 + 0], s[ch * 8 + 1]);
-                    v.y = pack_bf16(s[ch * 8 + 2], s[ch * 8 + 3]);
-                    v.z = pack_bf16(s[ch * 8 + 4], s[ch * 8 + 5]);
-                    v.w = pack_bf16(s[ch * 8 + 6], s[ch * 8 + 7]);
-                    *reinterpret_cast<uint4*>(prow + ((ch ^ sw) << 4)) = v;
+                for (int cc = 0; cc < KEYS / 2; cc += 32) {
+                    uint32_t w[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) w[i] = pack_bf16(s[2 * (cc + i)], s[2 * (cc + i) + 1]);
+                    tmem_st32(tmem_base + lane_addr + b * KEYS + cc, w);
                 }
-                fence_async_proxy();
+                tmem_wait_st();
                 tc_fence_before();
-                mbar_arrive(p_full);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(p_full);
             }
 
-            // epilogue: O / l -> bf16 (each thread stores half of its row's head_dim)
-            float* lslot = xch + (n_tiles & 1) * 256;   // the slot last used two tiles ago
-            lslot[half * 128 + row] = l;
-            named_barrier(1 + part, 64);
-            l += lslot[(half ^ 1) * 128 + row];
+            // epilogue: O / l -> bf16
             if (mbar_wait(pv_done, (n_tiles - 1) & 1, ab, 210)) {
                 tc_fence_after();
                 const float inv = l > 0.f ? 1.f / l : 0.f;
-                __nv_bfloat16* dst = p.out + (token * p.q_heads + head) * D + half * OC;
+                __nv_bfloat16* dst = p.out + (token * p.q_heads + head) * D;
 #pragma unroll 1
-                for (int cc = 0; cc < OC; cc += 32) {
+                for (int cc = 0; cc < D; cc += 32) {
                     uint32_t o[32];
-                    tmem_ld32(tmem_o + lane_addr + half * OC + cc, o);
+                    tmem_ld32(tmem_o + lane_addr + cc, o);
                     tmem_wait_ld();
                     if (row_valid) {
 #pragma unroll
@@ -362,7 +307,7 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         }
                     }
                 }
-                if (p.lse != nullptr && row_valid && half == 0) {
+                if (p.lse != nullptr && row_valid) {
                     const float ln2 = 0.6931471805599453f;
                     p.lse[int64_t(head) * p.tq + token] =
                         l > 0.f ? (m_ref * c + log2f(l)) * ln2 : -INFINITY;
@@ -386,8 +331,8 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 }
 
 template <int D>
-int launch(const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mck, const CUtensorMap& mcv,
-           const AttnParams& p, int n_tiles, cudaStream_t stream) {
+int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mck,
+           const CUtensorMap& mcv, const AttnParams& p, int n_tiles, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(varlen_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -399,7 +344,7 @@ int launch(const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mck,
         configured = true;
     }
     dim3 grid((unsigned)n_tiles, (unsigned)p.kv_heads);
-    varlen_attention_kernel<D><<<grid, THREADS, Smem<D>::TOTAL, stream>>>(mk, mv, mck, mcv, p);
+    varlen_attention_kernel<D><<<grid, THREADS, Smem<D>::TOTAL, stream>>>(mq, mk, mv, mck, mcv, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         bg_set_error("bg_varlen_attention: launch: %s", cudaGetErrorString(e));
@@ -417,6 +362,10 @@ int kv_map(CUtensorMap* map, const void* base, int64_t tokens, int heads, int d,
 }
 
 }  // namespace
+
+// Query rows one tile of bg_varlen_attention covers (128 for every supported head size).
+// A tile record may hold up to this many rows / (q_heads / kv_heads) consecutive tokens.
+extern "C" int bg_attention_tile_rows(int head_dim) { (void)head_dim; return 128; }
 
 extern "C" int bg_varlen_attention(const void* q, int64_t ldq, int64_t hsq, const void* k, const void* v,
                                    int64_t ldkv, int64_t hskv, const void* ck, const void* cv, int64_t ldc,
@@ -442,7 +391,15 @@ extern "C" int bg_varlen_attention(const void* q, int64_t ldq, int64_t hsq, cons
     }
     if (n_tiles == 0 || tq == 0) return BG_OK;
 
-    CUtensorMap mk, mv, mck, mcv;
+    CUtensorMap mq, mk, mv, mck, mcv;
+    {
+        uint64_t dims[3] = {(uint64_t)head_dim, (uint64_t)q_heads, (uint64_t)tq};
+        uint64_t strides[2] = {(uint64_t)hsq * 2, (uint64_t)ldq * 2};
+        uint32_t box[3] = {64, (uint32_t)g, (uint32_t)(ROWS / g)};
+        int rc = bg_make_tensor_map(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, q, dims, strides, box,
+                                    CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
+    }
     int rc = kv_map(&mk, k, tk, kv_heads, head_dim, ldkv, hskv);
     if (!rc) rc = kv_map(&mv, v, tk, kv_heads, head_dim, ldkv, hskv);
     if (!rc && ck) rc = kv_map(&mck, ck, ts, kv_heads, head_dim, ldc, hsc);
@@ -452,12 +409,12 @@ extern "C" int bg_varlen_attention(const void* q, int64_t ldq, int64_t hsq, cons
 
     AttnParams p;
     p.tiles = tiles; p.row_lo = row_lo; p.row_hi = row_hi;
-    p.q = static_cast<const __nv_bfloat16*>(q); p.ldq = ldq; p.hsq = hsq;
     p.out = static_cast<__nv_bfloat16*>(out); p.lse = lse; p.tq = tq;
     p.q_heads = q_heads; p.kv_heads = kv_heads;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = bg_status_word();
     if (!p.status) return BG_ERR_DRIVER;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    return head_dim == 64 ? launch<64>(mk, mv, mck, mcv, p, n_tiles, s) : launch<256>(mk, mv, mck, mcv, p, n_tiles, s);
+    return head_dim == 64 ? launch<64>(mq, mk, mv, mck, mcv, p, n_tiles, s)
+                          : launch<256>(mq, mk, mv, mck, mcv, p, n_tiles, s);
 }

@@ -109,7 +109,8 @@ class JudgmentEngine:
         keys = [self._window_key(i, longest, decoder) for i in range(s.layers)]
         plans, parts, cursor = {}, [positions], total
         for key in dict.fromkeys(keys):
-            hp = ops.make_host_plan(lengths, key, group=s.q_heads // s.kv_heads, owners=owners, state_lengths=state_lengths)
+            hp = ops.make_host_plan(lengths, key, group=s.q_heads // s.kv_heads, owners=owners, state_lengths=state_lengths,
+                                    head_dim=s.head_dim)
             plans[key] = (cursor, hp)
             parts.append(hp.packed)
             cursor += hp.packed.size

@@ -19,15 +19,15 @@ import torch
 from . import ops
 
 
-def _plan_from_cu(cu_q, window, group, device, *, decoder=False, cu_k=None):
+def _plan_from_cu(cu_q, window, group, device, *, decoder=False, cu_k=None, head_dim=None):
     """Attention plan from cu_seqlens tensors (synchronises: the custom-op surface carries no host lengths)."""
     lengths = (cu_q[1:] - cu_q[:-1]).tolist()
     if not decoder:
-        return ops.make_plan(lengths, window, device, group=group)
+        return ops.make_plan(lengths, window, device, group=group, head_dim=head_dim)
     key_lengths = (cu_k[1:] - cu_k[:-1]).tolist()
     state_lengths = [k - n for k, n in zip(key_lengths, lengths)]
     return ops.make_plan(lengths, window, device, group=group, owners=list(range(len(lengths))),
-                         state_lengths=state_lengths)
+                         state_lengths=state_lengths, head_dim=head_dim)
 
 
 def flash_packed_forward(q, k, v, cuq, cuk, scale, causal):
@@ -35,7 +35,7 @@ def flash_packed_forward(q, k, v, cuq, cuk, scale, causal):
     q [T,Hq,D], k/v [T,Hkv,D], non-causal attention inside each cu_seqlens segment."""
     if causal:
         raise ValueError('causal packed attention goes through flash_prefix_forward (state-prefix keys)')
-    plan = _plan_from_cu(cuq, None, q.shape[1] // k.shape[1], q.device)
+    plan = _plan_from_cu(cuq, None, q.shape[1] // k.shape[1], q.device, head_dim=q.shape[-1])
     out, lse = ops.varlen_attention(q, k, v, plan, scale, return_lse=True)
     return out.view(q.shape), lse
 
@@ -46,7 +46,7 @@ def flash_prefix_forward(q, k, v, ck, cv, indices, cuq, cuk, scale):
     the reference needs) is accepted and ignored; state segments are taken in question order,
     i.e. ck/cv hold one state per question back to back, or the caller uses `attention` below
     with a layout that knows the owners."""
-    plan = _plan_from_cu(cuq, None, q.shape[1] // k.shape[1], q.device, decoder=True, cu_k=cuk)
+    plan = _plan_from_cu(cuq, None, q.shape[1] // k.shape[1], q.device, decoder=True, cu_k=cuk, head_dim=q.shape[-1])
     out, lse = ops.varlen_attention(q, k, v, plan, scale, (ck, cv), return_lse=True)
     return out.view(q.shape), lse
 
@@ -91,6 +91,6 @@ def attention(q, k, v, layout, scale, window, cross=None):
         if ck.stride() != cv.stride():
             ck, cv = cross[0][0].contiguous().transpose(0, 1), cross[1][0].contiguous().transpose(0, 1)
         cr = (ck, cv)
-    plan = layout.plan(window, q3.shape[1] // k3.shape[1])
+    plan = layout.plan(window, q3.shape[1] // k3.shape[1], q3.shape[-1])
     out = ops.varlen_attention(q3, k3, v3, plan, scale, cr)
     return out.view(q3.shape[0], q3.shape[1], q3.shape[2]).transpose(0, 1)[None]

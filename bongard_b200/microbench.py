@@ -63,7 +63,7 @@ def attention(args, flush):
     gain = torch.zeros(d, device=DEV, dtype=torch.bfloat16)
     positions = torch.cat([torch.arange(n, dtype=torch.int32) for n in lengths]).to(DEV)
     ops.qk_norm_rope_(q, k, gain, gain, positions, ops.inv_freq(d, theta, DEV))
-    plan = ops.make_plan(lengths, window, DEV, group=hq // hkv)
+    plan = ops.make_plan(lengths, window, DEV, group=hq // hkv, head_dim=d)
     ms = timed(lambda: ops.varlen_attention(q, k, v, plan, d ** -0.5), args.iters, args.warmup, flush)
     flops = 4 * d * hq * plan.pairs
     return dict(op=f'varlen_attention_{args.variant}', tokens=t, sequences=len(lengths), tiles=plan.n_tiles,

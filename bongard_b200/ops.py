@@ -211,6 +211,7 @@ class AttentionPlan:
     tokens: int
     n_tiles: int
     pairs: int               # visible (query, key) pairs, for FLOP accounting
+    tile_rows: int = 128     # query rows (tokens x GQA group) a tile may hold
 
 
 def plan_rows(lengths, window, *, decoder):
@@ -245,6 +246,7 @@ class HostPlan:
     tokens: int
     n_tiles: int
     pairs: int
+    tile_rows: int = 128
 
     def to(self, device):
         dev = torch.from_numpy(self.packed).to(device, non_blocking=True)
@@ -252,10 +254,16 @@ class HostPlan:
 
     def view(self, dev):
         n8, t = self.n_tiles * 8, self.tokens
-        return AttentionPlan(dev[:n8].view(-1, 8), dev[n8:n8 + t], dev[n8 + t:n8 + 2 * t], t, self.n_tiles, self.pairs)
+        return AttentionPlan(dev[:n8].view(-1, 8), dev[n8:n8 + t], dev[n8 + t:n8 + 2 * t], t, self.n_tiles, self.pairs,
+                             self.tile_rows)
 
 
-def make_host_plan(lengths, window, *, group, owners=None, state_lengths=None):
+def tile_rows(head_dim):
+    """Query rows per attention tile for a head size: 256 at head_dim 256 (CTA pairs), else 128."""
+    return _lib.load().bg_attention_tile_rows(int(head_dim)) if head_dim else 128
+
+
+def make_host_plan(lengths, window, *, group, owners=None, state_lengths=None, head_dim=None):
     """Tile a pack of segments for the attention kernel (host arithmetic on lengths only).
 
     Encoder (owners None): tiles never cross a segment.  Decoder: consecutive questions of the
@@ -265,7 +273,8 @@ def make_host_plan(lengths, window, *, group, owners=None, state_lengths=None):
     decoder = owners is not None
     lo, hi = plan_rows(lengths, window, decoder=decoder)
     total = len(lo)
-    tq = 128 // group
+    rows = tile_rows(head_dim)
+    tq = rows // group
     runs = []      # [start, end, prefix_start, prefix_len, owner]
     offset = 0
     if decoder:
@@ -282,7 +291,7 @@ def make_host_plan(lengths, window, *, group, owners=None, state_lengths=None):
             offset += n
     runs = [r for r in runs if r[1] > r[0]]
     if not runs:
-        return HostPlan(np.zeros(0, dtype=np.int32), 0, 0, 0)
+        return HostPlan(np.zeros(0, dtype=np.int32), 0, 0, 0, rows)
     run = np.asarray([r[:4] for r in runs], dtype=np.int64)
     counts = (run[:, 1] - run[:, 0] + tq - 1) // tq
     which = np.repeat(np.arange(len(runs)), counts)
@@ -300,11 +309,12 @@ def make_host_plan(lengths, window, *, group, owners=None, state_lengths=None):
     pairs = int((hi - lo).sum())
     if decoder:
         pairs += int(sum(n * state_lengths[o] for n, o in zip(lengths, owners)))
-    return HostPlan(packed, total, tiles.shape[0], pairs)
+    return HostPlan(packed, total, tiles.shape[0], pairs, rows)
 
 
-def make_plan(lengths, window, device, *, group, owners=None, state_lengths=None):
-    return make_host_plan(lengths, window, group=group, owners=owners, state_lengths=state_lengths).to(device)
+def make_plan(lengths, window, device, *, group, owners=None, state_lengths=None, head_dim=None):
+    return make_host_plan(lengths, window, group=group, owners=owners, state_lengths=state_lengths,
+                          head_dim=head_dim).to(device)
 
 
 def varlen_attention(q, k, v, plan, scale, cross=None, return_lse=False):
@@ -321,6 +331,8 @@ def varlen_attention(q, k, v, plan, scale, cross=None, return_lse=False):
     tk, hkv = k.shape[0], k.shape[1]
     if plan.tokens != tq:
         raise ValueError(f'plan was built for {plan.tokens} tokens, q has {tq}')
+    if plan.tile_rows > lib.bg_attention_tile_rows(d):
+        raise ValueError(f'plan has {plan.tile_rows}-row tiles; head_dim {d} takes {lib.bg_attention_tile_rows(d)}')
     ck = cv = None
     ts = ldc = hsc = 0
     if cross is not None:

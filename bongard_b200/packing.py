@@ -50,11 +50,11 @@ class PackedLayout:
         reach = window if self.decoder else (window + 1) // 2
         return None if max(self.lengths) <= reach else window
 
-    def plan(self, window, group):
-        key = (self.effective_window(window), group)
+    def plan(self, window, group, head_dim=None):
+        key = (self.effective_window(window), group, head_dim)
         if key not in self.plans:
             self.plans[key] = ops.make_plan(self.lengths, key[0], self.positions.device, group=group,
-                                            owners=self.owners, state_lengths=self.state_lengths)
+                                            owners=self.owners, state_lengths=self.state_lengths, head_dim=head_dim)
         return self.plans[key]
 
 
@@ -102,7 +102,7 @@ def encoder_attention(module, hidden_states, position_embeddings, layout):
     """bongard/packing.py:201-210: projections, QK-norm + RoPE, packed attention, o_proj."""
     q, k, v = _project(module, hidden_states, layout.positions32, position_embeddings)
     group = q.shape[1] // k.shape[1]
-    out = ops.varlen_attention(q, k, v, layout.plan(module.sliding_window, group), module.scaling)
+    out = ops.varlen_attention(q, k, v, layout.plan(module.sliding_window, group, q.shape[-1]), module.scaling)
     from .attention import project_out
 
     return project_out(module, out, hidden_states.shape), None
@@ -118,5 +118,5 @@ def decoder_attention(module, hidden_states, position_embeddings, cache, layout,
         packed_cross = (cross.keys, cross.values)
     ck, cv = as_token_major(packed_cross[0]), as_token_major(packed_cross[1])
     group = q.shape[1] // k.shape[1]
-    out = ops.varlen_attention(q, k, v, layout.plan(module.sliding_window, group), module.scaling, (ck, cv))
+    out = ops.varlen_attention(q, k, v, layout.plan(module.sliding_window, group, q.shape[-1]), module.scaling, (ck, cv))
     return project_out(module, out, hidden_states.shape), None, None

@@ -134,13 +134,15 @@ int bg_linear_fp8_static(const void* x, int64_t ldx, const void* wq, int64_t ldw
  *   out [tq, q_heads * D] contiguous;
  *   lse fp32 [q_heads, tq] (natural log) or NULL.
  *   tiles int32 [n_tiles, 8] = {q_start, q_count, own_lo, own_hi, lo_max, hi_min, prefix_start,
- *   prefix_len}: q_count <= 128 / (q_heads / kv_heads) consecutive query tokens; [own_lo, own_hi)
+ *   prefix_len}: q_count <= bg_attention_tile_rows(head_dim) / (q_heads / kv_heads) consecutive
+ *   query tokens; [own_lo, own_hi)
  *   covers every row's own-key range, [lo_max, hi_min) is the part visible to all rows; the
  *   prefix keys are visible to every row.  row_lo / row_hi int32 [tq]: own-key range per token.
  * Replaces bongard/flash_varlen.py:129-139 attention, 13-22 _forward (op bongard::flash_packed_forward),
  * 61-77 _prefix (op bongard::flash_prefix_forward, without materialising the gathered keys), the
  * windowed layers bongard/packing.py:154-175 packed_attention serves, and the two-partition
  * serving path bongard/attention.py:122-169. */
+int bg_attention_tile_rows(int head_dim);
 int bg_varlen_attention(const void* q, int64_t ldq, int64_t hsq, const void* k, const void* v, int64_t ldkv,
                         int64_t hskv, const void* ck, const void* cv, int64_t ldc, int64_t hsc, void* out,
                         float* lse, const int32_t* tiles,

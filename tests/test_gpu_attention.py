@@ -37,7 +37,8 @@ def device():
 
 def run(q, k, v, lengths, scale, window, cross=None, owners=None, state_lengths=None, lse=False):
     hq, hkv = q.shape[1], k.shape[1]
-    plan = ops.make_plan(lengths, window, DEV, group=hq // hkv, owners=owners, state_lengths=state_lengths)
+    plan = ops.make_plan(lengths, window, DEV, group=hq // hkv, owners=owners, state_lengths=state_lengths,
+                         head_dim=q.shape[-1])
     cr = None if cross is None else (cross[0].to(DEV), cross[1].to(DEV))
     out = ops.varlen_attention(q.to(DEV), k.to(DEV), v.to(DEV), plan, scale, cr, return_lse=lse)
     if lse:
@@ -105,7 +106,7 @@ def test_strided_qkv_views():
     q = qkv[:, :hq * d].view(t, hq, d)
     k = qkv[:, hq * d:(hq + hkv) * d].view(t, hkv, d)
     v = qkv[:, (hq + hkv) * d:].view(t, hkv, d)
-    plan = ops.make_plan(lengths, None, DEV, group=2)
+    plan = ops.make_plan(lengths, None, DEV, group=2, head_dim=d)
     out = ops.varlen_attention(q, k, v, plan, 1 / 16).view(t, hq, d)
     want, _ = om.varlen_attention(q.float().cpu(), k.float().cpu(), v.float().cpu(), lengths, 1 / 16, None)
     assert_close(out, want)
@@ -121,6 +122,15 @@ def test_large_scores_need_the_running_maximum():
     out = run(q, k, v, lengths, 1.0, None)
     want, _ = om.varlen_attention(q.float(), k.float(), v.float(), lengths, 1.0, None)
     assert_close(out, want)
+
+
+def test_plan_tile_size_is_checked():
+    lengths = [150, 70]
+    t = sum(lengths)
+    plan = ops.make_plan(lengths, None, DEV, group=2, head_dim=64)
+    plan.tile_rows = 512          # a plan built for a larger tile than the kernel computes
+    with pytest.raises(ValueError):
+        ops.varlen_attention(rnd(t, 4, 64).to(DEV), rnd(t, 2, 64).to(DEV), rnd(t, 2, 64).to(DEV), plan, 0.125)
 
 
 def test_rejects_unsupported_shapes():
