@@ -35,7 +35,7 @@ from bongard_b200 import workload as wl  # noqa: E402
 METRIC = 'judged_questions_per_second'
 UNIT = 'questions/s'
 # DRAM bytes per algorithmic FLOP of the GEMM, from the ncu capture of the 8192-token MLP GEMMs (scaled to a launch by its FLOPs)
-GEMM_TRAFFIC_PER_FLOP = 9.14e-4   # (607.4 + 570.1) MB over (0.859 + 0.429) TFLOP, profiles/gemm_bf16_mlp_8192tokens.md
+GEMM_TRAFFIC_PER_FLOP = 7.0e-4    # (337.5 + 565.1) MB over (0.859 + 0.429) TFLOP, profiles/gemm_bf16_mlp_8192tokens.md
 
 
 def parse():
@@ -46,10 +46,18 @@ def parse():
     ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
     ap.add_argument('--shape', default='4b-4b', choices=sorted(wl.SHAPES))
     ap.add_argument('--requests', type=int, default=256, help='requests per rank per step')
-    ap.add_argument('--seed', type=int, default=4)
+    ap.add_argument('--seed', type=int, default=None, help='default: 4 (judged), 5 (long)')
+    ap.add_argument('--workload', default='judged', choices=['judged', 'long'],
+                    help="judged: 512-8192-token states, 1-24 questions; long: 32768-token states x 64 questions")
+    ap.add_argument('--linears', default='bf16', choices=['bf16', 'fp8'], help='projection / MLP GEMM precision')
     ap.add_argument('--cpu-seconds', type=float, default=15.0, help='CPU baseline budget per sample')
     ap.add_argument('--no-cpu-baseline', action='store_true')
-    return ap.parse_args()
+    args = ap.parse_args()
+    if args.seed is None:
+        args.seed = 5 if args.workload == 'long' else 4
+    if args.workload == 'long' and args.requests == 256:
+        args.requests = 4          # four 32768-token states with 64 questions each per GPU
+    return args
 
 
 def peaks():
@@ -60,9 +68,11 @@ def peaks():
     return dict(hbm=6650.0, burst=1590.0, sustained=1400.0, source='fallback')
 
 
-def make_requests(shape, seed, count):
+def make_requests(shape, seed, count, workload='judged'):
     if shape.name == 'tiny':
         return wl.tiny_requests(seed, requests=count, questions=3)
+    if workload == 'long':
+        return wl.long_context_requests(seed, vocab=shape.vocab, requests=count, eoi=shape.eoi_token)
     return wl.judged_requests(seed, vocab=shape.vocab, requests=count, eoi=shape.eoi_token)
 
 
@@ -186,7 +196,7 @@ def run_reference(args):
     gen = torch.Generator().manual_seed(args.seed)
     weights = {name: (torch.randn(dims, generator=gen, dtype=torch.bfloat16) * (0.02 if len(dims) >= 2 else 0.0))
                for name, dims in wl.weight_names(shape)}
-    requests = make_requests(shape, args.seed, args.requests)
+    requests = make_requests(shape, args.seed, args.requests, args.workload)
     sample = cpu_sample(shape, requests, args.cpu_seconds)
     questions = sum(len(r.questions) for r in sample)
     for _ in range(args.warmup):
@@ -221,13 +231,13 @@ def run_b200(args):
         dist.init_process_group('nccl', device_id=device)
     shape = wl.SHAPES[args.shape]
     weights = wl.make_weights_device(shape, args.seed, device)
-    engine = JudgmentEngine(weights, shape, device)
+    engine = JudgmentEngine(weights, shape, device, linears=args.linears)
     del weights
-    requests = make_requests(shape, args.seed + rank, args.requests)
+    requests = make_requests(shape, args.seed + rank, args.requests, args.workload)
     questions = sum(len(r.questions) for r in requests)
     batch = engine.prepare(requests)
     staged, offsets = engine.stage(batch)
-    max_candidates = 10 * 24 * args.requests
+    max_candidates = 10 * 64 * args.requests
 
     def barrier():
         if world > 1:
@@ -302,8 +312,12 @@ def run_b200(args):
             'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': device_ms / args.steps, 'higher_is_better': True,
             'scaling': 'weak', 'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic',
             'config': {
-                'workload': f'{shape.name} judged requests: {args.requests} requests per GPU per step, states 512-8192 tokens, '
-                            f'1-24 questions each, 8 questions per decoder group (seed {args.seed} + rank)',
+                'workload': (f'{shape.name} judged requests: {args.requests} requests per GPU per step, states 512-8192 tokens, '
+                             f'1-24 questions each, 8 questions per decoder group (seed {args.seed} + rank)'
+                             if args.workload == 'judged' else
+                             f'{shape.name} long-context shared evidence: {args.requests} requests per GPU per step, 32768-token '
+                             f'states, 64 questions each in groups of 8 (seed {args.seed} + rank)'),
+                'linears': args.linears,
                 'questions_per_step': int(total_questions), 'parallelism': f'dp{world}',
                 'l2': 'inputs larger than L2: 14 GB of weights and >1 GB of activations stream per layer',
                 'tflop_per_step_per_gpu': (batch.gemm_flops + batch.attn_flops) / 1e12,
@@ -311,7 +325,7 @@ def run_b200(args):
             'e2e': {'value': total_questions * args.steps / (e2e_ms / 1e3), 'unit': UNIT,
                     'h2d_bytes_per_step': batch.h2d_bytes, 'd2h_bytes_per_step': int(host.numel() * 8)},
             'gpu_launches': int(launches),
-            'roofline': {'bound': 'tensor', 'kernel': 'gemm_bf16_kernel', 'achieved': achieved, 'peak': pk['sustained'],
+            'roofline': {'bound': 'tensor', 'kernel': 'gemm_bf16_pair_kernel' if args.linears == 'bf16' else 'gemm_fp8_kernel', 'achieved': achieved, 'peak': pk['sustained'],
                          'unit': 'TFLOP/s', 'frac': achieved / pk['sustained'], 'peak_source': pk['source'] + ' sustained',
                          'launches': gemm_launches, 'share_of_step': gemm_ms / device_ms,
                          'traffic': None if GEMM_TRAFFIC_PER_FLOP is None else GEMM_TRAFFIC_PER_FLOP * gemm_flops / gemm_launches},
