@@ -51,6 +51,8 @@ def parse():
                     help="judged: 512-8192-token states, 1-24 questions; long: 32768-token states x 64 questions")
     ap.add_argument('--linears', default='bf16', choices=['bf16', 'fp8'], help='projection / MLP GEMM precision')
     ap.add_argument('--cpu-seconds', type=float, default=15.0, help='CPU baseline budget per sample')
+    ap.add_argument('--encoder-pack-tokens', type=int, default=65536)
+    ap.add_argument('--decoder-pack-tokens', type=int, default=16384)
     ap.add_argument('--no-cpu-baseline', action='store_true')
     args = ap.parse_args()
     if args.seed is None:
@@ -231,7 +233,8 @@ def run_b200(args):
         dist.init_process_group('nccl', device_id=device)
     shape = wl.SHAPES[args.shape]
     weights = wl.make_weights_device(shape, args.seed, device)
-    engine = JudgmentEngine(weights, shape, device, linears=args.linears)
+    engine = JudgmentEngine(weights, shape, device, linears=args.linears, encoder_pack_tokens=args.encoder_pack_tokens,
+                            decoder_pack_tokens=args.decoder_pack_tokens)
     del weights
     requests = make_requests(shape, args.seed + rank, args.requests, args.workload)
     questions = sum(len(r.questions) for r in requests)

@@ -157,11 +157,40 @@ class B200EncoderAttention(nn.Module):
 
         if packed_layout is not None:
             return encoder_attention(self, hidden_states, position_embeddings, packed_layout)
-        if hidden_states.shape[0] != 1:
-            raise ValueError('dense encoder batches must be packed: pass packed_layout (one row is served directly)')
-        # One dense sequence is a pack of one segment (bongard/model.py:313-321 encode()).
-        layout = _dense_layout(hidden_states.shape[1], hidden_states.device, kwargs.get('position_ids'))
-        return encoder_attention(self, hidden_states, position_embeddings, layout)
+        b, s, _ = hidden_states.shape
+        if b == 1 and not _has_padding(attention_mask):
+            # One dense sequence is a pack of one segment (bongard/model.py:313-321 encode()).
+            layout = _dense_layout(s, hidden_states.device, kwargs.get('position_ids'))
+            return encoder_attention(self, hidden_states, position_embeddings, layout)
+        # Right-padded batch (bongard/model.py:323-340 encode_batch): a token is valid iff it may
+        # attend to itself; valid tokens are packed, attended and scattered back, padding rows stay zero.
+        if attention_mask is None:
+            valid = torch.ones(b, s, dtype=torch.bool, device=hidden_states.device)
+        else:
+            diag = attention_mask.diagonal(dim1=-2, dim2=-1)[:, 0]
+            valid = diag if diag.dtype == torch.bool else diag == 0
+        lengths = valid.sum(1).tolist()
+        keep = valid.reshape(-1).nonzero().squeeze(1)
+        layout = packed_layout_for(lengths, hidden_states.device)
+        position_ids = kwargs.get('position_ids')
+        if position_ids is not None:
+            layout.positions32 = position_ids.expand(b, s).reshape(-1).index_select(0, keep).to(torch.int32)
+        packed = hidden_states.reshape(b * s, -1).index_select(0, keep)
+        out, _ = encoder_attention(self, packed[None], None, layout)
+        full = torch.zeros(b * s, out.shape[-1], device=out.device, dtype=out.dtype)
+        full.index_copy_(0, keep, out[0])
+        return full.view(b, s, -1), None
+
+
+def _has_padding(mask):
+    if mask is None or not torch.is_tensor(mask) or mask.ndim != 4:
+        return False
+    diag = mask.diagonal(dim1=-2, dim2=-1)
+    return bool((~diag).any()) if diag.dtype == torch.bool else bool((diag != 0).any())
+
+
+def packed_layout_for(lengths, device):
+    return packed_layout([n for n in lengths], [], device)
 
 
 def _dense_layout(length, device, position_ids=None):

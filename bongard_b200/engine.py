@@ -122,16 +122,29 @@ class JudgmentEngine:
         return HostPack(torch.from_numpy(ids).pin_memory(), torch.from_numpy(np.concatenate(parts)).pin_memory(),
                         total, keys, plans, rows, pairs)
 
-    def prepare(self, requests, branch_batch_size=8):
+    def prepare(self, requests, branch_batch_size=8, state_owners=None):
         """Host-side layout of a batch: token ids, positions, attention plans and readout rows
-        of every encoder and decoder pack, in pinned buffers ready for one copy each."""
+        of every encoder and decoder pack, in pinned buffers ready for one copy each.
+
+        Requests of one pack that share an owner and a state (`state_owners`, as in the reference's
+        forward_packed, bongard/packing.py:229-238) are encoded once and share the state K/V."""
         batch = HostBatch()
         s = self.shape
+        owners = list(range(len(requests))) if state_owners is None else list(state_owners)
+        if len(owners) != len(requests):
+            raise ValueError('state_owners must match requests')
         for pack in self._request_packs(requests):
             reqs = [requests[i] for i in pack]
-            state_lengths = [len(r.state) for r in reqs]
-            enc = self._host_pack([r.state for r in reqs])
-            members = [((local, qid), q) for local, r in enumerate(reqs) for qid, q in r.questions.items()]
+            states, rows, row_of = [], {}, []
+            for i, r in zip(pack, reqs):
+                key = (owners[i], r.state_key)
+                if key not in rows:
+                    rows[key] = len(states)
+                    states.append(r.state)
+                row_of.append(rows[key])
+            state_lengths = [len(st) for st in states]
+            enc = self._host_pack(states)
+            members = [((row_of[local], qid), q) for local, r in enumerate(reqs) for qid, q in r.questions.items()]
             decs = []
             for qpack in self._question_packs(members, branch_batch_size):
                 cand, dec, offset = [], [], 0
@@ -283,9 +296,7 @@ class JudgmentEngine:
     def forward_packed(self, requests, branch_batch_size=8, state_owners=None):
         """Same result structure as the reference's forward_packed: one dict per request,
         {qid: {'logits': [K], 'readouts': [K+1, hidden]}} (bongard/packing.py:316-318)."""
-        if state_owners is not None and list(state_owners) != list(range(len(requests))):
-            raise ValueError('shared state owners are a training-time feature; pass distinct requests')
-        batch = self.prepare(requests, branch_batch_size)
+        batch = self.prepare(requests, branch_batch_size, state_owners)
         staged, _ = self.stage(batch)
         logits, hidden_rows = self.execute(staged, keep_hidden=True)
         readouts = []

@@ -158,3 +158,23 @@ def test_enable_surfaces_and_fp8_end_to_end(tiny):
     assert float((p_eng - p_bf16).abs().max()) < 3e-2
     with pytest.raises(ValueError):
         enable_float8(backbone, 'tensorwise')
+
+
+def test_padded_dense_encoder_batch_matches_packed(tiny):
+    """The reference's encode_batch path: a right-padded [B, S] batch with an attention mask."""
+    weights, requests = tiny
+    backbone = build_backbone(wl.TINY, weights)
+    install_b200_inference(backbone)
+    states = [r.state for r in requests[:3]]
+    packed = PackedJudge(backbone, weights).encode(states)[0]
+    width = max(map(len, states))
+    ids = torch.tensor([list(st) + [0] * (width - len(st)) for st in states], device=DEV)
+    lengths = torch.tensor([len(st) for st in states], device=DEV)
+    mask = (torch.arange(width, device=DEV)[None, :] < lengths[:, None]).long()
+    with torch.inference_mode():
+        dense = backbone.encoder(input_ids=ids, attention_mask=mask, bongard_encoder_windows={}, use_cache=False).last_hidden_state
+    offset = 0
+    for i, st in enumerate(states):
+        a, b = dense[i, :len(st)].float(), packed[offset:offset + len(st)].float()
+        assert float((a - b).abs().max()) <= 3e-2 + 2e-2 * float(b.abs().max())
+        offset += len(st)
