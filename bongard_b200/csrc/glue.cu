@@ -80,8 +80,14 @@ __global__ void add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ y, const __
     const bool active = c < h;
     float f[8], x[8];
     float ss = 0.f;
+    // both row loads are issued before the first reduction so that two 16-byte requests per
+    // thread are in flight; y is read exactly once (streaming load)
+    uint4 raw_y = make_uint4(0, 0, 0, 0), raw_x = make_uint4(0, 0, 0, 0), raw_g = make_uint4(0, 0, 0, 0);
     if (active) {
-        unpack8(*reinterpret_cast<const uint4*>(y + row * h + c), f);
+        raw_y = __ldcs(reinterpret_cast<const uint4*>(y + row * h + c));
+        raw_x = *reinterpret_cast<const uint4*>(resid + row * h + c);
+        raw_g = __ldg(reinterpret_cast<const uint4*>(w_post + c));
+        unpack8(raw_y, f);
 #pragma unroll
         for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
     }
@@ -89,8 +95,8 @@ __global__ void add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ y, const __
     ss = 0.f;
     if (active) {
         float g[8];
-        unpack8(*reinterpret_cast<const uint4*>(w_post + c), g);
-        unpack8(*reinterpret_cast<const uint4*>(resid + row * h + c), x);
+        unpack8(raw_g, g);
+        unpack8(raw_x, x);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             x[i] = round_bf16(x[i] + round_bf16(f[i] * r * (1.f + g[i])));

@@ -4,12 +4,18 @@
     python -m bongard_b200.microbench mlp [--tokens 32768]
     python -m bongard_b200.microbench linear [--tokens 32768]
     python -m bongard_b200.microbench glue [--tokens 32768]
+    python -m bongard_b200.microbench serve [--shape 4b-4b] [--requests 40] [--no-graphs]
 
 attention: packed encoder self-attention, lengths uniform in 256-4096 (seed 2), 8 query / 4 KV
 heads of 256, QK-norm + RoPE applied by the glue kernel first; FLOPs = 4 D Hq (visible pairs).
 mlp: tokens x 2560 -> GeGLU(2 x 10240) -> 2560.  linear: the q|k|v and o projections.
 Each op is timed with CUDA events over `--iters` launches after `--warmup`; inputs are larger
 than L2 or L2 is flushed between launches (--flush).  Prints one JSON object per op.
+serve: wall-clock latency of `serving.Predictor.predict` (host token ids in, probabilities out):
+short requests one at a time (distinct states of 256-1024 tokens, one question each; median and
+p95 after one pass that captures the buckets), and 32 questions on one 2048-token state as one
+request against 32 separate requests (the two workloads the reference quotes latencies for,
+README.md:185-186, there on other hardware and real requests).
 """
 
 from __future__ import annotations
@@ -128,9 +134,59 @@ def glue(args, flush):
     return out
 
 
+def serve(args, flush):
+    import statistics
+    import time
+
+    from .engine import JudgmentEngine
+    from .serving import Predictor
+
+    shape = wl.SHAPES[args.shape]
+    engine = JudgmentEngine(wl.make_weights_device(shape, 4, DEV), shape)
+    served = Predictor(engine, graphs=not args.no_graphs)
+
+    def clock(request):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        served.predict(request)
+        return (time.perf_counter() - t0) * 1e3
+
+    short = wl.judged_requests(21, vocab=shape.vocab, requests=args.requests, state=(256, 1024), questions=(1, 1))
+    for r in short:
+        served.predict(r)                          # captures every bucket these requests touch
+    served.clear_state_cache()
+    cold = sorted(clock(r) for r in short)          # encoder + projection + decoder per request
+    warm = sorted(clock(r) for r in short)          # encoder state cached
+    out = [dict(op='serve_short', shape=shape.name, graphs=not args.no_graphs, requests=len(short),
+                state_tokens='256-1024', questions=1,
+                median_ms=statistics.median(cold), p95_ms=cold[int(0.95 * (len(cold) - 1))],
+                cached_state_median_ms=statistics.median(warm), cache=served.state_cache_info())]
+
+    shared = wl.judged_requests(22, vocab=shape.vocab, requests=1, state=(2048, 2048), questions=(32, 32))[0]
+    singles = [wl.Request(shared.state, {qid: q}) for qid, q in shared.questions.items()]
+    served.predict(shared)
+    for r in singles:
+        served.predict(r)
+    served.clear_state_cache()
+    together = min(clock(shared) for _ in range(3) if served.clear_state_cache() is None)
+    served.clear_state_cache()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for r in singles:
+        served.predict(r)
+    separate = (time.perf_counter() - t0) * 1e3
+    out.append(dict(op='serve_shared_state', shape=shape.name, graphs=not args.no_graphs, state_tokens=2048, questions=32,
+                    one_request_ms=together, separate_requests_ms=separate,
+                    question_tokens=sum(len(q.tokens) for q in shared.questions.values())))
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument('op', choices=['attention', 'mlp', 'linear', 'glue'])
+    ap.add_argument('op', choices=['attention', 'mlp', 'linear', 'glue', 'serve'])
+    ap.add_argument('--shape', default='4b-4b', choices=sorted(wl.SHAPES))
+    ap.add_argument('--requests', type=int, default=40)
+    ap.add_argument('--no-graphs', action='store_true', help='serve: launch every kernel eagerly')
     ap.add_argument('--variant', default='global', choices=['global', 'window'])
     ap.add_argument('--sequences', type=int, default=16)
     ap.add_argument('--tokens', type=int, default=32768)
@@ -141,7 +197,7 @@ def main():
     args = ap.parse_args()
     ops.device_check()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV) if args.flush else None
-    result = {'attention': attention, 'mlp': mlp, 'linear': linear, 'glue': glue}[args.op](args, flush)
+    result = {'attention': attention, 'mlp': mlp, 'linear': linear, 'glue': glue, 'serve': serve}[args.op](args, flush)
     ops.read_status()
     for row in result if isinstance(result, list) else [result]:
         print(json.dumps(row))

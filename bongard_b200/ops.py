@@ -252,6 +252,19 @@ class HostPlan:
         dev = torch.from_numpy(self.packed).to(device, non_blocking=True)
         return self.view(dev)
 
+    def padded(self, tokens, n_tiles):
+        """The same plan in arrays of a fixed size (for launches captured in a CUDA graph): tiles
+        beyond the plan's own are empty (no rows, no keys: the kernel skips them) and tokens
+        beyond its own see no key."""
+        if tokens < self.tokens or n_tiles < self.n_tiles:
+            raise ValueError(f'plan of {self.tokens} tokens / {self.n_tiles} tiles does not fit {tokens} / {n_tiles}')
+        n8, t = self.n_tiles * 8, self.tokens
+        out = np.zeros(n_tiles * 8 + 2 * tokens, dtype=np.int32)
+        out[:n8] = self.packed[:n8]
+        out[n_tiles * 8:n_tiles * 8 + t] = self.packed[n8:n8 + t]
+        out[n_tiles * 8 + tokens:n_tiles * 8 + tokens + t] = self.packed[n8 + t:n8 + 2 * t]
+        return HostPlan(out, tokens, n_tiles, self.pairs, self.tile_rows)
+
     def view(self, dev):
         n8, t = self.n_tiles * 8, self.tokens
         return AttentionPlan(dev[:n8].view(-1, 8), dev[n8:n8 + t], dev[n8 + t:n8 + 2 * t], t, self.n_tiles, self.pairs,
@@ -259,7 +272,7 @@ class HostPlan:
 
 
 def tile_rows(head_dim):
-    """Query rows per attention tile for a head size: 256 at head_dim 256 (CTA pairs), else 128."""
+    """Query rows (tokens x GQA group) one attention tile holds for a head size, as the library reports it."""
     return _lib.load().bg_attention_tile_rows(int(head_dim)) if head_dim else 128
 
 

@@ -1,0 +1,70 @@
+"""Single-request serving path (encode -> state K/V -> decode through captured CUDA graphs, with
+the encoder-state LRU) against the packed throughput engine on the same requests."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from bongard_b200 import workload as wl  # noqa: E402
+from bongard_b200.engine import JudgmentEngine  # noqa: E402
+from bongard_b200.serving import Predictor  # noqa: E402
+
+
+@pytest.fixture(scope='module')
+def engine():
+    return JudgmentEngine(wl.make_weights(wl.TINY, 1), wl.TINY)
+
+
+def cat(answers):
+    return torch.cat(list(answers.values()))
+
+
+def test_predict_matches_packed_engine(engine):
+    requests = wl.tiny_requests(1)
+    packed = engine.judge(requests)
+    served = Predictor(engine, state_bucket=64, question_bucket=32)
+    for request, expect in zip(requests, packed):
+        got = served.predict(request)
+        assert list(got) == list(expect)
+        # padded buckets change no row's arithmetic: same kernels, same accumulation order
+        assert float((cat(got) - cat(expect)).abs().max()) < 1e-6
+    assert served.graph_replays >= 3 * len(requests)
+    assert served.state_cache_info()['misses'] == len(requests)
+
+
+def test_graphs_and_eager_agree_bit_for_bit(engine):
+    requests = wl.tiny_requests(1)
+    graphed = Predictor(engine, state_bucket=64, question_bucket=32)
+    eager = Predictor(engine, state_bucket=64, question_bucket=32, graphs=False)
+    for request in requests:
+        assert torch.equal(cat(graphed.predict(request)), cat(eager.predict(request)))
+    assert eager.graph_replays == 0
+
+
+def test_state_reuse_and_cache_hits(engine):
+    requests = wl.tiny_requests(1)
+    served = Predictor(engine, state_bucket=512, question_bucket=256)      # every state shares one bucket
+    first = [cat(served.predict(r)) for r in requests]
+    replays = served.graph_replays
+    again = cat(served.predict(requests[-1]))                 # K/V of the last state are still loaded
+    assert torch.equal(again, first[-1])
+    assert served.graph_replays == replays + 1                # decoder only
+    back = cat(served.predict(requests[0]))                   # cached hidden state, K/V projected again
+    assert torch.equal(back, first[0])
+    assert served.graph_replays == replays + 3                # projection + decoder
+    info = served.state_cache_info()
+    assert info['entries'] == len(requests) and info['hits'] == 2 and info['misses'] == len(requests)
+    served.clear_state_cache()
+    assert torch.equal(cat(served.predict(requests[0])), first[0])
+    assert served.state_cache_info()['misses'] == len(requests) + 1
+
+
+def test_single_question_subsets(engine):
+    request = wl.tiny_requests(1)[0]
+    served = Predictor(engine, state_bucket=64, question_bucket=32)
+    whole = served.predict(request)
+    for qid, question in request.questions.items():
+        alone = wl.Request(request.state, {qid: question})
+        got = served.predict(alone)[qid]
+        assert float((got - whole[qid]).abs().max()) < 1e-6
