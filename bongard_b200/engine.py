@@ -79,7 +79,8 @@ class JudgmentEngine:
         self.enc = [_stack_layer(weights, f'encoder.text_model.layers.{i}.', self.device, fp8) for i in range(shape.layers)]
         self.dec = [_stack_layer(weights, f'decoder.layers.{i}.', self.device, fp8, True) for i in range(shape.layers)]
         self.head_w, self.head_c, self.head_g = g('head.w.weight'), g('head.candidate.weight'), g('head.global_readout.weight')
-        self.embed_scale = embed_scale(shape, BF16)
+        # per stack, as a checkpoint may override either (bongard/model.py:632-637)
+        self.embed_scale_enc = self.embed_scale_dec = embed_scale(shape, BF16)
         self.launches = 0          # kernels launched by this library (for reporting)
 
     # ------------------------------------------------------------------ host-side preparation
@@ -183,7 +184,8 @@ class JudgmentEngine:
 
     def _stack(self, layers, final_norm, pack, cross=None):
         s = self.shape
-        x = ops.embed(pack.ids, self.table, self.eoi, self.embed_scale, s.eoi_token)
+        scale = self.embed_scale_enc if layers is self.enc else self.embed_scale_dec
+        x = ops.embed(pack.ids, self.table, self.eoi, scale, s.eoi_token)
         n = ops.rmsnorm(x, layers[0].pre_attn, s.eps)
         t = x.shape[0]
         qd, kd = s.q_dim, s.kv_dim
