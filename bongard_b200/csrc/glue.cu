@@ -214,45 +214,81 @@ __global__ void embed_kernel(const int64_t* __restrict__ ids, const __nv_bfloat1
 }
 
 // Judgment head (bongard/model.py:92-95): logit = w.h + (C h).(G g) / sqrt(rank).
-// One block per candidate; thread j < rank owns row j of C and G.  fp32 throughout.
-__global__ void judgment_head_kernel(const __nv_bfloat16* __restrict__ hidden, int64_t ldh,
-                                     const int32_t* __restrict__ cand_rows, const int32_t* __restrict__ dec_rows,
-                                     const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ cmat,
-                                     const __nv_bfloat16* __restrict__ gmat, float* __restrict__ logits, int h,
-                                     int rank) {
+// A cluster of HEAD_SPLIT CTAs per candidate: CTA r takes rows [r, r+1) * rank/HEAD_SPLIT of C and G,
+// one warp per row with the lanes striding along it (coalesced 512-byte reads), and parks its partial
+// sum in shared memory; CTA 0 adds the partials in rank order through distributed shared memory, so
+// the result does not depend on scheduling.  A single question (2-10 candidates) thereby spreads the
+// 2.6 MB of head weights over 16-80 SMs instead of 2-10.  fp32 throughout.
+constexpr int HEAD_SPLIT = 8;
+
+__global__ void __cluster_dims__(1, HEAD_SPLIT, 1)
+judgment_head_kernel(const __nv_bfloat16* __restrict__ hidden, int64_t ldh,
+                     const int32_t* __restrict__ cand_rows, const int32_t* __restrict__ dec_rows,
+                     const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ cmat,
+                     const __nv_bfloat16* __restrict__ gmat, float* __restrict__ logits, int h,
+                     int rank) {
     extern __shared__ float sh[];      // h floats of the candidate row, h floats of the decision row
     __shared__ float scratch[33];
+    __shared__ float warp_acc[8];
+    __shared__ float partial;
     float* hc = sh;
     float* hg = sh + h;
     const int cand = blockIdx.x;
+    const int chunk = blockIdx.y;      // == rank of this CTA in its cluster
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     const __nv_bfloat16* pc = hidden + int64_t(cand_rows[cand]) * ldh;
     const __nv_bfloat16* pg = hidden + int64_t(dec_rows[cand]) * ldh;
-    for (int i = threadIdx.x; i < h; i += blockDim.x) {
-        hc[i] = __bfloat162float(pc[i]);
-        hg[i] = __bfloat162float(pg[i]);
+    for (int i = threadIdx.x * 8; i < h; i += blockDim.x * 8) {
+        unpack8(*reinterpret_cast<const uint4*>(pc + i), hc + i);
+        unpack8(*reinterpret_cast<const uint4*>(pg + i), hg + i);
     }
     __syncthreads();
+    const int per = (rank + HEAD_SPLIT - 1) / HEAD_SPLIT;
+    const int j_hi = min(rank, (chunk + 1) * per);
     float acc = 0.f;
-    for (int j = threadIdx.x; j < rank; j += blockDim.x) {
+    for (int j = chunk * per + warp; j < j_hi; j += warps) {
         const __nv_bfloat16* cr = cmat + int64_t(j) * h;
         const __nv_bfloat16* gr = gmat + int64_t(j) * h;
         float a = 0.f, b = 0.f;
-        for (int i = 0; i < h; i += 8) {
+        for (int i = lane * 8; i < h; i += 256) {
             float fc[8], fg[8];
-            unpack8(*reinterpret_cast<const uint4*>(cr + i), fc);
-            unpack8(*reinterpret_cast<const uint4*>(gr + i), fg);
+            unpack8(__ldg(reinterpret_cast<const uint4*>(cr + i)), fc);
+            unpack8(__ldg(reinterpret_cast<const uint4*>(gr + i)), fg);
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 a += fc[e] * hc[i + e];
                 b += fg[e] * hg[i + e];
             }
         }
-        acc += a * b;
+        a = warp_sum(a);
+        b = warp_sum(b);
+        acc += a * b;                  // identical in every lane
     }
-    acc *= rsqrtf(float(rank));
-    for (int i = threadIdx.x; i < h; i += blockDim.x) acc += __bfloat162float(w[i]) * hc[i];
-    const float total = block_sum(acc, scratch);
-    if (threadIdx.x == 0) logits[cand] = total;
+    if (lane == 0) warp_acc[warp] = acc;
+    float wdot = 0.f;
+    if (chunk == 0) {
+        float t = 0.f;
+        for (int i = threadIdx.x; i < h; i += blockDim.x) t += __bfloat162float(w[i]) * hc[i];
+        wdot = block_sum(t, scratch);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int k = 0; k < warps; ++k) t += warp_acc[k];
+        partial = t;
+    }
+    bg::cluster_sync();                // every CTA's partial is written and visible
+    if (chunk == 0 && threadIdx.x == 0) {
+        float total = 0.f;
+        const uint32_t addr = bg::smem_u32(&partial);
+        for (int r = 0; r < HEAD_SPLIT; ++r) {
+            float v;
+            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(bg::map_to_cta(addr, (uint32_t)r)));
+            total += v;
+        }
+        logits[cand] = total * rsqrtf(float(rank)) + wdot;
+    }
+    bg::cluster_sync();                // no CTA leaves while CTA 0 reads its partial
 }
 
 // Per-question temperature softmax in float64 (bongard/inference.py:54-73), one thread per question.
@@ -406,7 +442,7 @@ int bg_judgment_head(const void* hidden, int64_t ldh, const int32_t* cand_rows, 
         cudaFuncSetAttribute(judgment_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
         configured = true;
     }
-    judgment_head_kernel<<<(unsigned)candidates, 256, smem, static_cast<cudaStream_t>(stream)>>>(
+    judgment_head_kernel<<<dim3((unsigned)candidates, HEAD_SPLIT), 256, smem, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __nv_bfloat16*>(hidden), ldh, cand_rows, dec_rows, static_cast<const __nv_bfloat16*>(w),
         static_cast<const __nv_bfloat16*>(cmat), static_cast<const __nv_bfloat16*>(gmat), logits, (int)h, rank);
     return check_launch("bg_judgment_head");

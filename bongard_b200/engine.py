@@ -82,6 +82,9 @@ class JudgmentEngine:
         # per stack, as a checkpoint may override either (bongard/model.py:632-637)
         self.embed_scale_enc = self.embed_scale_dec = embed_scale(shape, BF16)
         self.launches = 0          # kernels launched by this library (for reporting)
+        # The serving path lets stacks of up to 256 tokens use the split-K weight-streaming GEMM.  The
+        # packed engine keeps it off, so that where a pack boundary falls never changes a result bit.
+        self.few_rows_kernels = False
 
     # ------------------------------------------------------------------ host-side preparation
     def _window_key(self, index, longest, decoder):
@@ -176,11 +179,11 @@ class JudgmentEngine:
     def _freqs(self, index):
         return ops.inv_freq(self.shape.head_dim, self.shape.layer_theta(index), self.device)
 
-    @staticmethod
-    def _lin(x, w, geglu=False):
+    def _lin(self, x, w, geglu=False):
         if isinstance(w, ops.Fp8Weight):
             return ops.linear_fp8(x, w, geglu=geglu)
-        return ops.linear_geglu(x, w) if geglu else ops.linear(x, w)
+        few = self.few_rows_kernels
+        return ops.linear_geglu(x, w, few_rows=few) if geglu else ops.linear(x, w, few_rows=few)
 
     def _stack(self, layers, final_norm, pack, cross=None):
         s = self.shape

@@ -84,8 +84,8 @@ def mlp(args, flush):
     out = []
     hidden = ops.linear_geglu(x, wgu)
     for name, fn, flops, nbytes in (
-            ('gate_up_geglu', lambda: ops.linear_geglu(x, wgu), 4 * t * h * i, 2 * (t * h + 2 * i * h + t * i)),
-            ('down', lambda: ops.linear(hidden, wd), 2 * t * h * i, 2 * (t * i + i * h + t * h))):
+            ('gate_up_geglu', lambda: ops.linear_geglu(x, wgu, few_rows=args.few_rows), 4 * t * h * i, 2 * (t * h + 2 * i * h + t * i)),
+            ('down', lambda: ops.linear(hidden, wd, few_rows=args.few_rows), 2 * t * h * i, 2 * (t * i + i * h + t * h))):
         ms = timed(fn, args.iters, args.warmup, flush)
         out.append(dict(op=f'gemm_bf16_{name}', tokens=t, ms=ms, tflops=flops / ms / 1e9, min_bytes=nbytes))
     both = timed(lambda: ops.linear(ops.linear_geglu(x, wgu), wd), args.iters, args.warmup, flush)
@@ -110,7 +110,7 @@ def linear(args, flush):
     out = []
     for name, n, k in (('qkv', 4096, 2560), ('o', 2560, 2048)):
         x, w = randn(t, k, seed=6), randn(n, k, std=0.02, seed=7)
-        ms = timed(lambda: ops.linear(x, w), args.iters, args.warmup, flush)
+        ms = timed(lambda: ops.linear(x, w, few_rows=args.few_rows), args.iters, args.warmup, flush)
         out.append(dict(op=f'gemm_bf16_{name}', tokens=t, ms=ms, tflops=2 * t * n * k / ms / 1e9,
                         min_bytes=2 * (t * k + n * k + t * n)))
     return out
@@ -186,6 +186,7 @@ def main():
     ap.add_argument('op', choices=['attention', 'mlp', 'linear', 'glue', 'serve'])
     ap.add_argument('--shape', default='4b-4b', choices=sorted(wl.SHAPES))
     ap.add_argument('--requests', type=int, default=40)
+    ap.add_argument('--few-rows', action='store_true', help='linear/mlp: allow the split-K kernel for <= 256 tokens')
     ap.add_argument('--no-graphs', action='store_true', help='serve: launch every kernel eagerly')
     ap.add_argument('--variant', default='global', choices=['global', 'window'])
     ap.add_argument('--sequences', type=int, default=16)

@@ -158,8 +158,18 @@ def embed(ids, table, eoi_embedding, scale, eoi_token=256_000):
     return out
 
 
-def linear(x, weight, out=None):
-    """x [..., K] @ weight[N, K].T -> [..., N] on the tensor cores."""
+def _gemm(lib, few_rows, m, n, k, epilogue):
+    """The entry point for a contraction: the weight-streaming kernel when the caller allows it
+    (`few_rows`) and the shape is one it takes, else the throughput kernels."""
+    if few_rows and lib.bg_gemm_bf16_skinny_supported(m, n, k, epilogue):
+        return lib.bg_gemm_bf16_skinny, 'bg_gemm_bf16_skinny'
+    return lib.bg_gemm_bf16, 'bg_gemm_bf16'
+
+
+def linear(x, weight, out=None, *, few_rows=False):
+    """x [..., K] @ weight[N, K].T -> [..., N] on the tensor cores.  `few_rows=True` lets inputs of
+    up to 256 rows take the split-K weight-streaming kernel (latency path; its fp32 summation
+    order differs from the throughput kernels)."""
     lib = _lib.load()
     flat, m, k, lda = _rows(x, 'x')
     _need(weight, 'weight')
@@ -170,14 +180,14 @@ def linear(x, weight, out=None):
         out = torch.empty((m, n), device=x.device, dtype=BF16)
     timer = GEMM_TIMER
     begin = timer.start() if timer is not None else None
-    _lib.check(lib.bg_gemm_bf16(_ptr(flat), lda, _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), m, n, k, 0,
-                                _stream()), 'bg_gemm_bf16')
+    fn, name = _gemm(lib, few_rows, m, n, k, 0)
+    _lib.check(fn(_ptr(flat), lda, _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), m, n, k, 0, _stream()), name)
     if timer is not None:
         timer.stop(begin, 2 * m * n * k)
     return out.view(*x.shape[:-1], n)
 
 
-def linear_geglu(x, gate_up):
+def linear_geglu(x, gate_up, *, few_rows=False):
     """gelu_tanh(x @ gate.T) * (x @ up.T) with gate_up = cat([gate, up]) of shape [2I, K]."""
     lib = _lib.load()
     flat, m, k, lda = _rows(x, 'x')
@@ -188,8 +198,8 @@ def linear_geglu(x, gate_up):
     out = torch.empty((m, n), device=x.device, dtype=BF16)
     timer = GEMM_TIMER
     begin = timer.start() if timer is not None else None
-    _lib.check(lib.bg_gemm_bf16(_ptr(flat), lda, _ptr(gate_up), gate_up.stride(0), _ptr(out), n, m, n, k, 1,
-                                _stream()), 'bg_gemm_bf16')
+    fn, name = _gemm(lib, few_rows, m, n, k, 1)
+    _lib.check(fn(_ptr(flat), lda, _ptr(gate_up), gate_up.stride(0), _ptr(out), n, m, n, k, 1, _stream()), name)
     if timer is not None:
         timer.stop(begin, 4 * m * n * k)
     return out.view(*x.shape[:-1], n)

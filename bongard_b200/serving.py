@@ -16,6 +16,9 @@ What differs from the packed throughput engine:
 * The state cache holds encoder hidden states (as the reference does) under a byte limit with
   LRU eviction; the bucket also remembers which state its projected K/V currently hold, so
   consecutive requests on one state skip both the encoder and the K/V projection.
+* Stacks of up to 256 tokens (a question group against a cached state) run their projections
+  on the split-K weight-streaming GEMM (`bg_gemm_bf16_skinny`), which is bound by HBM bandwidth
+  instead of by the 10-20 CTAs a 256-wide output tiling would give them.
 """
 
 from __future__ import annotations
@@ -80,6 +83,13 @@ def _round_up(n, step):
     return (n + step - 1) // step * step
 
 
+def _bucket(n, step, fine=32, fine_up_to=256):
+    """Bucket size for n tokens: multiples of `step`, but of `fine` up to `fine_up_to` tokens, where
+    the few-row GEMM's cost follows the row count and padding 130 tokens to 256 would double it."""
+    n = max(int(n), 1)
+    return _round_up(n, min(step, fine)) if n <= fine_up_to else _round_up(n, step)
+
+
 @dataclass
 class _Inputs:
     """Fixed-size device inputs of one stack with their pinned host mirror."""
@@ -98,7 +108,14 @@ class _Inputs:
 class _Stage:
     """One captured (or eager) stage: run() replays the graph or calls the function."""
 
-    def __init__(self, fn, use_graph):
+    def __init__(self, body, use_graph, engine):
+        def fn():
+            previous, engine.few_rows_kernels = engine.few_rows_kernels, True
+            try:
+                return body()
+            finally:
+                engine.few_rows_kernels = previous
+
         self.fn, self.graph, self.out = fn, None, None
         self.out = fn()                       # eager warm-up: lazy library init, allocator warm
         if use_graph:
@@ -119,10 +136,11 @@ class Predictor:
     """`predict(request)` for one `workload.Request`: {question id: float64 probabilities}."""
 
     def __init__(self, engine: JudgmentEngine, *, state_cache_mib=1024, graphs=True, state_bucket=256,
-                 question_bucket=128, max_graph_state=16384, max_graph_question=8192):
+                 question_bucket=128, fine_bucket=32, max_graph_state=16384, max_graph_question=8192):
         self.engine, self.graphs = engine, bool(graphs)
         self.cache = StateCache(int(state_cache_mib) * 2 ** 20)
         self.state_bucket, self.question_bucket = int(state_bucket), int(question_bucket)
+        self.fine_bucket = int(fine_bucket)   # granularity up to 256 tokens (see _bucket)
         self.max_graph_state, self.max_graph_question = int(max_graph_state), int(max_graph_question)
         s = engine.shape
         self.windows = list(dict.fromkeys(s.layer_window(i) for i in range(s.layers)))
@@ -192,7 +210,7 @@ class Predictor:
             e = self.engine
             inp = self._inputs(sb)
             self._fill(inp, [[0] * sb])
-            stage = _Stage(lambda: e._stack(e.enc, e.enc_norm, inp.pack), self._use_graph(sb, self.max_graph_state))
+            stage = _Stage(lambda: e._stack(e.enc, e.enc_norm, inp.pack), self._use_graph(sb, self.max_graph_state), e)
             self._enc[sb] = (inp, stage)
         return self._enc[sb]
 
@@ -200,7 +218,7 @@ class Predictor:
         if sb not in self._kv:
             e = self.engine
             state_in = torch.zeros(sb, e.shape.hidden, device=e.device, dtype=BF16)
-            stage = _Stage(lambda: e.state_kv(state_in), self._use_graph(sb, self.max_graph_state))
+            stage = _Stage(lambda: e.state_kv(state_in), self._use_graph(sb, self.max_graph_state), e)
             self._kv[sb] = {'state_in': state_in, 'stage': stage, 'holds': None}
         return self._kv[sb]
 
@@ -213,7 +231,7 @@ class Predictor:
             # a captured decoder reads the state K/V at fixed addresses, which only a captured
             # projection stage provides
             stage = _Stage(lambda: e._stack(e.dec, e.dec_norm, inp.pack, kv['stage'].out),
-                           self._use_graph(tb, self.max_graph_question) and kv['stage'].graph is not None)
+                           self._use_graph(tb, self.max_graph_question) and kv['stage'].graph is not None, e)
             self._dec[(sb, tb)] = (inp, stage)
         return self._dec[(sb, tb)]
 
@@ -228,7 +246,7 @@ class Predictor:
         """Candidate logits fp32 [sum of candidates] on the device, question order."""
         e = self.engine
         n_state = len(request.state)
-        sb = _round_up(max(n_state, 1), self.state_bucket)
+        sb = _bucket(n_state, self.state_bucket, self.fine_bucket)
         kv = self._state_kv(sb)
         key = request.state_key
         if kv['holds'] != key:
@@ -248,7 +266,7 @@ class Predictor:
             self.cache.get(key)                     # keeps the LRU order and the hit count honest
         questions = list(request.questions.values())
         total = sum(len(q.tokens) for q in questions)
-        tb = _round_up(max(total, 1), self.question_bucket)
+        tb = _bucket(total, self.question_bucket, self.fine_bucket)
         inp, stage = self._decoder(sb, tb)
         self._fill(inp, [q.tokens for q in questions], state_length=n_state)
         hidden = self._run(stage)

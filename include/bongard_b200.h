@@ -87,6 +87,17 @@ int bg_embed(const int64_t* ids, const void* table, const void* eoi_embedding, v
 int bg_gemm_bf16(const void* a, int64_t lda, const void* w, int64_t ldw, void* out, int64_t ldo, int64_t m,
                  int64_t n, int64_t k, int epilogue, void* stream);
 
+/* bg_gemm_bf16 for 1..256 rows (k % 64 == 0, n % 128 == 0; GeGLU: n % 64 == 0), the single-request
+ * serving case of bongard/model.py:448-458 (one question group decoded against a cached state), where
+ * the contraction is bound by streaming the weights from HBM: every weight byte is fetched once, K is
+ * split over the CTAs of a thread-block cluster sized so that one wave fills the GPU, and the partial
+ * tiles are summed in rank order through distributed shared memory (deterministic; the fp32 summation
+ * order differs from bg_gemm_bf16, so results may differ from it in the last bf16 bit).
+ * bg_gemm_bf16_skinny_supported returns 1 for shapes it takes, else 0; other shapes are BG_ERR_SHAPE. */
+int bg_gemm_bf16_skinny_supported(int64_t m, int64_t n, int64_t k, int epilogue);
+int bg_gemm_bf16_skinny(const void* a, int64_t lda, const void* w, int64_t ldw, void* out, int64_t ldo, int64_t m,
+                        int64_t n, int64_t k, int epilogue, void* stream);
+
 /* E4M3 quantisation with dynamic per-block scales: scale = 448 / max(amax, 1e-12), values clamped
  * to +-448 and rounded to nearest; the INVERSE scales are stored as fp32.
  *   rows : 1 x 128 blocks of x [m, k] -> q (uint8 [m, k], row stride ldq bytes), inv_scale_t [k/128, m].

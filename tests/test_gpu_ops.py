@@ -128,6 +128,47 @@ def test_linear_geglu(m, i, k):
     assert_close(got, want)
 
 
+# the four projections of a 4B layer and of the tiny model, at row counts around the 128-row tiles
+@pytest.mark.parametrize('n,k', [(4096, 2560), (2560, 2048), (2560, 10240), (512, 256), (256, 1024)])
+@pytest.mark.parametrize('m', [1, 100, 128, 129, 256])
+def test_linear_few_rows(m, n, k):
+    """The split-K weight-streaming kernel against fp32 and against the throughput kernel."""
+    x, w = rnd(m, k, seed=30), rnd(n, k, seed=31, std=0.02)
+    xd, wd = x.to(DEV), w.to(DEV)
+    got = ops.linear(xd, wd, few_rows=True)
+    assert_close(got, x.float() @ w.float().t())
+    # same products, another fp32 summation order: equal up to one rounding of the bf16 result
+    assert_close(got, ops.linear(xd, wd).float(), atol=2e-3, rtol=8e-3)
+    assert torch.equal(got, ops.linear(xd, wd, few_rows=True))          # deterministic reduction
+
+
+@pytest.mark.parametrize('m,i,k', [(3, 1024, 256), (140, 10240, 2560), (256, 10240, 2560), (200, 1024, 256)])
+def test_linear_geglu_few_rows(m, i, k):
+    x = rnd(m, k, seed=32)
+    gate, up = rnd(i, k, seed=33, std=0.02), rnd(i, k, seed=34, std=0.02)
+    got = ops.linear_geglu(x.to(DEV), torch.cat([gate, up]).to(DEV), few_rows=True)
+    want = torch.nn.functional.gelu(x.float() @ gate.float().t(), approximate='tanh') * (x.float() @ up.float().t())
+    assert_close(got, want)
+
+
+def test_linear_few_rows_falls_back_and_entry_point_rejects():
+    """Shapes the kernel does not take run on the throughput kernels; the entry point itself says no."""
+    from bongard_b200 import _lib
+
+    x, w = rnd(300, 256, seed=35).to(DEV), rnd(384, 256, seed=36, std=0.05).to(DEV)
+    assert_close(ops.linear(x, w, few_rows=True), x.float().cpu() @ w.float().cpu().t())      # 300 rows
+    assert_close(ops.linear(x[:8, :200], w[:128, :200].contiguous(), few_rows=True),            # k % 64 != 0
+                 x[:8, :200].float().cpu() @ w[:128, :200].float().cpu().t())
+    lib = _lib.load()
+    assert lib.bg_gemm_bf16_skinny_supported(256, 384, 256, 0) == 1
+    assert lib.bg_gemm_bf16_skinny_supported(257, 384, 256, 0) == 0
+    assert lib.bg_gemm_bf16_skinny_supported(8, 200, 256, 0) == 0
+    out = torch.empty(300, 384, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(ValueError):
+        _lib.check(lib.bg_gemm_bf16_skinny(x.data_ptr(), 256, w.data_ptr(), 256, out.data_ptr(), 384, 300, 384, 256, 0, 0),
+                   'bg_gemm_bf16_skinny')
+
+
 def test_geglu_mlp_matches_golden(golden_dir):
     g = {k: torch.from_numpy(v) for k, v in np.load(golden_dir / 'ops.npz').items() if k.startswith('mlp_')}
     x = g['mlp_x'].bfloat16()

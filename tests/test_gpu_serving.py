@@ -27,10 +27,20 @@ def test_predict_matches_packed_engine(engine):
     for request, expect in zip(requests, packed):
         got = served.predict(request)
         assert list(got) == list(expect)
-        # padded buckets change no row's arithmetic: same kernels, same accumulation order
-        assert float((cat(got) - cat(expect)).abs().max()) < 1e-6
+        # same math; the few-row GEMM sums K in another order, so bf16 roundings may differ
+        assert float((cat(got) - cat(expect)).abs().max()) < 4e-3
     assert served.graph_replays >= 3 * len(requests)
     assert served.state_cache_info()['misses'] == len(requests)
+
+
+def test_padding_changes_no_bit(engine):
+    """Bucket padding adds a pad segment and empty attention tiles; no valid row may notice."""
+    request = wl.tiny_requests(1)[0]
+    tight = Predictor(engine, state_bucket=1, question_bucket=1, graphs=False)
+    padded = Predictor(engine, state_bucket=256, question_bucket=128, graphs=False)
+    # both stay on the same kernels when the padded sizes do not cross the 256-row limit of the few-row GEMM
+    small = wl.Request(request.state[:100], dict(list(request.questions.items())[:1]))
+    assert torch.equal(cat(tight.predict(small)), cat(padded.predict(small)))
 
 
 def test_graphs_and_eager_agree_bit_for_bit(engine):
@@ -44,7 +54,7 @@ def test_graphs_and_eager_agree_bit_for_bit(engine):
 
 def test_state_reuse_and_cache_hits(engine):
     requests = wl.tiny_requests(1)
-    served = Predictor(engine, state_bucket=512, question_bucket=256)      # every state shares one bucket
+    served = Predictor(engine, state_bucket=512, question_bucket=256, fine_bucket=512)   # every state shares one bucket
     first = [cat(served.predict(r)) for r in requests]
     replays = served.graph_replays
     again = cat(served.predict(requests[-1]))                 # K/V of the last state are still loaded
