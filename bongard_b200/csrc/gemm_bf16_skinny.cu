@@ -12,10 +12,16 @@
 //   * K is split across the CTAs of a thread-block cluster (1-8 CTAs, chosen on the host so that
 //     tiles x split fills the GPU in one wave); each CTA streams its K slice through a 4-stage
 //     TMA ring and accumulates a partial tile in TMEM;
-//   * the partial tiles are reduced through distributed shared memory: every CTA parks its
-//     fp32 partial in its own shared memory (the drained ring), the cluster synchronises, and
-//     CTA r sums column slice r of all partials in rank order - deterministic, no global
-//     workspace, no second kernel - applies the epilogue and stores bf16.
+//   * the partial tiles are reduced through distributed shared memory: once every ring of the
+//     cluster has drained, each CTA sends column slice r of its fp32 partial straight from
+//     tensor memory into a slot in CTA r's shared memory (16-byte remote stores, which are
+//     posted - remote loads measured 5x slower), the cluster synchronises, and CTA r sums its
+//     slots in rank order - deterministic, no global workspace, no second kernel - applies the
+//     epilogue and stores bf16.
+//
+// Measured on B200 at 128 rows: the K loop runs at the rate the weight stream arrives from HBM
+// (skipping the activation loads or the MMAs changes nothing), so the ring is as deep as shared
+// memory allows (5-6 stages) to keep more bytes in flight.
 #include "common.cuh"
 
 namespace {
@@ -24,13 +30,11 @@ using namespace bg;
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int STAGES = 4;
-constexpr int A_BYTES = 2 * BM * BK * 2;    // room for two row tiles, 32 KB
-constexpr int B_MAX_ROWS = 160;
-constexpr int B_BYTES = B_MAX_ROWS * BK * 2;  // 20 KB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int RING_BYTES = STAGES * STAGE_BYTES;   // 208 KB; also holds the fp32 partial (<= 2*128*160*4 = 160 KB)
+constexpr int MAX_STAGES = 8;
+constexpr int TILE_BYTES = BM * BK * 2;     // one 128-row activation tile of a stage, 16 KB
+constexpr int RING_BYTES = 208 * 1024;      // the TMA ring; after it has drained, the reduction slots
 constexpr int SMEM_BYTES = RING_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int SLOT_BYTES = BM * 16;         // 4 fp32 columns of 128 rows
 constexpr int THREADS = 192;
 constexpr int ACC_STRIDE = 256;             // TMEM columns between the two row-tile accumulators
 
@@ -40,6 +44,8 @@ struct SkinnyParams {
     int row_tiles;                // 1 or 2
     int bn;                       // weight rows per tile = MMA N (plain: 128; GeGLU: 2 * half)
     int half;                     // GeGLU: gate rows per tile (= output columns per tile)
+    int stages, stage_bytes;      // ring depth and bytes per stage (row_tiles * 16 KB + bn * 128)
+    int max_units;                // 8-column output units a CTA may own in the reduction
     int64_t ldo;
     __nv_bfloat16* out;
     int32_t* status;
@@ -50,10 +56,9 @@ __device__ __forceinline__ uint32_t cluster_nctarank() {
     asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
     return r;
 }
-__device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_addr) {
-    float v;
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr));
-    return v;
+__device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, const uint32_t* v) {
+    asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};"
+                 ::"r"(cluster_addr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]) : "memory");
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -62,10 +67,10 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + RING_BYTES);
-    uint64_t* full = bars;                 // [STAGES]
-    uint64_t* empty = bars + STAGES;       // [STAGES]
-    uint64_t* acc_full = bars + 2 * STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+    uint64_t* full = bars;                     // [stages]
+    uint64_t* empty = bars + MAX_STAGES;       // [stages]
+    uint64_t* acc_full = bars + 2 * MAX_STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * MAX_STAGES + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -82,7 +87,7 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < p.stages; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
@@ -99,7 +104,6 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    float* partial = reinterpret_cast<float*>(smem);     // [row_tile][column][row] once the ring has drained
 
     const int part = warp & 3;
     const int row_in_tile = part * 32 + lane;
@@ -128,18 +132,18 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             const int w0 = p.epilogue == 1 ? tile * p.half : tile * p.bn;
             for (int kb = kb_lo; kb < kb_hi; ++kb) {
                 if (!mbar_wait(&empty[stage], phase ^ 1, ab, 301)) break;
-                uint8_t* sa = smem + stage * STAGE_BYTES;
-                uint8_t* sb = sa + A_BYTES;
+                uint8_t* sa = smem + stage * p.stage_bytes;
+                uint8_t* sb = sa + p.row_tiles * TILE_BYTES;
                 mbar_expect_tx(&full[stage], uint32_t(p.row_tiles * BM + p.bn) * BK * 2);
                 for (int t = 0; t < p.row_tiles; ++t)
-                    tma_load_2d(sa + t * (BM * BK * 2), &map_a, &full[stage], kb * BK, t * BM);
+                    tma_load_2d(sa + t * TILE_BYTES, &map_a, &full[stage], kb * BK, t * BM);
                 if (p.epilogue == 1) {
                     tma_load_2d(sb, &map_w, &full[stage], kb * BK, w0);
                     tma_load_2d(sb + p.half * BK * 2, &map_w, &full[stage], kb * BK, p.n + w0);
                 } else {
                     tma_load_2d(sb, &map_w, &full[stage], kb * BK, w0);
                 }
-                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                if (++stage == p.stages) { stage = 0; phase ^= 1; }
             }
         }
     } else if (warp == 1) {
@@ -152,51 +156,38 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             for (int kb = kb_lo; kb < kb_hi && ok; ++kb) {
                 if (!mbar_wait(&full[stage], phase, ab, 302)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
-                const uint32_t sb = sa + A_BYTES;
+                const uint32_t sa = smem_u32(smem + stage * p.stage_bytes);
+                const uint32_t sb = sa + p.row_tiles * TILE_BYTES;
                 for (int t = 0; t < p.row_tiles; ++t) {
 #pragma unroll
                     for (int kk = 0; kk < BK / 16; ++kk) {
-                        uint64_t da = smem_desc_sw128(sa + t * (BM * BK * 2) + kk * 32, 16, 1024);
+                        uint64_t da = smem_desc_sw128(sa + t * TILE_BYTES + kk * 32, 16, 1024);
                         uint64_t db = smem_desc_sw128(sb + kk * 32, 16, 1024);
                         mma_bf16_ss(tmem_base + t * ACC_STRIDE, da, db, idesc, (kb != kb_lo) || kk != 0);
                     }
                 }
                 mma_commit(&empty[stage]);
-                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                if (++stage == p.stages) { stage = 0; phase ^= 1; }
             }
             if (ok) mma_commit(acc_full);
         }
     } else {
-        // ------------------------------------------------------------ epilogue part 1 (warps 2..5)
-        if (mbar_wait(acc_full, 0, ab, 303)) {
+        // ------------------------------------------------------------ epilogue without a split (warps 2..5)
+        if (mbar_wait(acc_full, 0, ab, 303) && ks == 1) {
             tc_fence_after();
             for (int t = 0; t < p.row_tiles; ++t) {
                 const uint32_t taddr = tmem_base + (uint32_t(part * 32) << 16) + t * ACC_STRIDE;
                 const int row = t * BM + row_in_tile;
-                if (ks == 1) {
-                    // no split: straight from tensor memory to the output
-                    for (int u = 0; u < units; u += 4) {
-                        uint32_t a[32], b[32];
-                        tmem_ld32(taddr + u * 8, a);
-                        if (p.epilogue == 1) tmem_ld32(taddr + p.half + u * 8, b);
-                        tmem_wait_ld();
+                for (int u = 0; u < units; u += 4) {
+                    uint32_t a[32], b[32];
+                    tmem_ld32(taddr + u * 8, a);
+                    if (p.epilogue == 1) tmem_ld32(taddr + p.half + u * 8, b);
+                    tmem_wait_ld();
 #pragma unroll
-                        for (int v = 0; v < 4; ++v)
-                            if (u + v < units)
-                                store8(row, u + v, reinterpret_cast<const float*>(a) + v * 8,
-                                       reinterpret_cast<const float*>(b) + v * 8);
-                    }
-                } else {
-                    // park the fp32 partial column-major: lanes write consecutive rows, no bank conflicts
-                    float* dst = partial + (size_t)t * p.bn * BM + row_in_tile;
-                    for (int c = 0; c < p.bn; c += 32) {
-                        uint32_t r[32];
-                        tmem_ld32(taddr + c, r);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) dst[(size_t)(c + i) * BM] = __uint_as_float(r[i]);
-                    }
+                    for (int v = 0; v < 4; ++v)
+                        if (u + v < units)
+                            store8(row, u + v, reinterpret_cast<const float*>(a) + v * 8,
+                                   reinterpret_cast<const float*>(b) + v * 8);
                 }
             }
         }
@@ -207,41 +198,60 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
 
     if (ks > 1) {
         // ------------------------------------------------------------ split-K reduction over the cluster
-        cluster_sync();                                   // every CTA's partial is parked and visible
+        // Slot of 4 columns x 128 rows: [source rank][row tile][plane: gate|up][unit][half unit][row][4 floats].
+        const int planes = p.epilogue == 1 ? 2 : 1;
+        auto slot = [&](int src, int t, int plane, int ul, int h) {
+            return (uint32_t)((((((src * p.row_tiles + t) * planes + plane) * p.max_units + ul) * 2 + h) * SLOT_BYTES) +
+                              row_in_tile * 16);
+        };
+        const uint32_t base = smem_u32(smem);
+        cluster_sync();                                   // every ring of the cluster has drained
+        if (warp >= 2 && !ab.raised()) {
+            tc_fence_after();
+            for (int t = 0; t < p.row_tiles; ++t) {
+                const uint32_t taddr = tmem_base + (uint32_t(part * 32) << 16) + t * ACC_STRIDE;
+                for (int c = 0; c < p.bn; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(taddr + c, r);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        const int col = c + q * 4;
+                        const int plane = (p.epilogue == 1 && col >= p.half) ? 1 : 0;
+                        const int cl = col - plane * p.half;
+                        const int unit = cl >> 3;
+                        const int owner = ((unit + 1) * ks - 1) / units;      // the rank whose slice holds `unit`
+                        const int ul = unit - owner * units / ks;
+                        st_cluster_v4(map_to_cta(base + slot(rank, t, plane, ul, (cl >> 2) & 1), (uint32_t)owner),
+                                      r + q * 4);
+                    }
+                }
+            }
+        }
+        cluster_sync();                                   // every slot of this CTA has been written
         if (warp >= 2 && !ab.raised()) {
             const int u_lo = rank * units / ks, u_hi = (rank + 1) * units / ks;
-            const uint32_t base = smem_u32(partial);
             for (int t = 0; t < p.row_tiles; ++t) {
                 const int row = t * BM + row_in_tile;
                 for (int u = u_lo; u < u_hi; ++u) {
-                    // all loads of a unit are issued before the first add; the sum runs in rank order
-                    float va[8][8], vb[8][8];
-#pragma unroll
-                    for (int src = 0; src < 8; ++src) {
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            const uint32_t off = (uint32_t)(((t * p.bn + u * 8 + e) * BM + row_in_tile) * 4);
-                            va[src][e] = src < ks ? ld_cluster_f32(map_to_cta(base + off, (uint32_t)src)) : 0.f;
-                            vb[src][e] = (src < ks && p.epilogue == 1)
-                                ? ld_cluster_f32(map_to_cta(base + off + (uint32_t)(p.half * BM * 4), (uint32_t)src)) : 0.f;
-                        }
-                    }
                     float a[8], b[8];
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        a[e] = va[0][e];
-                        b[e] = vb[0][e];
+                    for (int e = 0; e < 8; ++e) a[e] = b[e] = 0.f;
+                    for (int src = 0; src < ks; ++src) {           // rank order: the sum is deterministic
 #pragma unroll
-                        for (int src = 1; src < 8; ++src) {
-                            a[e] += va[src][e];
-                            b[e] += vb[src][e];
+                        for (int h = 0; h < 2; ++h) {
+                            const float4 va = *reinterpret_cast<const float4*>(smem + slot(src, t, 0, u - u_lo, h));
+                            a[h * 4 + 0] += va.x; a[h * 4 + 1] += va.y; a[h * 4 + 2] += va.z; a[h * 4 + 3] += va.w;
+                            if (p.epilogue == 1) {
+                                const float4 vb = *reinterpret_cast<const float4*>(smem + slot(src, t, 1, u - u_lo, h));
+                                b[h * 4 + 0] += vb.x; b[h * 4 + 1] += vb.y; b[h * 4 + 2] += vb.z; b[h * 4 + 3] += vb.w;
+                            }
                         }
                     }
                     store8(row, u, a, b);
                 }
             }
         }
-        cluster_sync();                                   // nobody leaves while a peer still reads its partial
     }
 
     // ---------------------------------------------------------------- teardown
@@ -331,13 +341,20 @@ extern "C" int bg_gemm_bf16_skinny(const void* a, int64_t lda, const void* w, in
         configured = true;
     }
 
+    p.stage_bytes = p.row_tiles * TILE_BYTES + ((p.bn * BK * 2 + 1023) & ~1023);
+    p.stages = RING_BYTES / p.stage_bytes < MAX_STAGES ? RING_BYTES / p.stage_bytes : MAX_STAGES;
+
     // Split K over 1-8 CTAs of a cluster: fewest waves first, then the shortest K slice; a split pays
-    // for its reduction with about 4 K-blocks of time, every CTA for about 8 of fixed cost.
+    // for its reduction with about 4 K-blocks of time, every CTA for about 8 of fixed cost.  The
+    // reduction slots of a CTA (one per source rank) must fit the drained ring.
     const int kblocks = (int)(k / BK);
+    const int units = (epilogue == 1 ? p.half : p.bn) / 8;
     int best_ks = 1;
     int64_t best_cost = INT64_MAX;
     for (int ks = 1; ks <= 8; ++ks) {
         if (ks > kblocks) break;
+        const int max_units = (units + ks - 1) / ks;
+        if (ks > 1 && ks * p.row_tiles * (epilogue == 1 ? 2 : 1) * max_units * 2 * SLOT_BYTES > RING_BYTES) continue;
         const int resident = max_clusters(ks);
         const int waves = (tiles + resident - 1) / resident;
         const int64_t cost = int64_t(waves) * ((kblocks + ks - 1) / ks + 8 + (ks > 1 ? 4 : 0));
@@ -357,6 +374,8 @@ extern "C" int bg_gemm_bf16_skinny(const void* a, int64_t lda, const void* w, in
     if (rc) return rc;
     p.status = bg_status_word();
     if (!p.status) return BG_ERR_DRIVER;
+
+    p.max_units = (units + best_ks - 1) / best_ks;
 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(tiles * best_ks));

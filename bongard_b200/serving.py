@@ -102,6 +102,7 @@ class _Inputs:
     pack: DevicePack
     offsets: dict           # window -> offset of its plan inside ints
     plan_tiles: int
+    tail: int = 0           # offset of the free-form tail (readout rows, question offsets)
     copied: object = None   # event after the last host-to-device copies of the mirror
 
 
@@ -155,7 +156,8 @@ class Predictor:
         device = self.engine.device
         plan_tiles = tokens // self.tile_tokens + 2
         plan_ints = plan_tiles * 8 + 2 * tokens
-        n_ints = tokens + len(self.windows) * plan_ints
+        tail = tokens + len(self.windows) * plan_ints       # readout rows and question offsets ride along
+        n_ints = tail + 3 * tokens + 1
         host_ids = torch.zeros(tokens, dtype=torch.int64).pin_memory()
         host_ints = torch.zeros(n_ints, dtype=torch.int32).pin_memory()
         ids, ints = host_ids.to(device), host_ints.to(device)
@@ -166,9 +168,9 @@ class Predictor:
             plans[w] = ops.HostPlan(np.zeros(plan_ints, dtype=np.int32), tokens, plan_tiles, 0, rows).view(
                 ints[offsets[w]:offsets[w] + plan_ints])
         pack = DevicePack(ids, ints[:tokens], self.keys, plans)
-        return _Inputs(tokens, host_ids, host_ints, ids, ints, pack, offsets, plan_tiles)
+        return _Inputs(tokens, host_ids, host_ints, ids, ints, pack, offsets, plan_tiles, tail)
 
-    def _fill(self, inp, sequences, *, state_length=None):
+    def _fill(self, inp, sequences, *, state_length=None, tail=None):
         """Write token ids, positions and padded attention plans of `sequences` (+ one pad
         segment up to the bucket size) into the pinned mirror and start the two copies."""
         s = self.engine.shape
@@ -196,6 +198,8 @@ class Predictor:
             hp = ops.make_host_plan(lengths, w, group=self.group, owners=owners, state_lengths=state_lengths,
                                     head_dim=s.head_dim).padded(inp.tokens, inp.plan_tiles)
             ints[offset:offset + hp.packed.size] = hp.packed
+        if tail is not None:
+            ints[inp.tail:inp.tail + len(tail)] = tail
         inp.ids.copy_(inp.host_ids, non_blocking=True)
         inp.ints.copy_(inp.host_ints, non_blocking=True)
         inp.copied = torch.cuda.Event()
@@ -243,7 +247,8 @@ class Predictor:
     # ------------------------------------------------------------------ the request
     @torch.inference_mode()
     def logits(self, request):
-        """Candidate logits fp32 [sum of candidates] on the device, question order."""
+        """(candidate logits fp32 [sum of candidates] on the device in question order, device
+        offsets int32 [questions + 1] into them, the same offsets as a host list)."""
         e = self.engine
         n_state = len(request.state)
         sb = _bucket(n_state, self.state_bucket, self.fine_bucket)
@@ -268,31 +273,28 @@ class Predictor:
         total = sum(len(q.tokens) for q in questions)
         tb = _bucket(total, self.question_bucket, self.fine_bucket)
         inp, stage = self._decoder(sb, tb)
-        self._fill(inp, [q.tokens for q in questions], state_length=n_state)
-        hidden = self._run(stage)
-        cand, dec, offset = [], [], 0
+        cand, dec, sizes, offset = [], [], [0], 0
         for q in questions:
             cand.extend(offset + p for p in q.candidate_positions)
             dec.extend([offset + q.decision_position] * len(q.candidate_positions))
+            sizes.append(sizes[-1] + len(q.candidate_positions))
             offset += len(q.tokens)
-        rows = torch.tensor(cand + dec, dtype=torch.int32).pin_memory().to(e.device, non_blocking=True)
         n = len(cand)
-        return ops.judgment_head(hidden, rows[:n], rows[n:], e.head_w, e.head_c, e.head_g)
+        # readout rows and per-question candidate offsets travel in the same copy as the plans
+        self._fill(inp, [q.tokens for q in questions], state_length=n_state, tail=cand + dec + sizes)
+        hidden = self._run(stage)
+        rows = inp.ints[inp.tail:inp.tail + 2 * n + len(sizes)]
+        logits = ops.judgment_head(hidden, rows[:n], rows[n:2 * n], e.head_w, e.head_c, e.head_g)
+        return logits, rows[2 * n:], sizes
 
     @torch.inference_mode()
     def predict(self, request, temperature=1.0):
         """{question id: float64 probabilities [K]} with one device-to-host read
         (bongard/inference.py:305-321)."""
-        sizes = [len(q.candidate_positions) for q in request.questions.values()]
-        offsets = torch.tensor(np.concatenate(([0], np.cumsum(sizes))), dtype=torch.int32).pin_memory()
-        logits = self.logits(request)
-        probs = ops.candidate_softmax(logits, offsets.to(self.engine.device, non_blocking=True), temperature).cpu()
+        logits, offsets, sizes = self.logits(request)
+        probs = ops.candidate_softmax(logits, offsets, temperature).cpu()
         ops.read_status()
-        out, cursor = {}, 0
-        for qid, n in zip(request.questions, sizes):
-            out[qid] = probs[cursor:cursor + n]
-            cursor += n
-        return out
+        return {qid: probs[lo:hi] for qid, lo, hi in zip(request.questions, sizes, sizes[1:])}
 
     def state_cache_info(self):
         return self.cache.info()
