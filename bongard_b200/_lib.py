@@ -36,6 +36,8 @@ SIGNATURES = {
     'bg_attention_tile_rows': ([INT], INT),
     'bg_varlen_attention': ([P, I64, I64, P, P, I64, I64, P, P, I64, I64, P, P, P, I32, P, P, I64, I64, I64, INT, INT, INT,
                              F32, P], INT),
+    'bg_varlen_attention_backward': ([P, I64, I64, P, P, I64, I64, P, P, I64, I64, P, P, I64, I64, P, P, P, P, P, P, P,
+                                      P, I32, P, I32, P, P, I64, I64, I64, INT, INT, INT, F32, P], INT),
     'bg_judgment_head': ([P, I64, P, P, P, P, P, P, I64, I64, INT, P], INT),
     'bg_candidate_softmax': ([P, P, P, I64, F64, P], INT),
 }

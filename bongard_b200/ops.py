@@ -222,6 +222,8 @@ class AttentionPlan:
     n_tiles: int
     pairs: int               # visible (query, key) pairs, for FLOP accounting
     tile_rows: int = 128     # query rows (tokens x GQA group) a tile may hold
+    kv_tiles: torch.Tensor = None    # int32 [n_kv_tiles, 8], key tiles of the backward passes (optional)
+    n_kv_tiles: int = 0
 
 
 def plan_rows(lengths, window, *, decoder):
@@ -257,6 +259,7 @@ class HostPlan:
     n_tiles: int
     pairs: int
     tile_rows: int = 128
+    n_kv_tiles: int = 0      # key tiles for the backward passes, appended after row_hi
 
     def to(self, device):
         dev = torch.from_numpy(self.packed).to(device, non_blocking=True)
@@ -277,8 +280,12 @@ class HostPlan:
 
     def view(self, dev):
         n8, t = self.n_tiles * 8, self.tokens
-        return AttentionPlan(dev[:n8].view(-1, 8), dev[n8:n8 + t], dev[n8 + t:n8 + 2 * t], t, self.n_tiles, self.pairs,
+        plan = AttentionPlan(dev[:n8].view(-1, 8), dev[n8:n8 + t], dev[n8 + t:n8 + 2 * t], t, self.n_tiles, self.pairs,
                              self.tile_rows)
+        if self.n_kv_tiles:
+            plan.kv_tiles = dev[n8 + 2 * t:n8 + 2 * t + self.n_kv_tiles * 8].view(-1, 8)
+            plan.n_kv_tiles = self.n_kv_tiles
+        return plan
 
 
 def tile_rows(head_dim):
@@ -286,7 +293,54 @@ def tile_rows(head_dim):
     return _lib.load().bg_attention_tile_rows(int(head_dim)) if head_dim else 128
 
 
-def make_host_plan(lengths, window, *, group, owners=None, state_lengths=None, head_dim=None):
+def make_host_kv_tiles(lengths, window, *, owners=None, state_lengths=None, keys_per_tile=128):
+    """Key tiles for the backward passes (host arithmetic on lengths only): int32 [n, 8] rows
+    {k_start, k_count, q_lo, q_hi, is_state, 0, 0, 0}.
+
+    An own-key tile holds up to 128 consecutive keys of one segment; [q_lo, q_hi) are the query
+    tokens whose key range meets it (which of them see which key is decided per pair from the
+    row ranges).  A state tile holds keys of one owner's state; its queries are all tokens of the
+    owner's questions, which therefore have to be consecutive in the pack.  Heaviest first."""
+    lengths = [int(n) for n in lengths]
+    decoder = owners is not None
+    lo, hi = plan_rows(lengths, window, decoder=decoder)
+    tiles = []
+    offset = 0
+    for n in lengths:
+        if n:
+            seg_lo, seg_hi = lo[offset:offset + n], hi[offset:offset + n]
+            for k0 in range(offset, offset + n, keys_per_tile):
+                count = min(keys_per_tile, offset + n - k0)
+                q_lo = offset + int(np.searchsorted(seg_hi, k0, side='right'))       # first token with hi > k0
+                q_hi = offset + int(np.searchsorted(seg_lo, k0 + count, side='left'))  # first token with lo >= end
+                tiles.append((k0, count, q_lo, max(q_lo, q_hi), 0))
+        offset += n
+    if decoder:
+        state_offsets = np.concatenate(([0], np.cumsum(np.asarray(state_lengths, dtype=np.int64))))
+        runs, offset = [], 0
+        for n, owner in zip(lengths, owners):
+            if n:
+                if runs and runs[-1][2] == owner:
+                    runs[-1][1] = offset + n
+                else:
+                    runs.append([offset, offset + n, owner])
+            offset += n
+        seen = set()
+        for start, end, owner in runs:
+            if owner in seen:
+                raise ValueError('the questions of one owner must be consecutive in the pack (backward pass)')
+            seen.add(owner)
+            base, length = int(state_offsets[owner]), int(state_lengths[owner])
+            for k0 in range(0, length, keys_per_tile):
+                tiles.append((base + k0, min(keys_per_tile, length - k0), start, end, 1))
+    if not tiles:
+        return np.zeros((0, 8), dtype=np.int32)
+    out = np.zeros((len(tiles), 8), dtype=np.int32)
+    out[:, :5] = np.asarray(tiles, dtype=np.int64)
+    return out[np.argsort(-(out[:, 3] - out[:, 2]), kind='stable')]
+
+
+def make_host_plan(lengths, window, *, group, owners=None, state_lengths=None, head_dim=None, backward=False):
     """Tile a pack of segments for the attention kernel (host arithmetic on lengths only).
 
     Encoder (owners None): tiles never cross a segment.  Decoder: consecutive questions of the
@@ -328,16 +382,21 @@ def make_host_plan(lengths, window, *, group, owners=None, state_lengths=None, h
     tiles = np.stack([q_start, q_count, own_lo, own_hi, lo_max, hi_min, run[which, 2], run[which, 3]], axis=1)
     work = run[which, 3] + own_hi - own_lo
     tiles = tiles[np.argsort(-work, kind='stable')].astype(np.int32)
-    packed = np.concatenate([tiles.reshape(-1), lo.astype(np.int32), hi.astype(np.int32)])
+    parts = [tiles.reshape(-1), lo.astype(np.int32), hi.astype(np.int32)]
+    n_kv = 0
+    if backward:
+        kv = make_host_kv_tiles(lengths, window, owners=owners, state_lengths=state_lengths)
+        parts.append(kv.reshape(-1))
+        n_kv = kv.shape[0]
     pairs = int((hi - lo).sum())
     if decoder:
         pairs += int(sum(n * state_lengths[o] for n, o in zip(lengths, owners)))
-    return HostPlan(packed, total, tiles.shape[0], pairs, rows)
+    return HostPlan(np.concatenate(parts), total, tiles.shape[0], pairs, rows, n_kv)
 
 
-def make_plan(lengths, window, device, *, group, owners=None, state_lengths=None, head_dim=None):
+def make_plan(lengths, window, device, *, group, owners=None, state_lengths=None, head_dim=None, backward=False):
     return make_host_plan(lengths, window, group=group, owners=owners, state_lengths=state_lengths,
-                          head_dim=head_dim).to(device)
+                          head_dim=head_dim, backward=backward).to(device)
 
 
 def varlen_attention(q, k, v, plan, scale, cross=None, return_lse=False):
@@ -376,6 +435,76 @@ def varlen_attention(q, k, v, plan, scale, cross=None, return_lse=False):
     if timer is not None:
         timer.stop(begin, 4 * d * hq * plan.pairs)
     return (out, lse) if return_lse else out
+
+
+def varlen_attention_backward(q, k, v, plan, scale, out, lse, dout, cross=None):
+    """Gradients of varlen_attention: (dq, dk, dv) or (dq, dk, dv, dck, dcv) with a state prefix.
+    `plan` must carry key tiles (make_plan(..., backward=True)); `out`, `lse` are the forward's
+    results, `dout` [T, Hq*D] or [T, Hq, D] the gradient of `out`."""
+    lib = _lib.load()
+    for t, name in ((q, 'q'), (k, 'k'), (v, 'v'), (out, 'out'), (dout, 'dout')):
+        _need(t, name)
+    _need(lse, 'lse', torch.float32)
+    tq, hq, d = q.shape
+    tk, hkv = k.shape[0], k.shape[1]
+    if plan.tokens != tq or plan.kv_tiles is None:
+        raise ValueError('the plan must match q and carry key tiles (make_plan(..., backward=True))')
+    if k.stride() != v.stride() or k.shape != v.shape:
+        raise ValueError('k and v must share shape and strides')
+    out = out.reshape(tq, hq * d)
+    if not out.is_contiguous() or not lse.is_contiguous() or lse.shape != (hq, tq):
+        raise ValueError('out must be contiguous [T, Hq*D] and lse contiguous [Hq, T]')
+    dout = dout.reshape(tq, hq, d)
+    if dout.stride(2) != 1:
+        dout = dout.contiguous()
+    ck = cv = dck = dcv = None
+    ts = ldc = hsc = 0
+    if cross is not None:
+        ck, cv = cross
+        _need(ck, 'cross keys'), _need(cv, 'cross values')
+        if ck.shape != cv.shape or ck.stride() != cv.stride() or ck.shape[1:] != k.shape[1:] or ck.stride(2) != 1:
+            raise ValueError('cross keys/values must be [S, kv_heads, D] with equal strides')
+        ts, ldc, hsc = ck.shape[0], ck.stride(0), ck.stride(1)
+        dck = torch.zeros((ts, hkv, d), device=q.device, dtype=BF16)    # states without a question keep zero
+        dcv = torch.zeros((ts, hkv, d), device=q.device, dtype=BF16)
+    dq = torch.empty((tq, hq, d), device=q.device, dtype=BF16)
+    dk = torch.empty((tk, hkv, d), device=q.device, dtype=BF16)
+    dv = torch.empty((tk, hkv, d), device=q.device, dtype=BF16)
+    delta = torch.empty((hq, tq), device=q.device, dtype=torch.float32)
+    _lib.check(lib.bg_varlen_attention_backward(
+        _ptr(q), q.stride(0), q.stride(1), _ptr(k), _ptr(v), k.stride(0), k.stride(1), _ptr(ck), _ptr(cv), ldc, hsc,
+        _ptr(out), _ptr(dout), dout.stride(0), dout.stride(1), _ptr(lse), _ptr(delta), _ptr(dq), _ptr(dk), _ptr(dv),
+        _ptr(dck), _ptr(dcv), _ptr(plan.tiles), plan.n_tiles, _ptr(plan.kv_tiles), plan.n_kv_tiles,
+        _ptr(plan.row_lo), _ptr(plan.row_hi), tq, tk, ts, hq, hkv, d, float(scale), _stream()),
+        'bg_varlen_attention_backward')
+    return (dq, dk, dv) if cross is None else (dq, dk, dv, dck, dcv)
+
+
+class _VarlenAttention(torch.autograd.Function):
+    """out = varlen_attention(q, k, v[, state k, v]) with the tensor-core backward."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, ck, cv, plan, scale):
+        cross = None if ck is None else (ck, cv)
+        out, lse = varlen_attention(q, k, v, plan, scale, cross, return_lse=True)
+        ctx.save_for_backward(q, k, v, ck, cv, out, lse)
+        ctx.plan, ctx.scale = plan, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, ck, cv, out, lse = ctx.saved_tensors
+        cross = None if ck is None else (ck, cv)
+        grads = varlen_attention_backward(q, k, v, ctx.plan, ctx.scale, out, lse, dout, cross)
+        dq, dk, dv = grads[:3]
+        dck, dcv = (grads[3], grads[4]) if cross is not None else (None, None)
+        return dq, dk, dv, dck, dcv, None, None
+
+
+def varlen_attention_autograd(q, k, v, plan, scale, cross=None):
+    """varlen_attention that records its backward (plan built with backward=True)."""
+    ck, cv = cross if cross is not None else (None, None)
+    return _VarlenAttention.apply(q, k, v, ck, cv, plan, scale)
 
 
 # --------------------------------------------------------------------------------------

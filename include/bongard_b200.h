@@ -160,6 +160,28 @@ int bg_varlen_attention(const void* q, int64_t ldq, int64_t hsq, const void* k, 
                         int32_t n_tiles, const int32_t* row_lo, const int32_t* row_hi, int64_t tq, int64_t tk,
                         int64_t ts, int q_heads, int kv_heads, int head_dim, float scale, void* stream);
 
+/* Backward of bg_varlen_attention: dq [tq, q_heads, D], dk, dv [tk, kv_heads, D] and, with a state
+ * prefix, dck, dcv [ts, kv_heads, D] (all contiguous bf16, every row written once, no atomics).
+ *   out [tq, q_heads * D] and lse fp32 [q_heads, tq] are the forward's results; dout [tq, q_heads, D]
+ *   with token stride ldd and head stride hsd; delta fp32 [q_heads, tq] is scratch (rowsum(dout * out)).
+ *   q_tiles / row_lo / row_hi as in the forward; kv_tiles int32 [n_kv_tiles, 8] = {k_start, k_count,
+ *   q_lo, q_hi, is_state, 0, 0, 0}: up to 128 consecutive keys (of k/v, or of ck/cv when is_state) and
+ *   the query tokens [q_lo, q_hi) that may see them; state tiles are seen by all of those tokens, own
+ *   tiles by a token t iff row_lo[t] <= key < row_hi[t].  Every key of k/v needs exactly one tile.
+ * Three passes of one kernel (dQ per query tile; dK and dV per key tile) recompute the probabilities
+ * from lse on the tensor cores.
+ * Replaces bongard/flash_varlen.py:30-39 _backward (op bongard::flash_packed_backward) and 85-105
+ * _prefix_backward (op bongard::flash_prefix_backward, without the gathered keys and the index_add_
+ * scatter of their gradients). */
+int bg_varlen_attention_backward(const void* q, int64_t ldq, int64_t hsq, const void* k, const void* v, int64_t ldkv,
+                                 int64_t hskv, const void* ck, const void* cv, int64_t ldc, int64_t hsc,
+                                 const void* out, const void* dout, int64_t ldd, int64_t hsd, const float* lse,
+                                 float* delta, void* dq, void* dk, void* dv, void* dck, void* dcv,
+                                 const int32_t* q_tiles, int32_t n_q_tiles, const int32_t* kv_tiles,
+                                 int32_t n_kv_tiles, const int32_t* row_lo, const int32_t* row_hi, int64_t tq,
+                                 int64_t tk, int64_t ts, int q_heads, int kv_heads, int head_dim, float scale,
+                                 void* stream);
+
 /* logits[c] = w . h + (C h) . (G g) / sqrt(rank) with h = hidden[cand_rows[c]], g = hidden[dec_rows[c]].
  * Replaces bongard/model.py:85-95 JudgmentHead.forward as called by 520-529 score_readouts. */
 int bg_judgment_head(const void* hidden, int64_t ldh, const int32_t* cand_rows, const int32_t* dec_rows,
