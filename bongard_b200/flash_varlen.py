@@ -7,9 +7,12 @@ tensors in [1, heads, tokens, D] order.  Two differences, both extensions:
   - the decoder path never materialises per-question copies of the state K/V
     (bongard/flash_varlen.py:61-63 `_prefix_keys`): the kernel streams the owner's state as a
     key prefix.
-The two forward custom ops keep the reference's output contract
-(out shaped like q [T, Hq, D], lse [Hq, T] fp32; bongard/flash_varlen.py:25-27, 80-82).
-They are inference ops: no autograd formula is registered.
+The custom ops keep the reference's contracts: forwards return (out shaped like q [T, Hq, D],
+lse [Hq, T] fp32; bongard/flash_varlen.py:25-27, 80-82), `flash_packed_backward` returns
+(dq, dk, dv) and `flash_prefix_backward` (dq, dk, dv, dck, dcv) (bongard/flash_varlen.py:30-39,
+85-105), and the forwards carry the same autograd registration (bongard/flash_varlen.py:46-58,
+113-126), so `attention` is differentiable: gradients come from the tensor-core backward
+kernel, for active windows too.
 """
 
 from __future__ import annotations
@@ -19,15 +22,15 @@ import torch
 from . import ops
 
 
-def _plan_from_cu(cu_q, window, group, device, *, decoder=False, cu_k=None, head_dim=None):
+def _plan_from_cu(cu_q, window, group, device, *, decoder=False, cu_k=None, head_dim=None, backward=False):
     """Attention plan from cu_seqlens tensors (synchronises: the custom-op surface carries no host lengths)."""
     lengths = (cu_q[1:] - cu_q[:-1]).tolist()
     if not decoder:
-        return ops.make_plan(lengths, window, device, group=group, head_dim=head_dim)
+        return ops.make_plan(lengths, window, device, group=group, head_dim=head_dim, backward=backward)
     key_lengths = (cu_k[1:] - cu_k[:-1]).tolist()
     state_lengths = [k - n for k, n in zip(key_lengths, lengths)]
     return ops.make_plan(lengths, window, device, group=group, owners=list(range(len(lengths))),
-                         state_lengths=state_lengths, head_dim=head_dim)
+                         state_lengths=state_lengths, head_dim=head_dim, backward=backward)
 
 
 def flash_packed_forward(q, k, v, cuq, cuk, scale, causal):
@@ -51,15 +54,77 @@ def flash_prefix_forward(q, k, v, ck, cv, indices, cuq, cuk, scale):
     return out.view(q.shape), lse
 
 
+def flash_packed_backward(q, k, v, cuq, cuk, out, lse, dout, scale, causal):
+    """Op `bongard::flash_packed_backward` (bongard/flash_varlen.py:30-39): (dq, dk, dv)."""
+    if causal:
+        raise ValueError('causal packed attention goes through flash_prefix_backward (state-prefix keys)')
+    plan = _plan_from_cu(cuq, None, q.shape[1] // k.shape[1], q.device, head_dim=q.shape[-1], backward=True)
+    return ops.varlen_attention_backward(q, k, v, plan, scale, out, lse, dout)
+
+
+def flash_prefix_backward(q, k, v, ck, cv, indices, cuq, cuk, out, lse, dout, scale):
+    """Op `bongard::flash_prefix_backward` (bongard/flash_varlen.py:85-105): (dq, dk, dv, dck, dcv);
+    the state gradients are written by the key-tile passes directly, so there is no gathered
+    gradient to scatter back with index_add_."""
+    plan = _plan_from_cu(cuq, None, q.shape[1] // k.shape[1], q.device, decoder=True, cu_k=cuk, head_dim=q.shape[-1],
+                         backward=True)
+    return ops.varlen_attention_backward(q, k, v, plan, scale, out, lse, dout, (ck, cv))
+
+
 def _register():
-    """Expose the two forwards as torch custom ops under the reference's names when that
-    namespace is still free (the reference registers the same names if it is imported)."""
+    """Expose the forwards and backwards as torch custom ops under the reference's names, with the
+    reference's autograd registration, when that namespace is still free (the reference registers
+    the same names if it is imported)."""
     try:
-        torch.library.custom_op('bongard::flash_packed_forward', mutates_args=())(_packed_op)
-        torch.library.custom_op('bongard::flash_prefix_forward', mutates_args=())(_prefix_op)
-        return True
+        packed = torch.library.custom_op('bongard::flash_packed_forward', mutates_args=())(_packed_op)
+        prefix = torch.library.custom_op('bongard::flash_prefix_forward', mutates_args=())(_prefix_op)
+        packed_bwd = torch.library.custom_op('bongard::flash_packed_backward', mutates_args=())(_packed_bwd_op)
+        prefix_bwd = torch.library.custom_op('bongard::flash_prefix_backward', mutates_args=())(_prefix_bwd_op)
     except Exception:   # already registered by the reference package
         return False
+    packed.register_fake(lambda q, k, v, cuq, cuk, scale, causal:
+                         (torch.empty_like(q), q.new_empty((q.shape[1], q.shape[0]), dtype=torch.float32)))
+    prefix.register_fake(lambda q, k, v, ck, cv, indices, cuq, cuk, scale:
+                         (torch.empty_like(q), q.new_empty((q.shape[1], q.shape[0]), dtype=torch.float32)))
+    packed_bwd.register_fake(lambda q, k, v, cuq, cuk, out, lse, dout, scale, causal:
+                             (torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)))
+    prefix_bwd.register_fake(lambda q, k, v, ck, cv, indices, cuq, cuk, out, lse, dout, scale:
+                             tuple(torch.empty_like(t) for t in (q, k, v, ck, cv)))
+
+    def packed_context(ctx, inputs, output):
+        q, k, v, cuq, cuk, ctx.scale, ctx.causal = inputs
+        out, lse = output
+        ctx.save_for_backward(q, k, v, cuq, cuk, out, lse)
+        ctx.mark_non_differentiable(lse)
+
+    def packed_grad(ctx, dout, ignored):
+        return (*packed_bwd(*ctx.saved_tensors, dout, ctx.scale, ctx.causal), None, None, None, None)
+
+    def prefix_context(ctx, inputs, output):
+        *tensors, ctx.scale = inputs
+        out, lse = output
+        ctx.save_for_backward(*tensors, out, lse)
+        ctx.mark_non_differentiable(lse)
+
+    def prefix_grad(ctx, dout, ignored):
+        return (*prefix_bwd(*ctx.saved_tensors, dout, ctx.scale), None, None, None, None)
+
+    packed.register_autograd(packed_grad, setup_context=packed_context)
+    prefix.register_autograd(prefix_grad, setup_context=prefix_context)
+    return True
+
+
+def _packed_bwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cuq: torch.Tensor, cuk: torch.Tensor,
+                   out: torch.Tensor, lse: torch.Tensor, dout: torch.Tensor, scale: float, causal: bool
+                   ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    return flash_packed_backward(q, k, v, cuq, cuk, out, lse, dout, scale, causal)
+
+
+def _prefix_bwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ck: torch.Tensor, cv: torch.Tensor,
+                   indices: torch.Tensor, cuq: torch.Tensor, cuk: torch.Tensor, out: torch.Tensor, lse: torch.Tensor,
+                   dout: torch.Tensor, scale: float
+                   ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    return flash_prefix_backward(q, k, v, ck, cv, indices, cuq, cuk, out, lse, dout, scale)
 
 
 def _packed_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cuq: torch.Tensor, cuk: torch.Tensor,
@@ -91,6 +156,10 @@ def attention(q, k, v, layout, scale, window, cross=None):
         if ck.stride() != cv.stride():
             ck, cv = cross[0][0].contiguous().transpose(0, 1), cross[1][0].contiguous().transpose(0, 1)
         cr = (ck, cv)
-    plan = layout.plan(window, q3.shape[1] // k3.shape[1], q3.shape[-1])
-    out = ops.varlen_attention(q3, k3, v3, plan, scale, cr)
+    group, head_dim = q3.shape[1] // k3.shape[1], q3.shape[-1]
+    needs_grad = torch.is_grad_enabled() and any(t.requires_grad for t in (q3, k3, v3) + (cr or ()))
+    if needs_grad:
+        out = ops.varlen_attention_autograd(q3, k3, v3, layout.plan(window, group, head_dim, backward=True), scale, cr)
+    else:
+        out = ops.varlen_attention(q3, k3, v3, layout.plan(window, group, head_dim), scale, cr)
     return out.view(q3.shape[0], q3.shape[1], q3.shape[2]).transpose(0, 1)[None]

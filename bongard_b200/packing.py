@@ -50,11 +50,13 @@ class PackedLayout:
         reach = window if self.decoder else (window + 1) // 2
         return None if max(self.lengths) <= reach else window
 
-    def plan(self, window, group, head_dim=None):
-        key = (self.effective_window(window), group, head_dim)
+    def plan(self, window, group, head_dim=None, backward=False):
+        """The attention plan of a window; `backward=True` adds the key tiles of the backward passes."""
+        key = (self.effective_window(window), group, head_dim, bool(backward))
         if key not in self.plans:
             self.plans[key] = ops.make_plan(self.lengths, key[0], self.positions.device, group=group,
-                                            owners=self.owners, state_lengths=self.state_lengths, head_dim=head_dim)
+                                            owners=self.owners, state_lengths=self.state_lengths, head_dim=head_dim,
+                                            backward=backward)
         return self.plans[key]
 
 

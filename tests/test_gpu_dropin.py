@@ -117,6 +117,61 @@ def test_custom_ops_keep_the_reference_contract():
         assert torch.equal(out2, out)
 
 
+def test_attention_surface_is_differentiable():
+    """flash_varlen.attention / packing.layout_attention record a backward (encoder with an active
+    window, decoder with a state prefix), and the custom ops carry the reference's autograd
+    registration (bongard/flash_varlen.py:46-58, 113-126)."""
+    hq, hkv, d, lengths, window = 4, 2, 64, [90, 37, 200], 64
+    t = sum(lengths)
+    g = torch.Generator().manual_seed(3)
+    q, k, v, dout = (torch.randn(t, h, d, generator=g).bfloat16() for h in (hq, hkv, hkv, hq))
+
+    def oracle(cross=None, owners=None, state_lengths=None, win=window):
+        leaves = [x.float().requires_grad_(True) for x in (q, k, v)] + [x.float().requires_grad_(True) for x in cross or ()]
+        out, _ = om.varlen_attention(*leaves[:3], lengths, 0.125, win, cross=tuple(leaves[3:]) or None, owners=owners,
+                                     state_lengths=state_lengths)
+        out.backward(dout.float())
+        return [x.grad for x in leaves]
+
+    def close(got, want):
+        got, want = got.float().cpu(), want.float()
+        assert float((got - want).abs().max()) < 2e-2 * (float(want.abs().max()) + 1e-6)
+
+    to = lambda x: x.to(DEV).transpose(0, 1)[None].contiguous().requires_grad_(True)   # noqa: E731  [1,H,T,D] leaves
+    q4, k4, v4 = to(q), to(k), to(v)
+    layout = packing.packed_layout(lengths, [window], DEV)
+    out = flash_varlen.attention(q4, k4, v4, layout, 0.125, window)
+    out.backward(dout.to(DEV).transpose(0, 1)[None])
+    for got, want in zip((q4.grad, k4.grad, v4.grad), oracle()):
+        close(got[0].transpose(0, 1), want)
+
+    state_lengths, owners = [70, 130], [0, 0, 1]
+    ck, cv = (torch.randn(sum(state_lengths), hkv, d, generator=g).bfloat16() for _ in range(2))
+    q4, k4, v4, ck4, cv4 = to(q), to(k), to(v), to(ck), to(cv)
+    layout = packing.packed_layout(lengths, [window], DEV, owners=owners, state_lengths=state_lengths)
+    out = packing.layout_attention(q4, k4, v4, layout, 0.125, window, (ck4, cv4))
+    out.backward(dout.to(DEV).transpose(0, 1)[None])
+    for got, want in zip((q4.grad, k4.grad, v4.grad, ck4.grad, cv4.grad), oracle((ck, cv), owners, state_lengths)):
+        close(got[0].transpose(0, 1), want)
+
+    if flash_varlen.REGISTERED:
+        cu = torch.tensor([0, 90, 127, 327], dtype=torch.int32, device=DEV)
+        leaves = [x.to(DEV).requires_grad_(True) for x in (q, k, v)]
+        out, _ = torch.ops.bongard.flash_packed_forward(*leaves, cu, cu, 0.125, False)
+        out.backward(dout.to(DEV))
+        for leaf, want in zip(leaves, oracle(win=None)):
+            close(leaf.grad, want)
+        # one state per question, back to back, as the reference's op takes them
+        states = [50, 64, 20]
+        ck, cv = (torch.randn(sum(states), hkv, d, generator=g).bfloat16() for _ in range(2))
+        cuk = torch.tensor([0, 140, 241, 461], dtype=torch.int32, device=DEV)
+        leaves = [x.to(DEV).requires_grad_(True) for x in (q, k, v, ck, cv)]
+        out, _ = torch.ops.bongard.flash_prefix_forward(*leaves, torch.zeros(0, dtype=torch.int64, device=DEV), cu, cuk, 0.125)
+        out.backward(dout.to(DEV))
+        for leaf, want in zip(leaves, oracle((ck, cv), [0, 1, 2], states, win=None)):
+            close(leaf.grad, want)
+
+
 def test_project_qk_surface(golden_dir, tiny):
     weights, _ = tiny
     g = {k: torch.from_numpy(v) for k, v in np.load(golden_dir / 'ops.npz').items() if k.startswith(('qk_', 'state_'))}
