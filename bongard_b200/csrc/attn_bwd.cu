@@ -59,7 +59,8 @@ struct Layout {
     static constexpr int X2 = X1 + RES;
     static constexpr int Y1 = PASS == DV ? X1 + RES : X2 + RES;       // two slots
     static constexpr int Y2 = Y1 + 2 * STR;
-    static constexpr int COLS = Y2 + STR;                             // per-column info of two streamed tiles
+    static constexpr int NY2 = PASS == DV ? 2 : 1;                    // DQ/DK have room for one slot only
+    static constexpr int COLS = Y2 + NY2 * STR;                       // per-column info of two streamed tiles
     static constexpr int BARS = COLS + 2 * STREAM * 16;
     static constexpr int TOTAL = BARS + 256;
 };
@@ -83,12 +84,12 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid_co
     uint64_t* x_full = bars + 0;
     uint64_t* y1_full = bars + 1;    // [2]
     uint64_t* y1_empty = bars + 3;   // [2]
-    uint64_t* y2_full = bars + 5;
-    uint64_t* y2_empty = bars + 6;
-    uint64_t* a_full = bars + 7;     // [2]
-    uint64_t* e_full = bars + 9;     // 4 warp arrivals
-    uint64_t* out_done = bars + 10;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+    uint64_t* y2_full = bars + 5;    // [2]
+    uint64_t* y2_empty = bars + 7;   // [2]
+    uint64_t* a_full = bars + 9;     // [2]
+    uint64_t* e_full = bars + 11;    // 4 warp arrivals
+    uint64_t* out_done = bars + 12;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     ColInfo* cols = reinterpret_cast<ColInfo*>(smem + L::COLS);
 
@@ -119,9 +120,9 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid_co
             mbar_init(&y1_full[b], 1);
             mbar_init(&y1_empty[b], 1);
             mbar_init(&a_full[b], 1);
+            mbar_init(&y2_full[b], 1);
+            mbar_init(&y2_empty[b], 1);
         }
-        mbar_init(y2_full, 1);
-        mbar_init(y2_empty, 1);
         mbar_init(e_full, 4);
         mbar_init(out_done, 1);
         mbar_fence_init();
@@ -176,11 +177,13 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid_co
                     for (int s = 0; s < SLABS; ++s)
                         tma_load_3d(smem + L::Y1 + slot * L::STR + s * SLAB_STR, from_state ? &map_cy1 : &map_y1,
                                     &y1_full[slot], s * 64, head0, r0);
-                    if (!mbar_wait(y2_empty, (j & 1) ^ 1, ab, 402)) break;
-                    mbar_expect_tx(y2_full, L::STR);
+                    const int s2 = L::NY2 == 2 ? j & 1 : 0;                 // slot of Y2(j)
+                    const int u2 = L::NY2 == 2 ? j >> 1 : j;                // its use count
+                    if (!mbar_wait(&y2_empty[s2], (u2 & 1) ^ 1, ab, 402)) break;
+                    mbar_expect_tx(&y2_full[s2], L::STR);
                     for (int s = 0; s < SLABS; ++s)
-                        tma_load_3d(smem + L::Y2 + s * SLAB_STR, from_state ? &map_cy2 : &map_y2, y2_full, s * 64,
-                                    head0, r0);
+                        tma_load_3d(smem + L::Y2 + s2 * L::STR + s * SLAB_STR, from_state ? &map_cy2 : &map_y2,
+                                    &y2_full[s2], s * 64, head0, r0);
                 }
             }
         } else if (warp == 1) {
@@ -190,51 +193,90 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid_co
                 constexpr uint32_t idesc_o = instr_desc(ROWS, D, 1, 1, 0, 1);      // B operand MN-major
                 const uint32_t sx1 = smem_u32(smem + L::X1), sx2 = smem_u32(smem + L::X2);
                 const uint32_t sy1 = smem_u32(smem + L::Y1), sy2 = smem_u32(smem + L::Y2);
-                auto issue_a = [&](int j) {
-                    const int b = j & 1;
-                    if (!mbar_wait(&y1_full[b], (j >> 1) & 1, ab, 403)) return;
-                    // Score buffer b still feeds OUT(j-2) as its A operand: wait for that MMA to finish.
-                    if (j >= 2 && !mbar_wait(out_done, j & 1, ab, 404)) return;
-                    tc_fence_after();
-#pragma unroll
-                    for (int s = 0; s < SLABS; ++s)
-#pragma unroll
-                        for (int kk = 0; kk < 4; ++kk) {
-                            uint64_t da = smem_desc_sw128(sx1 + s * SLAB_RES + kk * 32, 16, 1024);
-                            uint64_t db = smem_desc_sw128(sy1 + b * L::STR + s * SLAB_STR + kk * 32, 16, 1024);
-                            mma_bf16_ss(tmem_base + b * STREAM, da, db, idesc_a, (s | kk) != 0);
-                        }
-                    if (PASS != DV) {
-                        if (!mbar_wait(y2_full, j & 1, ab, 405)) return;
-                        tc_fence_after();
-#pragma unroll
-                        for (int s = 0; s < SLABS; ++s)
-#pragma unroll
-                            for (int kk = 0; kk < 4; ++kk) {
-                                uint64_t da = smem_desc_sw128(sx2 + s * SLAB_RES + kk * 32, 16, 1024);
-                                uint64_t db = smem_desc_sw128(sy2 + s * SLAB_STR + kk * 32, 16, 1024);
-                                mma_bf16_ss(tmem_base + 128 + b * STREAM, da, db, idesc_a, (s | kk) != 0);
-                            }
-                        mma_commit(y2_empty);
-                    }
-                    mma_commit(&a_full[b]);
-                };
+                // Event-driven issue: OUT(jo) goes as soon as E(jo) is in tensor memory, the score MMAs of
+                // tile ja as soon as its streamed tiles have landed and its score buffer is free - whichever is
+                // ready first, so that a tile still in flight never holds back an MMA whose inputs are there.
+                auto ready = [&](uint64_t* bar, uint32_t parity) { return mbar_try_wait(bar, parity); };
                 if (mbar_wait(x_full, 0, ab, 406)) {
-                    issue_a(0);
-                    for (int j = 0; j < n_iter; ++j) {
-                        if (j + 1 < n_iter) issue_a(j + 1);
-                        if (!mbar_wait(e_full, j & 1, ab, 407)) break;
-                        if (PASS == DV && !mbar_wait(y2_full, j & 1, ab, 408)) break;
-                        tc_fence_after();
-                        const uint32_t sb = PASS == DV ? sy2 : sy1 + (j & 1) * L::STR;
+                    int ja = 0, jo = 0;             // next score tile, next OUT
+                    bool a1_done = false;           // A1(ja) issued, A2(ja) still to come
+                    uint64_t idle_since = 0;
+                    uint32_t spins = 0;
+                    while (jo < n_iter) {
+                        bool progressed = false;
+                        // ---- OUT(jo) += E(jo) * B
+                        if (jo < ja) {
+                            const int y2s = L::NY2 == 2 ? jo & 1 : 0;
+                            const uint32_t y2p = L::NY2 == 2 ? (jo >> 1) & 1 : jo & 1;
+                            if (ready(e_full, jo & 1) && (PASS != DV || ready(&y2_full[y2s], y2p))) {
+                                tc_fence_after();
+                                const uint32_t sb = PASS == DV ? sy2 + y2s * L::STR : sy1 + (jo & 1) * L::STR;
 #pragma unroll
-                        for (int kk = 0; kk < STREAM / 16; ++kk) {
-                            uint64_t db = smem_desc_sw128(sb + kk * 2048, SLAB_STR, 1024);
-                            mma_bf16_ts(tmem_out, tmem_base + (j & 1) * STREAM + kk * 8, db, idesc_o, (j | kk) != 0);
+                                for (int kk = 0; kk < STREAM / 16; ++kk) {
+                                    uint64_t db = smem_desc_sw128(sb + kk * 2048, SLAB_STR, 1024);
+                                    mma_bf16_ts(tmem_out, tmem_base + (jo & 1) * STREAM + kk * 8, db, idesc_o,
+                                                (jo | kk) != 0);
+                                }
+                                mma_commit(out_done);
+                                mma_commit(&y1_empty[jo & 1]);
+                                if (PASS == DV) mma_commit(&y2_empty[y2s]);
+                                ++jo;
+                                progressed = true;
+                            }
                         }
-                        mma_commit(out_done);
-                        mma_commit(&y1_empty[j & 1]);
-                        if (PASS == DV) mma_commit(y2_empty);
+                        // ---- scores of tile ja into buffer ja & 1
+                        if (!progressed && ja < n_iter && ja - jo <= 1) {
+                            const int b = ja & 1;
+                            if (!a1_done) {
+                                // Buffer b fed OUT(ja-2) as its A operand; that MMA must have finished.  It has if
+                                // OUT(ja-1) was issued (E(ja-1) is only stored after it); otherwise ask the barrier.
+                                const bool buffer_free = ja < 2 || jo == ja || ready(out_done, (jo - 1) & 1);
+                                if (buffer_free && ready(&y1_full[b], (ja >> 1) & 1)) {
+                                    tc_fence_after();
+#pragma unroll
+                                    for (int s = 0; s < SLABS; ++s)
+#pragma unroll
+                                        for (int kk = 0; kk < 4; ++kk) {
+                                            uint64_t da = smem_desc_sw128(sx1 + s * SLAB_RES + kk * 32, 16, 1024);
+                                            uint64_t db = smem_desc_sw128(sy1 + b * L::STR + s * SLAB_STR + kk * 32, 16, 1024);
+                                            mma_bf16_ss(tmem_base + b * STREAM, da, db, idesc_a, (s | kk) != 0);
+                                        }
+                                    a1_done = true;
+                                    progressed = true;
+                                    if (PASS == DV) {
+                                        mma_commit(&a_full[b]);
+                                        a1_done = false;
+                                        ++ja;
+                                    }
+                                }
+                            } else if (ready(&y2_full[0], ja & 1)) {
+                                tc_fence_after();
+#pragma unroll
+                                for (int s = 0; s < SLABS; ++s)
+#pragma unroll
+                                    for (int kk = 0; kk < 4; ++kk) {
+                                        uint64_t da = smem_desc_sw128(sx2 + s * SLAB_RES + kk * 32, 16, 1024);
+                                        uint64_t db = smem_desc_sw128(sy2 + s * SLAB_STR + kk * 32, 16, 1024);
+                                        mma_bf16_ss(tmem_base + 128 + b * STREAM, da, db, idesc_a, (s | kk) != 0);
+                                    }
+                                mma_commit(&y2_empty[0]);
+                                mma_commit(&a_full[b]);
+                                a1_done = false;
+                                ++ja;
+                                progressed = true;
+                            }
+                        }
+                        if (progressed) {
+                            idle_since = 0;
+                            spins = 0;
+                        } else {
+                            if (ab.raised()) break;
+                            if ((++spins & 0x3ff) == 0) {
+                                const uint64_t now = global_timer_ns();
+                                if (idle_since == 0) idle_since = now;
+                                else if (now - idle_since > kWaitBudgetNs) { ab.raise(407); break; }
+                            }
+                        }
                     }
                 }
             }
@@ -269,26 +311,32 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid_co
             }
 
             bool ok = true;     // after a failed wait the loop only keeps the named barrier in step
+            // facts of the 64 streamed query rows of tile j (DK/DV), fetched one tile ahead
+            auto column_facts = [&](int j) {
+                ColInfo ci;
+                ci.lse2 = 0.f; ci.delta = 0.f; ci.lo = 0; ci.hi = 0;              // lo == hi: sees nothing
+                if (PASS != DQ && tid < STREAM && j < n_iter) {
+                    bool unused;
+                    const int64_t token = int64_t(stream_origin(j, unused)) + tid / G;
+                    const int head = kvh * G + tid % G;
+                    if (token < t3) {
+                        ci.lse2 = p.lse[int64_t(head) * p.tq + token] * LOG2E;
+                        ci.delta = p.delta[int64_t(head) * p.tq + token];
+                        if (state_tile) { ci.lo = INT_MIN; ci.hi = INT_MAX; }
+                        else { ci.lo = p.row_lo[token]; ci.hi = p.row_hi[token]; }
+                    }
+                }
+                return ci;
+            };
+            ColInfo next_facts = column_facts(0);
             for (int j = 0; j < n_iter; ++j) {
                 const int b = j & 1;
                 bool from_state;
                 const int r0 = stream_origin(j, from_state);
                 if (PASS != DQ) {
-                    // facts of the 64 streamed query rows, shared through shared memory
-                    if (tid < STREAM) {
-                        const int64_t token = int64_t(r0) + tid / G;
-                        const int head = kvh * G + tid % G;
-                        ColInfo ci;
-                        ci.lse2 = 0.f; ci.delta = 0.f; ci.lo = 0; ci.hi = 0;      // lo == hi: sees nothing
-                        if (token < t3) {
-                            ci.lse2 = p.lse[int64_t(head) * p.tq + token] * LOG2E;
-                            ci.delta = p.delta[int64_t(head) * p.tq + token];
-                            if (state_tile) { ci.lo = INT_MIN; ci.hi = INT_MAX; }
-                            else { ci.lo = p.row_lo[token]; ci.hi = p.row_hi[token]; }
-                        }
-                        cols[b * STREAM + tid] = ci;
-                    }
+                    if (tid < STREAM) cols[b * STREAM + tid] = next_facts;     // shared through shared memory
                     named_barrier(1, 128);
+                    next_facts = column_facts(j + 1);                           // in flight during this tile's math
                 }
                 if (ok) ok = mbar_wait(&a_full[b], (j >> 1) & 1, ab, 409);
                 if (!ok) continue;

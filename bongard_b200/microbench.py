@@ -69,12 +69,21 @@ def attention(args, flush):
     gain = torch.zeros(d, device=DEV, dtype=torch.bfloat16)
     positions = torch.cat([torch.arange(n, dtype=torch.int32) for n in lengths]).to(DEV)
     ops.qk_norm_rope_(q, k, gain, gain, positions, ops.inv_freq(d, theta, DEV))
-    plan = ops.make_plan(lengths, window, DEV, group=hq // hkv, head_dim=d)
+    plan = ops.make_plan(lengths, window, DEV, group=hq // hkv, head_dim=d, backward=args.backward)
     ms = timed(lambda: ops.varlen_attention(q, k, v, plan, d ** -0.5), args.iters, args.warmup, flush)
     flops = 4 * d * hq * plan.pairs
-    return dict(op=f'varlen_attention_{args.variant}', tokens=t, sequences=len(lengths), tiles=plan.n_tiles,
+    out = [dict(op=f'varlen_attention_{args.variant}', tokens=t, sequences=len(lengths), tiles=plan.n_tiles,
                 ms=ms, tflops=flops / ms / 1e9, algorithmic_tflop=flops / 1e12,
-                min_bytes=2 * t * (2 * hq + 2 * hkv) * d)
+                min_bytes=2 * t * (2 * hq + 2 * hkv) * d)]
+    if args.backward:
+        # five contractions per visible pair (S, dP, dV, dK, dQ) against the forward's two
+        o, lse = ops.varlen_attention(q, k, v, plan, d ** -0.5, return_lse=True)
+        dout = randn(t, hq, d, seed=3)
+        ms = timed(lambda: ops.varlen_attention_backward(q, k, v, plan, d ** -0.5, o, lse, dout), args.iters,
+                   args.warmup, flush)
+        out.append(dict(op=f'varlen_attention_backward_{args.variant}', tokens=t, key_tiles=plan.n_kv_tiles, ms=ms,
+                        tflops=2.5 * flops / ms / 1e9, algorithmic_tflop=2.5 * flops / 1e12))
+    return out
 
 
 def mlp(args, flush):
@@ -186,6 +195,7 @@ def main():
     ap.add_argument('op', choices=['attention', 'mlp', 'linear', 'glue', 'serve'])
     ap.add_argument('--shape', default='4b-4b', choices=sorted(wl.SHAPES))
     ap.add_argument('--requests', type=int, default=40)
+    ap.add_argument('--backward', action='store_true', help='attention: also time the backward passes')
     ap.add_argument('--few-rows', action='store_true', help='linear/mlp: allow the split-K kernel for <= 256 tokens')
     ap.add_argument('--no-graphs', action='store_true', help='serve: launch every kernel eagerly')
     ap.add_argument('--variant', default='global', choices=['global', 'window'])
