@@ -6,9 +6,10 @@
 //     dQ = dS K            dK = dS^T Q
 // P is recomputed from the saved log-sum-exp, never stored.  Head size 256 leaves no room in
 // tensor memory (512 columns) for dK, dV and the score tiles at once, so the work is three passes
-// of ONE kernel template, each the shape of the forward kernel - a resident 128-row tile, 64-row
-// tiles streamed past it, scores in TMEM, the elementwise step by four warps (thread = lane),
-// its result written back to TMEM as bf16 and consumed from there by a TS-form MMA:
+// of ONE kernel template, each the shape of the forward kernel - a resident 128-row tile, tiles
+// streamed past it (64 rows where two resident tiles fill shared memory, 128 rows for dV), scores
+// in TMEM, the elementwise step by eight warps (two per TMEM lane quadrant, half of the score
+// columns each), its result written back to TMEM as bf16 and consumed from there by a TS-form MMA:
 //
 //   pass   resident (X1, X2)    streamed (Y1, Y2)     A1 = X1 Y1^T   A2 = X2 Y2^T   OUT += E * B
 //   DQ     Q tile, dO tile      K, V key tiles        S              dP             dS   * K (Y1)
@@ -28,10 +29,9 @@ namespace {
 using namespace bg;
 
 constexpr int ROWS = 128;          // resident rows (TMEM lanes)
-constexpr int STREAM = 64;         // streamed rows per iteration
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;       // warp 0 TMA, warp 1 MMA, warps 2-9 elementwise (two per TMEM lane quadrant)
+constexpr int EW_WARPS = 8;
 constexpr int SLAB_RES = ROWS * 128;      // one 64-column slab of a resident tile
-constexpr int SLAB_STR = STREAM * 128;    // one 64-column slab of a streamed tile
 constexpr float LOG2E = 1.4426950408889634f;
 
 enum Pass { DQ = 0, DK = 1, DV = 2 };
@@ -50,18 +50,24 @@ struct BwdParams {
     int32_t* status;
 };
 
+// Shared memory.  DQ and DK keep two resident tiles (128 KB at head size 256), which leaves room for
+// 64-row streamed tiles only: Y1 (needed by the score MMA and by OUT) in two slots, Y2 (needed by
+// the second score MMA only) in one.  DV keeps one resident tile and streams 128-row tiles through
+// one slot each, the forward kernel's budget.
 template <int D, int PASS>
 struct Layout {
     static constexpr int SLABS = D / 64;
+    static constexpr int SR = PASS == DV ? 128 : 64;                  // streamed rows per iteration
+    static constexpr int SLAB_STR = SR * 128;
     static constexpr int RES = SLABS * SLAB_RES;
     static constexpr int STR = SLABS * SLAB_STR;
+    static constexpr int NY1 = PASS == DV ? 1 : 2;
     static constexpr int X1 = 0;
     static constexpr int X2 = X1 + RES;
-    static constexpr int Y1 = PASS == DV ? X1 + RES : X2 + RES;       // two slots
-    static constexpr int Y2 = Y1 + 2 * STR;
-    static constexpr int NY2 = PASS == DV ? 2 : 1;                    // DQ/DK have room for one slot only
-    static constexpr int COLS = Y2 + NY2 * STR;                       // per-column info of two streamed tiles
-    static constexpr int BARS = COLS + 2 * STREAM * 16;
+    static constexpr int Y1 = PASS == DV ? X1 + RES : X2 + RES;
+    static constexpr int Y2 = Y1 + NY1 * STR;
+    static constexpr int COLS = Y2 + STR;                             // per-column facts of two streamed tiles
+    static constexpr int BARS = COLS + 2 * SR * 16;
     static constexpr int TOTAL = BARS + 256;
 };
 
@@ -79,17 +85,19 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid_co
                      const BwdParams p) {
     using L = Layout<D, PASS>;
     constexpr int SLABS = L::SLABS;
+    constexpr int SR = L::SR;
+    constexpr int HALF = SR / 2;        // streamed rows (score columns) one elementwise warp handles
     extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BARS);
     uint64_t* x_full = bars + 0;
     uint64_t* y1_full = bars + 1;    // [2]
     uint64_t* y1_empty = bars + 3;   // [2]
-    uint64_t* y2_full = bars + 5;    // [2]
-    uint64_t* y2_empty = bars + 7;   // [2]
-    uint64_t* a_full = bars + 9;     // [2]
-    uint64_t* e_full = bars + 11;    // 4 warp arrivals
-    uint64_t* out_done = bars + 12;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+    uint64_t* y2_full = bars + 5;
+    uint64_t* y2_empty = bars + 6;
+    uint64_t* a_full = bars + 7;     // [2]
+    uint64_t* e_full = bars + 9;     // 8 warp arrivals
+    uint64_t* out_done = bars + 10;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     ColInfo* cols = reinterpret_cast<ColInfo*>(smem + L::COLS);
 
@@ -101,13 +109,13 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid_co
 
     const int32_t* t = p.tiles + int64_t(blockIdx.x) * 8;
     // DQ: the forward tile record.  DK/DV: a key tile.
-    const int t0 = t[0], t1 = t[1], t2 = t[2], t3 = t[3], t4 = t[4], t5 = t[5], t6 = t[6], t7 = t[7];
+    const int t0 = t[0], t1 = t[1], t2 = t[2], t3 = t[3], t4 = t[4], t6 = t[6], t7 = t[7];
     int n_pre = 0, n_iter = 0;
     if (PASS == DQ) {
-        n_pre = (t7 + STREAM - 1) / STREAM;
-        n_iter = n_pre + (t3 - t2 + STREAM - 1) / STREAM;
+        n_pre = (t7 + SR - 1) / SR;
+        n_iter = n_pre + (t3 - t2 + SR - 1) / SR;
     } else {
-        const int per = STREAM / G;                      // query tokens per streamed tile
+        const int per = SR / G;                          // query tokens per streamed tile
         n_iter = (t3 - t2 + per - 1) / per;
     }
     const bool state_tile = PASS != DQ && t4 != 0;
@@ -120,10 +128,10 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid_co
             mbar_init(&y1_full[b], 1);
             mbar_init(&y1_empty[b], 1);
             mbar_init(&a_full[b], 1);
-            mbar_init(&y2_full[b], 1);
-            mbar_init(&y2_empty[b], 1);
         }
-        mbar_init(e_full, 4);
+        mbar_init(y2_full, 1);
+        mbar_init(y2_empty, 1);
+        mbar_init(e_full, EW_WARPS);
         mbar_init(out_done, 1);
         mbar_fence_init();
         tma_prefetch_desc(&map_x1);
@@ -139,17 +147,21 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid_co
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_out = tmem_base + 256;
+    // score buffers: A1[b] at column b * SR; A2[b] (DQ/DK, SR = 64) at 128 + b * SR
     const bool run = n_iter > 0 && !ab.raised();
 
     // First streamed row (key or query token) of iteration j, and whether it comes from the state tensors.
     auto stream_origin = [&](int j, bool& from_state) {
         if (PASS == DQ) {
             from_state = j < n_pre;
-            return from_state ? t6 + j * STREAM : t2 + (j - n_pre) * STREAM;
+            return from_state ? t6 + j * SR : t2 + (j - n_pre) * SR;
         }
         from_state = false;
-        return t2 + j * (STREAM / G);
+        return t2 + j * (SR / G);
     };
+    // slot and barrier parity of Y1(j)
+    auto y1_slot = [](int j) { return L::NY1 == 2 ? j & 1 : 0; };
+    auto y1_parity = [](int j) { return uint32_t(L::NY1 == 2 ? (j >> 1) & 1 : j & 1); };
 
     if (run) {
         if (warp == 0) {
@@ -167,29 +179,52 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid_co
                         if (PASS == DK) tma_load_3d(smem + L::X2 + s * SLAB_RES, mx2, x_full, s * 64, kvh, t0);
                     }
                 }
-                for (int j = 0; j < n_iter; ++j) {
-                    bool from_state;
-                    const int r0 = stream_origin(j, from_state);
-                    const int head0 = PASS == DQ ? kvh : kvh * G;
-                    const int slot = j & 1;
-                    if (!mbar_wait(&y1_empty[slot], ((j >> 1) & 1) ^ 1, ab, 401)) break;
-                    mbar_expect_tx(&y1_full[slot], L::STR);
-                    for (int s = 0; s < SLABS; ++s)
-                        tma_load_3d(smem + L::Y1 + slot * L::STR + s * SLAB_STR, from_state ? &map_cy1 : &map_y1,
-                                    &y1_full[slot], s * 64, head0, r0);
-                    const int s2 = L::NY2 == 2 ? j & 1 : 0;                 // slot of Y2(j)
-                    const int u2 = L::NY2 == 2 ? j >> 1 : j;                // its use count
-                    if (!mbar_wait(&y2_empty[s2], (u2 & 1) ^ 1, ab, 402)) break;
-                    mbar_expect_tx(&y2_full[s2], L::STR);
-                    for (int s = 0; s < SLABS; ++s)
-                        tma_load_3d(smem + L::Y2 + s2 * L::STR + s * SLAB_STR, from_state ? &map_cy2 : &map_y2,
-                                    &y2_full[s2], s * 64, head0, r0);
+                // The two streams drain at different times (Y2 right after its score MMA, Y1 after OUT, or the
+                // other way round for DV), so each is refilled as soon as its own slot is free.
+                const int head0 = PASS == DQ ? kvh : kvh * G;
+                int i1 = 0, i2 = 0;
+                uint64_t idle_since = 0;
+                uint32_t spins = 0;
+                while (i1 < n_iter || i2 < n_iter) {
+                    bool progressed = false;
+                    if (i1 < n_iter && mbar_try_wait(&y1_empty[y1_slot(i1)], y1_parity(i1) ^ 1)) {
+                        bool from_state;
+                        const int r0 = stream_origin(i1, from_state);
+                        const int slot = y1_slot(i1);
+                        mbar_expect_tx(&y1_full[slot], L::STR);
+                        for (int s = 0; s < SLABS; ++s)
+                            tma_load_3d(smem + L::Y1 + slot * L::STR + s * L::SLAB_STR, from_state ? &map_cy1 : &map_y1,
+                                        &y1_full[slot], s * 64, head0, r0);
+                        ++i1;
+                        progressed = true;
+                    }
+                    if (i2 < n_iter && mbar_try_wait(y2_empty, (i2 & 1) ^ 1)) {
+                        bool from_state;
+                        const int r0 = stream_origin(i2, from_state);
+                        mbar_expect_tx(y2_full, L::STR);
+                        for (int s = 0; s < SLABS; ++s)
+                            tma_load_3d(smem + L::Y2 + s * L::SLAB_STR, from_state ? &map_cy2 : &map_y2, y2_full, s * 64,
+                                        head0, r0);
+                        ++i2;
+                        progressed = true;
+                    }
+                    if (progressed) {
+                        idle_since = 0;
+                        spins = 0;
+                    } else {
+                        if (ab.raised()) break;
+                        if ((++spins & 0x3ff) == 0) {
+                            const uint64_t now = global_timer_ns();
+                            if (idle_since == 0) idle_since = now;
+                            else if (now - idle_since > kWaitBudgetNs) { ab.raise(401); break; }
+                        }
+                    }
                 }
             }
         } else if (warp == 1) {
             // ------------------------------------------------------------ MMA issuer
             if (lane == 0) {
-                constexpr uint32_t idesc_a = instr_desc(ROWS, STREAM, 1, 1, 0, 0);
+                constexpr uint32_t idesc_a = instr_desc(ROWS, SR, 1, 1, 0, 0);
                 constexpr uint32_t idesc_o = instr_desc(ROWS, D, 1, 1, 0, 1);      // B operand MN-major
                 const uint32_t sx1 = smem_u32(smem + L::X1), sx2 = smem_u32(smem + L::X2);
                 const uint32_t sy1 = smem_u32(smem + L::Y1), sy2 = smem_u32(smem + L::Y2);
@@ -205,24 +240,19 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid_co
                     while (jo < n_iter) {
                         bool progressed = false;
                         // ---- OUT(jo) += E(jo) * B
-                        if (jo < ja) {
-                            const int y2s = L::NY2 == 2 ? jo & 1 : 0;
-                            const uint32_t y2p = L::NY2 == 2 ? (jo >> 1) & 1 : jo & 1;
-                            if (ready(e_full, jo & 1) && (PASS != DV || ready(&y2_full[y2s], y2p))) {
-                                tc_fence_after();
-                                const uint32_t sb = PASS == DV ? sy2 + y2s * L::STR : sy1 + (jo & 1) * L::STR;
+                        if (jo < ja && ready(e_full, jo & 1) && (PASS != DV || ready(y2_full, jo & 1))) {
+                            tc_fence_after();
+                            const uint32_t sb = PASS == DV ? sy2 : sy1 + y1_slot(jo) * L::STR;
 #pragma unroll
-                                for (int kk = 0; kk < STREAM / 16; ++kk) {
-                                    uint64_t db = smem_desc_sw128(sb + kk * 2048, SLAB_STR, 1024);
-                                    mma_bf16_ts(tmem_out, tmem_base + (jo & 1) * STREAM + kk * 8, db, idesc_o,
-                                                (jo | kk) != 0);
-                                }
-                                mma_commit(out_done);
-                                mma_commit(&y1_empty[jo & 1]);
-                                if (PASS == DV) mma_commit(&y2_empty[y2s]);
-                                ++jo;
-                                progressed = true;
+                            for (int kk = 0; kk < SR / 16; ++kk) {
+                                uint64_t db = smem_desc_sw128(sb + kk * 2048, L::SLAB_STR, 1024);
+                                mma_bf16_ts(tmem_out, tmem_base + (jo & 1) * SR + kk * 8, db, idesc_o, (jo | kk) != 0);
                             }
+                            mma_commit(out_done);
+                            if (PASS == DV) mma_commit(y2_empty);
+                            else mma_commit(&y1_empty[y1_slot(jo)]);
+                            ++jo;
+                            progressed = true;
                         }
                         // ---- scores of tile ja into buffer ja & 1
                         if (!progressed && ja < n_iter && ja - jo <= 1) {
@@ -231,35 +261,37 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid_co
                                 // Buffer b fed OUT(ja-2) as its A operand; that MMA must have finished.  It has if
                                 // OUT(ja-1) was issued (E(ja-1) is only stored after it); otherwise ask the barrier.
                                 const bool buffer_free = ja < 2 || jo == ja || ready(out_done, (jo - 1) & 1);
-                                if (buffer_free && ready(&y1_full[b], (ja >> 1) & 1)) {
+                                if (buffer_free && ready(&y1_full[y1_slot(ja)], y1_parity(ja))) {
                                     tc_fence_after();
 #pragma unroll
                                     for (int s = 0; s < SLABS; ++s)
 #pragma unroll
                                         for (int kk = 0; kk < 4; ++kk) {
                                             uint64_t da = smem_desc_sw128(sx1 + s * SLAB_RES + kk * 32, 16, 1024);
-                                            uint64_t db = smem_desc_sw128(sy1 + b * L::STR + s * SLAB_STR + kk * 32, 16, 1024);
-                                            mma_bf16_ss(tmem_base + b * STREAM, da, db, idesc_a, (s | kk) != 0);
+                                            uint64_t db = smem_desc_sw128(
+                                                sy1 + y1_slot(ja) * L::STR + s * L::SLAB_STR + kk * 32, 16, 1024);
+                                            mma_bf16_ss(tmem_base + b * SR, da, db, idesc_a, (s | kk) != 0);
                                         }
-                                    a1_done = true;
                                     progressed = true;
                                     if (PASS == DV) {
+                                        mma_commit(&y1_empty[0]);          // Q tile: only the scores read it
                                         mma_commit(&a_full[b]);
-                                        a1_done = false;
                                         ++ja;
+                                    } else {
+                                        a1_done = true;
                                     }
                                 }
-                            } else if (ready(&y2_full[0], ja & 1)) {
+                            } else if (ready(y2_full, ja & 1)) {
                                 tc_fence_after();
 #pragma unroll
                                 for (int s = 0; s < SLABS; ++s)
 #pragma unroll
                                     for (int kk = 0; kk < 4; ++kk) {
                                         uint64_t da = smem_desc_sw128(sx2 + s * SLAB_RES + kk * 32, 16, 1024);
-                                        uint64_t db = smem_desc_sw128(sy2 + s * SLAB_STR + kk * 32, 16, 1024);
-                                        mma_bf16_ss(tmem_base + 128 + b * STREAM, da, db, idesc_a, (s | kk) != 0);
+                                        uint64_t db = smem_desc_sw128(sy2 + s * L::SLAB_STR + kk * 32, 16, 1024);
+                                        mma_bf16_ss(tmem_base + 128 + b * SR, da, db, idesc_a, (s | kk) != 0);
                                     }
-                                mma_commit(&y2_empty[0]);
+                                mma_commit(y2_empty);
                                 mma_commit(&a_full[b]);
                                 a1_done = false;
                                 ++ja;
@@ -281,12 +313,15 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid_co
                 }
             }
         } else {
-            // ------------------------------------------------------------ elementwise step + epilogue (warps 2..5)
+            // ------------------------------------------------------------ elementwise step + epilogue (warps 2..9)
+            // Two warps share a TMEM lane quadrant: warp w reads lanes (w & 3) * 32.., and half h = (w - 2) / 4
+            // of the score columns (and of the output columns in the epilogue).
             const int part = warp & 3;
+            const int half = (warp - 2) >> 2;
             const int row = part * 32 + lane;                 // TMEM lane = resident row
             const uint32_t lane_addr = uint32_t(part * 32) << 16;
             const float c = p.scale * LOG2E;
-            const int tid = threadIdx.x - 64;                 // 0..127 among these warps
+            const int tid = threadIdx.x - 64;                 // 0..255 among these warps
 
             // resident-row facts
             bool lane_valid;
@@ -310,12 +345,11 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid_co
                 lane_key = t0 + row;
             }
 
-            bool ok = true;     // after a failed wait the loop only keeps the named barrier in step
-            // facts of the 64 streamed query rows of tile j (DK/DV), fetched one tile ahead
+            // facts of the streamed query rows of tile j (DK/DV), fetched one tile ahead
             auto column_facts = [&](int j) {
                 ColInfo ci;
                 ci.lse2 = 0.f; ci.delta = 0.f; ci.lo = 0; ci.hi = 0;              // lo == hi: sees nothing
-                if (PASS != DQ && tid < STREAM && j < n_iter) {
+                if (PASS != DQ && tid < SR && j < n_iter) {
                     bool unused;
                     const int64_t token = int64_t(stream_origin(j, unused)) + tid / G;
                     const int head = kvh * G + tid % G;
@@ -329,24 +363,26 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid_co
                 return ci;
             };
             ColInfo next_facts = column_facts(0);
+            bool ok = true;     // after a failed wait the loop only keeps the named barrier in step
             for (int j = 0; j < n_iter; ++j) {
                 const int b = j & 1;
                 bool from_state;
                 const int r0 = stream_origin(j, from_state);
                 if (PASS != DQ) {
-                    if (tid < STREAM) cols[b * STREAM + tid] = next_facts;     // shared through shared memory
-                    named_barrier(1, 128);
+                    if (tid < SR) cols[b * SR + tid] = next_facts;              // shared through shared memory
+                    named_barrier(1, EW_WARPS * 32);
                     next_facts = column_facts(j + 1);                           // in flight during this tile's math
                 }
                 if (ok) ok = mbar_wait(&a_full[b], (j >> 1) & 1, ab, 409);
                 if (!ok) continue;
                 tc_fence_after();
-                float s[STREAM], dp[STREAM];
+                float s[HALF], dp[HALF];
+                const int c0 = half * HALF;                   // first score column of this warp
 #pragma unroll
-                for (int cc = 0; cc < STREAM; cc += 32) {
-                    tmem_ld32(tmem_base + lane_addr + b * STREAM + cc, reinterpret_cast<uint32_t*>(s + cc));
+                for (int cc = 0; cc < HALF; cc += 32) {
+                    tmem_ld32(tmem_base + lane_addr + b * SR + c0 + cc, reinterpret_cast<uint32_t*>(s + cc));
                     if (PASS != DV)
-                        tmem_ld32(tmem_base + lane_addr + 128 + b * STREAM + cc, reinterpret_cast<uint32_t*>(dp + cc));
+                        tmem_ld32(tmem_base + lane_addr + 128 + b * SR + c0 + cc, reinterpret_cast<uint32_t*>(dp + cc));
                 }
                 tmem_wait_ld();
 
@@ -354,16 +390,16 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid_co
                     const int lo = from_state ? t6 : lane_lo;
                     const int hi = from_state ? t6 + t7 : lane_hi;
 #pragma unroll
-                    for (int i = 0; i < STREAM; ++i) {
-                        const int key = r0 + i;
+                    for (int i = 0; i < HALF; ++i) {
+                        const int key = r0 + c0 + i;
                         const bool vis = lane_valid && key >= lo && key < hi;
                         const float pr = vis ? fast_exp2(fmaf(s[i], c, -lane_lse2)) : 0.f;
                         s[i] = pr * (dp[i] - lane_delta) * p.scale;
                     }
                 } else {
 #pragma unroll
-                    for (int i = 0; i < STREAM; ++i) {
-                        const ColInfo ci = cols[b * STREAM + i];
+                    for (int i = 0; i < HALF; ++i) {
+                        const ColInfo ci = cols[b * SR + c0 + i];
                         const bool vis = lane_valid && lane_key >= ci.lo && lane_key < ci.hi;
                         const float pr = vis ? fast_exp2(fmaf(s[i], c, -ci.lse2)) : 0.f;
                         s[i] = PASS == DV ? pr : pr * (dp[i] - ci.delta) * p.scale;
@@ -377,24 +413,26 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid_co
                     if (!ok) continue;
                     tc_fence_after();
                 }
-                uint32_t w[STREAM / 2];
+                // packed bf16 over the first SR / 2 columns of the score buffer: this warp's half of them
+                uint32_t w[HALF / 2];
 #pragma unroll
-                for (int i = 0; i < STREAM / 2; ++i) w[i] = pack_bf16(s[2 * i], s[2 * i + 1]);
-                tmem_st32(tmem_base + lane_addr + b * STREAM, w);
+                for (int i = 0; i < HALF / 2; ++i) w[i] = pack_bf16(s[2 * i], s[2 * i + 1]);
+                if (HALF == 64) tmem_st32(tmem_base + lane_addr + b * SR + half * (HALF / 2), w);
+                else tmem_st16(tmem_base + lane_addr + b * SR + half * (HALF / 2), w);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(e_full);
             }
 
-            // epilogue: OUT -> bf16
+            // epilogue: OUT -> bf16, each warp of a quadrant takes half of the D columns
             if (ok && mbar_wait(out_done, (n_iter - 1) & 1, ab, 411)) {
                 tc_fence_after();
                 __nv_bfloat16* dst;
                 if (PASS == DQ) dst = p.out + (lane_token * p.q_heads + lane_head) * D;
                 else dst = (state_tile ? p.out_state : p.out) + (int64_t(lane_key) * p.kv_heads + kvh) * D;
 #pragma unroll 1
-                for (int cc = 0; cc < D; cc += 32) {
+                for (int cc = half * (D / 2); cc < (half + 1) * (D / 2); cc += 32) {
                     uint32_t o[32];
                     tmem_ld32(tmem_out + lane_addr + cc, o);
                     tmem_wait_ld();
@@ -412,7 +450,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid_co
                 }
             }
         }
-    } else if (warp >= 2 && n_iter == 0 && !ab.raised()) {
+    } else if (warp >= 2 && warp < 6 && n_iter == 0 && !ab.raised()) {
         // no query sees this tile (or the tile has no key): its gradient rows are zero
         const int row = (warp & 3) * 32 + lane;
         if (PASS == DQ) {
@@ -553,6 +591,7 @@ extern "C" int bg_varlen_attention_backward(
     if (!p.status) return BG_ERR_DRIVER;
 
     // Tensor maps.  Query-type tiles are (token, head-in-group) rows; key-type tiles are keys of one KV head.
+    constexpr int STREAM = 64;     // streamed rows of the DQ and DK passes; DV streams ROWS-row tiles (the *_res boxes)
     CUtensorMap q_res, do_res, q_str, do_str, k_res, v_res, k_str, v_str, ck_res, cv_res, ck_str, cv_str;
     int rc = row_map(&q_res, q, tq, q_heads, head_dim, ldq, hsq, g, ROWS / g);
     if (!rc) rc = row_map(&do_res, dout, tq, q_heads, head_dim, ldd, hsd, g, ROWS / g);
@@ -586,8 +625,10 @@ extern "C" int bg_varlen_attention_backward(
         p.tiles = kv_tiles; p.out = static_cast<__nv_bfloat16*>(dk); p.out_state = static_cast<__nv_bfloat16*>(dck);
         rc = head_dim == 64 ? launch_pass<64, DK>(m, p, n_kv_tiles, stream) : launch_pass<256, DK>(m, p, n_kv_tiles, stream);
         if (rc) return rc;
+        // DV: resident K; streamed Q, dO in 128-row tiles
+        const CUtensorMap mv[8] = {k_res, v_res, ck_res, cv_res, q_res, do_res, q_res, do_res};
         p.out = static_cast<__nv_bfloat16*>(dv); p.out_state = static_cast<__nv_bfloat16*>(dcv);
-        rc = head_dim == 64 ? launch_pass<64, DV>(m, p, n_kv_tiles, stream) : launch_pass<256, DV>(m, p, n_kv_tiles, stream);
+        rc = head_dim == 64 ? launch_pass<64, DV>(mv, p, n_kv_tiles, stream) : launch_pass<256, DV>(mv, p, n_kv_tiles, stream);
         if (rc) return rc;
     }
     return BG_OK;
