@@ -30,7 +30,7 @@ constexpr int STAGES = 6;
 constexpr int A_BYTES = BM * BK * 2;        // 16 KB
 constexpr int B_BYTES = (BN / 2) * BK * 2;  // 16 KB: this CTA's half of the weight panel
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + 2 * 256 * 4;
 constexpr int THREADS = 192;
 
 struct PairParams {
@@ -40,7 +40,18 @@ struct PairParams {
     int tiles_m, tiles_n;         // in units of 256-row pair tiles
     int group_m;
     int32_t* status;
+    // epilogue 2 (q|k|v projection with QK-norm + RoPE)
+    int q_dim, kv_dim, head_dim, table_rows;
+    float eps;
+    const __nv_bfloat16* q_gain;  // [head_dim] RMSNorm weights w (the gain is 1 + w)
+    const __nv_bfloat16* k_gain;
+    const int32_t* positions;     // [m]
+    const float2* rope_table;     // [table_rows, head_dim / 2] (cos, sin)
 };
+
+constexpr int GAIN_BYTES = 2 * 256 * 4;     // (1 + w) of the q and k norms as fp32, after the barriers
+
+__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
     int per_group = group_m * tiles_n;
@@ -93,6 +104,15 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     cluster_sync();               // both CTAs' barriers are initialised before anyone signals across
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    float* gains = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 256);   // [2][256]: q, k
+    if (p.epilogue == 2 && warp >= 2) {
+        for (int i = threadIdx.x - 64; i < 2 * p.head_dim; i += 128) {
+            const bool is_k = i >= p.head_dim;
+            gains[(is_k ? 256 : 0) + (is_k ? i - p.head_dim : i)] =
+                1.f + __bfloat162float((is_k ? p.k_gain : p.q_gain)[is_k ? i - p.head_dim : i]);
+        }
+        named_barrier(1, 128);
+    }
 
     const int pairs = gridDim.x >> 1, pair = blockIdx.x >> 1;
     const int num_tiles = p.tiles_m * p.tiles_n;
@@ -164,7 +184,93 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             tc_fence_after();
             const int row = tm * 2 * BM + rank * BM + row_in_tile;
             const uint32_t taddr = tmem_base + (uint32_t(part * 32) << 16) + buf * BN;
-            if (p.epilogue == 0) {
+            if (p.epilogue == 2) {
+                // q|k|v projection: every head of this 256-column tile is complete in this thread's TMEM lane.
+                // Query and key heads get the RMSNorm over the head with gain (1 + w) and the rotate-half RoPE
+                // of the token's position (bongard/attention.py:172-180) before the one rounding to bf16;
+                // the projection itself is rounded to bf16 first, as the module chain does.  Value heads are
+                // stored as they are.
+                const int col0 = tn * BN;
+                const int D = p.head_dim, HD = D >> 1;
+                int pos = row < p.m ? p.positions[row] : 0;
+                pos = pos < 0 ? 0 : (pos >= p.table_rows ? p.table_rows - 1 : pos);
+                const float2* trow = p.rope_table + int64_t(pos) * HD;
+#pragma unroll 1
+                for (int hb = 0; hb < BN; hb += D) {
+                    const int hcol = col0 + hb;                       // first output column of this head
+                    if (hcol >= p.n) break;
+                    __nv_bfloat16* dst = p.out + int64_t(row) * p.ldo + hcol;
+                    if (hcol >= p.q_dim + p.kv_dim) {
+                        // value head: plain store
+#pragma unroll 1
+                        for (int c = 0; c < D; c += 32) {
+                            uint32_t r[32];
+                            tmem_ld32(taddr + hb + c, r);
+                            tmem_wait_ld();
+                            if (row < p.m) {
+#pragma unroll
+                                for (int v = 0; v < 4; ++v) {
+                                    uint4 o;
+                                    o.x = pack_bf16(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+                                    o.y = pack_bf16(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+                                    o.z = pack_bf16(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+                                    o.w = pack_bf16(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+                                    *reinterpret_cast<uint4*>(dst + c + v * 8) = o;
+                                }
+                            }
+                        }
+                        continue;
+                    }
+                    const float* gain = gains + (hcol >= p.q_dim ? 256 : 0);
+                    float ss = 0.f;
+#pragma unroll 1
+                    for (int c = 0; c < D; c += 32) {
+                        uint32_t r[32];
+                        tmem_ld32(taddr + hb + c, r);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const float x = round_bf16(__uint_as_float(r[i]));
+                            ss += x * x;
+                        }
+                    }
+                    const float rinv = rsqrtf(ss / float(D) + p.eps);
+#pragma unroll 1
+                    for (int c = 0; c < HD; c += 32) {
+                        uint32_t lo[32], hi[32];
+                        tmem_ld32(taddr + hb + c, lo);
+                        tmem_ld32(taddr + hb + HD + c, hi);
+                        tmem_wait_ld();
+                        if (row < p.m) {
+#pragma unroll
+                            for (int v = 0; v < 4; ++v) {
+                                float ol[8], oh[8];
+#pragma unroll
+                                for (int q4 = 0; q4 < 4; ++q4) {
+                                    // two (cos, sin) pairs per 16-byte load
+                                    const float4 t = __ldg(reinterpret_cast<const float4*>(trow + c + v * 8 + q4 * 2));
+#pragma unroll
+                                    for (int e2 = 0; e2 < 2; ++e2) {
+                                        const int i = v * 8 + q4 * 2 + e2;
+                                        const float cs = e2 ? t.z : t.x, sn = e2 ? t.w : t.y;
+                                        const float a = round_bf16(__uint_as_float(lo[i])) * rinv * gain[c + i];
+                                        const float b = round_bf16(__uint_as_float(hi[i])) * rinv * gain[HD + c + i];
+                                        ol[q4 * 2 + e2] = a * cs - b * sn;
+                                        oh[q4 * 2 + e2] = b * cs + a * sn;
+                                    }
+                                }
+                                uint4 o;
+                                o.x = pack_bf16(ol[0], ol[1]); o.y = pack_bf16(ol[2], ol[3]);
+                                o.z = pack_bf16(ol[4], ol[5]); o.w = pack_bf16(ol[6], ol[7]);
+                                *reinterpret_cast<uint4*>(dst + c + v * 8) = o;
+                                o.x = pack_bf16(oh[0], oh[1]); o.y = pack_bf16(oh[2], oh[3]);
+                                o.z = pack_bf16(oh[4], oh[5]); o.w = pack_bf16(oh[6], oh[7]);
+                                *reinterpret_cast<uint4*>(dst + HD + c + v * 8) = o;
+                            }
+                        }
+                    }
+                }
+            } else if (p.epilogue == 0) {
                 const int col0 = tn * BN;
                 __nv_bfloat16* dst = p.out + int64_t(row) * p.ldo + col0;
 #pragma unroll 1
@@ -235,10 +341,54 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 
 }  // namespace
 
+static int pair_launch(PairParams p, const CUtensorMap& map_a, const CUtensorMap& map_w, void* out, int64_t ldo,
+                       int64_t m, int64_t n, int64_t k, int epilogue, cudaStream_t stream);
+
 // Launcher used by bg_gemm_bf16 for every problem with more than 128 rows.
 int bg_gemm_bf16_pair_launch(const CUtensorMap& map_a, const CUtensorMap& map_w, void* out, int64_t ldo, int64_t m,
                              int64_t n, int64_t k, int epilogue, cudaStream_t stream) {
-    PairParams p;
+    PairParams p = {};
+    return pair_launch(p, map_a, map_w, out, ldo, m, n, k, epilogue, stream);
+}
+
+// out[m, q_dim + 2 kv_dim] = a . w^T with QK-norm + RoPE applied to the query and key heads in the epilogue.
+extern "C" int bg_gemm_bf16_qkv_rope(const void* a, int64_t lda, const void* w, int64_t ldw, void* out, int64_t ldo,
+                                     int64_t m, int64_t k, int q_dim, int kv_dim, int head_dim, const void* q_gain,
+                                     const void* k_gain, const int32_t* positions, const float* rope_table,
+                                     int64_t table_rows, float eps, void* stream) {
+    const int64_t n = int64_t(q_dim) + 2 * int64_t(kv_dim);
+    if (m < 0 || k <= 0 || q_dim <= 0 || kv_dim <= 0 || (head_dim != 64 && head_dim != 128 && head_dim != 256) ||
+        q_dim % head_dim || kv_dim % head_dim || table_rows <= 0) {
+        bg_set_error("bg_gemm_bf16_qkv_rope: bad shape (q_dim %d, kv_dim %d, head_dim %d)", q_dim, kv_dim, head_dim);
+        return BG_ERR_SHAPE;
+    }
+    if (m == 0) return BG_OK;
+    if ((k % 8) || (lda % 8) || (ldw % 8) || (ldo % 8) ||
+        ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out) |
+          reinterpret_cast<uintptr_t>(rope_table)) & 15)) {
+        bg_set_error("bg_gemm_bf16_qkv_rope: pointers must be 16-byte aligned, k and leading dimensions multiples of 8");
+        return BG_ERR_ALIGN;
+    }
+    CUtensorMap map_a, map_w;
+    uint64_t dims_a[2] = {(uint64_t)k, (uint64_t)m}, str_a[1] = {(uint64_t)lda * 2};
+    uint64_t dims_w[2] = {(uint64_t)k, (uint64_t)n}, str_w[1] = {(uint64_t)ldw * 2};
+    uint32_t box_a[2] = {BK, BM}, box_w[2] = {BK, 128};
+    int rc = bg_make_tensor_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a, dims_a, str_a, box_a,
+                                CU_TENSOR_MAP_SWIZZLE_128B);
+    if (!rc) rc = bg_make_tensor_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, dims_w, str_w, box_w,
+                                     CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    PairParams p = {};
+    p.q_dim = q_dim; p.kv_dim = kv_dim; p.head_dim = head_dim; p.table_rows = (int)table_rows; p.eps = eps;
+    p.q_gain = static_cast<const __nv_bfloat16*>(q_gain);
+    p.k_gain = static_cast<const __nv_bfloat16*>(k_gain);
+    p.positions = positions;
+    p.rope_table = reinterpret_cast<const float2*>(rope_table);
+    return pair_launch(p, map_a, map_w, out, ldo, m, n, k, 2, static_cast<cudaStream_t>(stream));
+}
+
+static int pair_launch(PairParams p, const CUtensorMap& map_a, const CUtensorMap& map_w, void* out, int64_t ldo,
+                       int64_t m, int64_t n, int64_t k, int epilogue, cudaStream_t stream) {
     p.m = (int)m; p.n = (int)n; p.k = (int)k; p.epilogue = epilogue; p.ldo = ldo;
     p.out = static_cast<__nv_bfloat16*>(out);
     p.tiles_m = (int)((m + 2 * BM - 1) / (2 * BM));

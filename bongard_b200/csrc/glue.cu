@@ -191,6 +191,17 @@ __global__ void qk_norm_rope_kernel(__nv_bfloat16* __restrict__ q, int64_t ldq, 
     }
 }
 
+// (cos, sin) of position * inv_freq[i] for every position below `rows`, the angles the QK-norm + RoPE
+// kernel computes on the fly; the q|k|v GEMM epilogue reads them from this table instead.
+__global__ void rope_table_kernel(float2* __restrict__ table, int64_t rows, int half, const float* __restrict__ inv_freq) {
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= rows * half) return;
+    const float pos = float(i / half);
+    float sn, cs;
+    sincosf(pos * inv_freq[i % half], &sn, &cs);
+    table[i] = make_float2(cs, sn);
+}
+
 // Scaled word embedding with the end-of-image override (transformers modeling_t5gemma2.py:644-647).
 __global__ void embed_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                              const __nv_bfloat16* __restrict__ eoi, __nv_bfloat16* __restrict__ out, int h,
@@ -413,6 +424,17 @@ int bg_qk_norm_rope_table(void* q, int64_t ldq, int q_heads, void* k, int64_t ld
     }
     return qk_norm_rope_launch(q, ldq, q_heads, k, ldk, k_heads, q_weight, k_weight, nullptr, nullptr, cos_table,
                                sin_table, tokens, head_dim, eps, 1, stream);
+}
+
+int bg_rope_table(float* table, int64_t rows, int head_dim, const float* inv_freq, void* stream) {
+    if (rows <= 0 || head_dim <= 0 || head_dim % 2) {
+        bg_set_error("bg_rope_table: bad shape");
+        return BG_ERR_SHAPE;
+    }
+    const int64_t n = rows * (head_dim / 2);
+    rope_table_kernel<<<(unsigned)((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<float2*>(table), rows, head_dim / 2, inv_freq);
+    return check_launch("bg_rope_table");
 }
 
 int bg_embed(const int64_t* ids, const void* table, const void* eoi_embedding, void* out, int64_t rows, int64_t h,

@@ -122,6 +122,22 @@ def linear(args, flush):
         ms = timed(lambda: ops.linear(x, w, few_rows=args.few_rows), args.iters, args.warmup, flush)
         out.append(dict(op=f'gemm_bf16_{name}', tokens=t, ms=ms, tflops=2 * t * n * k / ms / 1e9,
                         min_bytes=2 * (t * k + n * k + t * n)))
+        if name == 'qkv':
+            # the same projection with QK-norm + RoPE in its epilogue, against projection + separate kernel
+            gain = randn(256, std=0.1, seed=12)
+            positions = (torch.arange(t, device=DEV, dtype=torch.int32) % 4096)
+            table = ops.rope_table(256, 1e4, 4096, DEV)
+            ms = timed(lambda: ops.linear_qkv_rope(x, w, 2048, 1024, 256, gain, gain, positions, table), args.iters,
+                       args.warmup, flush)
+            out.append(dict(op='gemm_bf16_qkv_fused_norm_rope', tokens=t, ms=ms, tflops=2 * t * n * k / ms / 1e9))
+            freqs = ops.inv_freq(256, 1e4, DEV)
+
+            def two_kernels():
+                y = ops.linear(x, w)
+                ops.qk_norm_rope_(y[:, :2048].view(t, 8, 256), y[:, 2048:3072].view(t, 4, 256), gain, gain, positions, freqs)
+
+            ms = timed(two_kernels, args.iters, args.warmup, flush)
+            out.append(dict(op='gemm_bf16_qkv_then_norm_rope', tokens=t, ms=ms, tflops=2 * t * n * k / ms / 1e9))
     return out
 
 

@@ -187,6 +187,48 @@ def linear(x, weight, out=None, *, few_rows=False):
     return out.view(*x.shape[:-1], n)
 
 
+_ROPE_TABLES = {}
+
+
+def rope_table(head_dim, theta, rows, device):
+    """(cos, sin) fp32 [rows', head_dim/2, 2] of position * inv_freq for positions below rows' >= rows
+    (grown in powers of two, one table per (head_dim, theta, device))."""
+    key = (int(head_dim), float(theta), str(device))
+    table = _ROPE_TABLES.get(key)
+    if table is None or table.shape[0] < rows:
+        size = 8192
+        while size < rows:
+            size *= 2
+        table = torch.empty((size, head_dim // 2, 2), device=device, dtype=torch.float32)
+        _lib.check(_lib.load().bg_rope_table(_ptr(table), size, head_dim, _ptr(inv_freq(head_dim, theta, device)),
+                                             _stream()), 'bg_rope_table')
+        _ROPE_TABLES[key] = table
+    return table
+
+
+def linear_qkv_rope(x, weight, q_dim, kv_dim, head_dim, q_weight, k_weight, positions, table, eps=1e-6):
+    """x [T, K] @ [Wq; Wk; Wv].T -> [T, q_dim + 2 kv_dim] with QK-norm + RoPE applied to the query and
+    key heads inside the GEMM epilogue (value heads untouched)."""
+    lib = _lib.load()
+    flat, m, k, lda = _rows(x, 'x')
+    _need(weight, 'weight'), _need(positions, 'positions', torch.int32), _need(table, 'rope table', torch.float32)
+    n = q_dim + 2 * kv_dim
+    if weight.shape != (n, k) or weight.stride(1) != 1:
+        raise ValueError(f'weight must be [{n}, {k}] with contiguous rows')
+    if positions.numel() != m or table.shape[1:] != (head_dim // 2, 2) or not table.is_contiguous():
+        raise ValueError('positions must have one entry per row and the table must be [rows, head_dim/2, 2]')
+    out = torch.empty((m, n), device=x.device, dtype=BF16)
+    timer = GEMM_TIMER
+    begin = timer.start() if timer is not None else None
+    _lib.check(lib.bg_gemm_bf16_qkv_rope(_ptr(flat), lda, _ptr(weight), weight.stride(0), _ptr(out), n, m, k, q_dim,
+                                         kv_dim, head_dim, _ptr(_need(q_weight, 'q_norm')), _ptr(_need(k_weight, 'k_norm')),
+                                         _ptr(positions), _ptr(table), table.shape[0], eps, _stream()),
+               'bg_gemm_bf16_qkv_rope')
+    if timer is not None:
+        timer.stop(begin, 2 * m * n * k)
+    return out
+
+
 def linear_geglu(x, gate_up, *, few_rows=False):
     """gelu_tanh(x @ gate.T) * (x @ up.T) with gate_up = cat([gate, up]) of shape [2I, K]."""
     lib = _lib.load()

@@ -87,6 +87,22 @@ int bg_embed(const int64_t* ids, const void* table, const void* eoi_embedding, v
 int bg_gemm_bf16(const void* a, int64_t lda, const void* w, int64_t ldw, void* out, int64_t ldo, int64_t m,
                  int64_t n, int64_t k, int epilogue, void* stream);
 
+/* The q|k|v projection with QK-norm + RoPE fused into its epilogue: out[m, q_dim + 2 kv_dim] =
+ * a[m, k] . w^T where w stacks the q, k and v projection weights; every query and key head gets the
+ * fp32 RMSNorm over head_dim with gain (1 + q_gain / k_gain) and the rotate-half rotation by the
+ * angles of its token's position before the single rounding to bf16 (the projection is rounded to
+ * bf16 first, as the module chain does); value heads are stored as projected.  positions int32 [m];
+ * rope_table fp32 [table_rows, head_dim / 2, 2] = (cos, sin), filled by bg_rope_table from the same
+ * inv_freq bg_qk_norm_rope takes, covering every position in use.  head_dim 64, 128 or 256.
+ * Replaces q_proj/k_proj/v_proj + q_norm/k_norm + apply_rotary_pos_emb of HF:248-262 and
+ * bongard/attention.py:172-180 project_qk in one kernel (the reference fuses norm + RoPE only on
+ * Metal, bongard/qk_norm_rope.metal:4-33, and keeps the projections separate). */
+int bg_rope_table(float* table, int64_t rows, int head_dim, const float* inv_freq, void* stream);
+int bg_gemm_bf16_qkv_rope(const void* a, int64_t lda, const void* w, int64_t ldw, void* out, int64_t ldo, int64_t m,
+                          int64_t k, int q_dim, int kv_dim, int head_dim, const void* q_gain, const void* k_gain,
+                          const int32_t* positions, const float* rope_table, int64_t table_rows, float eps,
+                          void* stream);
+
 /* bg_gemm_bf16 for 1..256 rows (k % 64 == 0, n % 128 == 0; GeGLU: n % 64 == 0), the single-request
  * serving case of bongard/model.py:448-458 (one question group decoded against a cached state), where
  * the contraction is bound by streaming the weights from HBM: every weight byte is fetched once, K is

@@ -169,6 +169,31 @@ def test_linear_few_rows_falls_back_and_entry_point_rejects():
                    'bg_gemm_bf16_skinny')
 
 
+@pytest.mark.parametrize('d,hq,hkv,theta', [(64, 4, 2, 1e4), (256, 8, 4, 1e6), (128, 2, 2, 1e4)])
+@pytest.mark.parametrize('m', [7, 300])
+def test_qkv_projection_with_fused_norm_rope(d, hq, hkv, theta, m):
+    """The q|k|v GEMM with QK-norm + RoPE in its epilogue against the two-kernel path (same rounding
+    points, another summation order: a bf16 ulp at most) and against the fp32 oracle."""
+    k_in, qd, kd = 256, hq * d, hkv * d
+    x, w = rnd(m, k_in, seed=40), rnd(qd + 2 * kd, k_in, seed=41, std=0.05)
+    qw, kw = rnd(d, seed=42, std=0.1), rnd(d, seed=43, std=0.1)
+    positions = (torch.arange(m, dtype=torch.int32) * 37) % 5000
+    xd, wd, qwd, kwd, pd = (t.to(DEV) for t in (x, w, qw, kw, positions))
+    table = ops.rope_table(d, theta, 5000, DEV)
+    fused = ops.linear_qkv_rope(xd, wd, qd, kd, d, qwd, kwd, pd, table)
+    plain = ops.linear(xd, wd)
+    q, k = plain[:, :qd].view(m, hq, d), plain[:, qd:qd + kd].view(m, hkv, d)
+    ops.qk_norm_rope_(q, k, qwd, kwd, pd, ops.inv_freq(d, theta, DEV))
+    assert_close(fused, plain.float(), atol=2e-3, rtol=8e-3)
+    assert torch.equal(fused[:, qd + kd:], plain[:, qd + kd:])                       # value heads untouched
+    proj = (x.float() @ w.float().t()).bfloat16().float()
+    cos, sin = om.rope_tables(positions.long(), d, theta, torch.float32)
+    want_q, want_k = om.qk_norm_rope(proj[:, :qd].view(m, hq, d), proj[:, qd:qd + kd].view(m, hkv, d), qw.float(),
+                                     kw.float(), cos, sin)
+    assert_close(fused[:, :qd].view(m, hq, d), want_q, atol=3e-2, rtol=2e-2)
+    assert_close(fused[:, qd:qd + kd].view(m, hkv, d), want_k, atol=3e-2, rtol=2e-2)
+
+
 def test_geglu_mlp_matches_golden(golden_dir):
     g = {k: torch.from_numpy(v) for k, v in np.load(golden_dir / 'ops.npz').items() if k.startswith('mlp_')}
     x = g['mlp_x'].bfloat16()
