@@ -374,17 +374,23 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid_co
                     next_facts = column_facts(j + 1);                           // in flight during this tile's math
                 }
                 if (ok) ok = mbar_wait(&a_full[b], (j >> 1) & 1, ab, 409);
-                if (!ok) continue;
-                tc_fence_after();
                 float s[HALF], dp[HALF];
                 const int c0 = half * HALF;                   // first score column of this warp
+                if (ok) {
+                    tc_fence_after();
 #pragma unroll
-                for (int cc = 0; cc < HALF; cc += 32) {
-                    tmem_ld32(tmem_base + lane_addr + b * SR + c0 + cc, reinterpret_cast<uint32_t*>(s + cc));
-                    if (PASS != DV)
-                        tmem_ld32(tmem_base + lane_addr + 128 + b * SR + c0 + cc, reinterpret_cast<uint32_t*>(dp + cc));
+                    for (int cc = 0; cc < HALF; cc += 32) {
+                        tmem_ld32(tmem_base + lane_addr + b * SR + c0 + cc, reinterpret_cast<uint32_t*>(s + cc));
+                        if (PASS != DV)
+                            tmem_ld32(tmem_base + lane_addr + 128 + b * SR + c0 + cc,
+                                      reinterpret_cast<uint32_t*>(dp + cc));
+                    }
+                    tmem_wait_ld();
                 }
-                tmem_wait_ld();
+                // E is written over the first half of the score buffer, i.e. over columns the OTHER warp of this
+                // lane quadrant reads its scores from: nobody stores before everybody has loaded.
+                named_barrier(2, EW_WARPS * 32);
+                if (!ok) continue;
 
                 if (PASS == DQ) {
                     const int lo = from_state ? t6 : lane_lo;

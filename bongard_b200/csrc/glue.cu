@@ -302,6 +302,51 @@ judgment_head_kernel(const __nv_bfloat16* __restrict__ hidden, int64_t ldh,
     bg::cluster_sync();                // no CTA leaves while CTA 0 reads its partial
 }
 
+// dst[c, r] = src[r, c] for a bf16 matrix, through a padded 64 x 64 shared-memory tile so that both the
+// reads and the writes are coalesced.  Feeds the backward of the linears: the tensor-core GEMM takes both
+// operands K-contiguous, and dX = dY W / dW = dY^T X contract over the dimension that is NOT contiguous
+// in W, dY and X.
+__global__ void transpose_kernel(const __nv_bfloat16* __restrict__ src, int64_t lds, __nv_bfloat16* __restrict__ dst,
+                                 int64_t ldd, int64_t rows, int64_t cols) {
+    __shared__ __nv_bfloat16 tile[64][66];
+    const int64_t r0 = int64_t(blockIdx.y) * 64, c0 = int64_t(blockIdx.x) * 64;
+    const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;     // 256 threads: 64 columns x 4 rows per pass
+    for (int i = ty; i < 64; i += 4) {
+        const int64_t r = r0 + i, c = c0 + tx;
+        tile[i][tx] = (r < rows && c < cols) ? src[r * lds + c] : __float2bfloat16(0.f);
+    }
+    __syncthreads();
+    for (int i = ty; i < 64; i += 4) {
+        const int64_t c = c0 + i, r = r0 + tx;
+        if (c < cols && r < rows) dst[c * ldd + r] = tile[tx][i];
+    }
+}
+
+// Backward of the GeGLU epilogue h = gelu_tanh(g) * u for gu = [g | u] (both [rows, inter], bf16):
+// dgu = [dh * u * gelu_tanh'(g) | dh * gelu_tanh(g)].
+__global__ void geglu_backward_kernel(const __nv_bfloat16* __restrict__ gu, const __nv_bfloat16* __restrict__ dh,
+                                      __nv_bfloat16* __restrict__ dgu, int64_t rows, int64_t inter) {
+    const int64_t i = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
+    if (i >= rows * inter) return;
+    const int64_t row = i / inter, col = i % inter;             // inter % 8 == 0: the 8 elements share a row
+    float g[8], u[8], d[8], dg[8], du[8];
+    unpack8(*reinterpret_cast<const uint4*>(gu + row * 2 * inter + col), g);
+    unpack8(*reinterpret_cast<const uint4*>(gu + row * 2 * inter + inter + col), u);
+    unpack8(*reinterpret_cast<const uint4*>(dh + i), d);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+        const float x = g[e];
+        const float t = tanhf(k0 * (x + k1 * x * x * x));
+        const float gelu = 0.5f * x * (1.f + t);
+        const float dgelu = 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * k0 * (1.f + 3.f * k1 * x * x);
+        dg[e] = d[e] * u[e] * dgelu;
+        du[e] = d[e] * gelu;
+    }
+    *reinterpret_cast<uint4*>(dgu + row * 2 * inter + col) = pack8(dg);
+    *reinterpret_cast<uint4*>(dgu + row * 2 * inter + inter + col) = pack8(du);
+}
+
 // Per-question temperature softmax in float64 (bongard/inference.py:54-73), one thread per question.
 __global__ void candidate_softmax_kernel(const float* __restrict__ logits, const int32_t* __restrict__ offsets,
                                          double* __restrict__ probs, int questions, double temperature) {
@@ -435,6 +480,31 @@ int bg_rope_table(float* table, int64_t rows, int head_dim, const float* inv_fre
     rope_table_kernel<<<(unsigned)((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<float2*>(table), rows, head_dim / 2, inv_freq);
     return check_launch("bg_rope_table");
+}
+
+int bg_transpose_bf16(const void* src, int64_t lds, void* dst, int64_t ldd, int64_t rows, int64_t cols, void* stream) {
+    if (rows < 0 || cols < 0 || lds < cols || ldd < rows) {
+        bg_set_error("bg_transpose_bf16: bad shape");
+        return BG_ERR_SHAPE;
+    }
+    if (rows == 0 || cols == 0) return BG_OK;
+    dim3 grid((unsigned)((cols + 63) / 64), (unsigned)((rows + 63) / 64));
+    transpose_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(src), lds, static_cast<__nv_bfloat16*>(dst), ldd, rows, cols);
+    return check_launch("bg_transpose_bf16");
+}
+
+int bg_geglu_backward(const void* gu, const void* dh, void* dgu, int64_t rows, int64_t inter, void* stream) {
+    if (rows < 0 || inter <= 0 || inter % 8) {
+        bg_set_error("bg_geglu_backward: the intermediate size must be a multiple of 8");
+        return BG_ERR_SHAPE;
+    }
+    if (rows == 0) return BG_OK;
+    const int64_t groups = rows * inter / 8;
+    geglu_backward_kernel<<<(unsigned)((groups + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(gu), static_cast<const __nv_bfloat16*>(dh), static_cast<__nv_bfloat16*>(dgu),
+        rows, inter);
+    return check_launch("bg_geglu_backward");
 }
 
 int bg_embed(const int64_t* ids, const void* table, const void* eoi_embedding, void* out, int64_t rows, int64_t h,

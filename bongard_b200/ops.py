@@ -247,6 +247,81 @@ def linear_geglu(x, gate_up, *, few_rows=False):
     return out.view(*x.shape[:-1], n)
 
 
+def transpose(x, pad_to=8):
+    """x [R, C] -> contiguous [C, R'] with R' = R rounded up to `pad_to` (zero padded): the layout the
+    GEMM needs when the contraction runs over R."""
+    lib = _lib.load()
+    _need(x, 'x')
+    if x.ndim != 2 or x.stride(1) != 1:
+        raise ValueError('transpose takes a 2-D tensor with contiguous rows')
+    r, c = x.shape
+    rp = (r + pad_to - 1) // pad_to * pad_to
+    out = (torch.zeros if rp != r else torch.empty)((c, rp), device=x.device, dtype=BF16)
+    _lib.check(lib.bg_transpose_bf16(_ptr(x), x.stride(0), _ptr(out), rp, r, c, _stream()), 'bg_transpose_bf16')
+    return out
+
+
+def linear_backward(x, weight, dy, *, need_dx=True, need_dw=True):
+    """Gradients of y = x @ weight.T: dx = dy @ weight, dw = dy.T @ x, both on the tensor cores."""
+    flat, m, k, _ = _rows(x, 'x')
+    n = weight.shape[0]
+    dy2 = dy.reshape(m, n)
+    if dy2.stride(1) != 1:
+        dy2 = dy2.contiguous()
+    dx = dw = None
+    if need_dx:
+        dx = linear(dy2, transpose(weight)).view(x.shape)             # contraction over N
+    if need_dw:
+        dw = linear(transpose(dy2), transpose(flat))                 # contraction over the rows, zero padded
+    return dx, dw
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight):
+        ctx.save_for_backward(x, weight)
+        return linear(x, weight)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        dx, dw = linear_backward(x, weight, dy, need_dx=ctx.needs_input_grad[0], need_dw=ctx.needs_input_grad[1])
+        return dx, dw
+
+
+class _LinearGeglu(torch.autograd.Function):
+    """h = gelu_tanh(x Wg^T) * (x Wu^T).  The pre-activations are recomputed in the backward (one more
+    GEMM) instead of being kept: they are four times the size of x."""
+
+    @staticmethod
+    def forward(ctx, x, gate_up):
+        ctx.save_for_backward(x, gate_up)
+        return linear_geglu(x, gate_up)
+
+    @staticmethod
+    def backward(ctx, dh):
+        x, gate_up = ctx.saved_tensors
+        lib = _lib.load()
+        flat, m, k, _ = _rows(x, 'x')
+        inter = gate_up.shape[0] // 2
+        gu = linear(flat, gate_up)
+        dh2 = dh.reshape(m, inter).contiguous()
+        dgu = torch.empty_like(gu)
+        _lib.check(lib.bg_geglu_backward(_ptr(gu), _ptr(dh2), _ptr(dgu), m, inter, _stream()), 'bg_geglu_backward')
+        dx, dw = linear_backward(x, gate_up, dgu, need_dx=ctx.needs_input_grad[0], need_dw=ctx.needs_input_grad[1])
+        return dx, dw
+
+
+def linear_autograd(x, weight):
+    """linear() that records its backward."""
+    return _Linear.apply(x, weight)
+
+
+def linear_geglu_autograd(x, gate_up):
+    """linear_geglu() that records its backward."""
+    return _LinearGeglu.apply(x, gate_up)
+
+
 # --------------------------------------------------------------------------------------
 # packed variable-length attention
 # --------------------------------------------------------------------------------------

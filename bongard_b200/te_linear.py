@@ -38,7 +38,9 @@ class B200Linear(nn.Module):
         if len(linears) == 1:
             self.weight = linears[0].weight          # the native parameter object: state_dict keys stay HF-shaped
         else:
-            self.weight = nn.Parameter(torch.cat([linear.weight.detach() for linear in linears], 0), requires_grad=False)
+            # stacked rows as one parameter, trainable when its sources are (bongard/te_linear.py:47-55)
+            self.weight = nn.Parameter(torch.cat([linear.weight.detach() for linear in linears], 0),
+                                       requires_grad=all(linear.weight.requires_grad for linear in linears))
         self._cache = None
         self.counts = Counter()
 
@@ -51,6 +53,13 @@ class B200Linear(nn.Module):
         return self._cache[1]
 
     def forward(self, x, *, geglu=False):
+        if self.training and torch.is_grad_enabled() and (x.requires_grad or self.weight.requires_grad):
+            # train mode: the reference goes through autograd here (bongard/te_linear.py:63-77); the bf16
+            # recipe records a tensor-core backward, the fp8 recipe is an inference recipe
+            if self.bongard_recipe != 'bf16':
+                raise ValueError("the 'fp8' recipe is forward-only; train with recipe 'bf16'")
+            w = self.weight if self.weight.dtype == torch.bfloat16 else self.weight.to(torch.bfloat16)
+            return ops.linear_geglu_autograd(x, w) if geglu else ops.linear_autograd(x, w)
         w = self._operand()
         if self.bongard_recipe == 'fp8':
             return ops.linear_fp8(x, w, geglu=geglu)

@@ -114,6 +114,17 @@ int bg_gemm_bf16_skinny_supported(int64_t m, int64_t n, int64_t k, int epilogue)
 int bg_gemm_bf16_skinny(const void* a, int64_t lda, const void* w, int64_t ldw, void* out, int64_t ldo, int64_t m,
                         int64_t n, int64_t k, int epilogue, void* stream);
 
+/* Helpers for the backward of the bf16 linears (the reference trains through them with autograd:
+ * bongard/te_linear.py:59-77 TELinear.forward, 98-103 TEMLP.forward, bongard/fused_mlp.py:62-79).
+ * With y = x W^T: dx = dy W and dW = dy^T x contract over dimensions that are not contiguous in dy, W
+ * and x, while bg_gemm_bf16 wants both operands contiguous along the contraction, so the operands are
+ * transposed first: dx = bg_gemm_bf16(dy, W^T), dW = bg_gemm_bf16(dy^T, x^T).
+ *   bg_transpose_bf16: dst[c, r] = src[r, c] (row strides lds, ldd in elements).
+ *   bg_geglu_backward: for gu = [g | u] [rows, 2 inter] and dh [rows, inter]:
+ *       dgu = [dh * u * gelu_tanh'(g) | dh * gelu_tanh(g)]. */
+int bg_transpose_bf16(const void* src, int64_t lds, void* dst, int64_t ldd, int64_t rows, int64_t cols, void* stream);
+int bg_geglu_backward(const void* gu, const void* dh, void* dgu, int64_t rows, int64_t inter, void* stream);
+
 /* E4M3 quantisation with dynamic per-block scales: scale = 448 / max(amax, 1e-12), values clamped
  * to +-448 and rounded to nearest; the INVERSE scales are stored as fp32.
  *   rows : 1 x 128 blocks of x [m, k] -> q (uint8 [m, k], row stride ldq bytes), inv_scale_t [k/128, m].

@@ -172,6 +172,36 @@ def test_attention_surface_is_differentiable():
             close(leaf.grad, want)
 
 
+def test_converted_mlp_trains_like_the_native_one(tiny):
+    """Train mode: the converted MLP (te_linear and fused_mlp surfaces, bf16 recipe) gives the native
+    module's gradients for its input and its weights; the fp8 recipe refuses to train."""
+    weights, _ = tiny
+    x = torch.randn(3, 50, wl.TINY.hidden, generator=torch.Generator().manual_seed(4)).bfloat16().to(DEV)
+    dy = torch.randn(3, 50, wl.TINY.hidden, generator=torch.Generator().manual_seed(5)).bfloat16().to(DEV)
+
+    def run(convert):
+        backbone = build_backbone(wl.TINY, weights).train()
+        layer = backbone.decoder.layers[0]
+        convert(backbone)
+        inp = x.clone().requires_grad_(True)
+        out = layer.mlp(layer.pre_feedforward_layernorm(inp))
+        out.backward(dy)
+        grads = {n: p.grad.float().cpu() for n, p in layer.named_parameters() if p.grad is not None}
+        return out.detach().float().cpu(), inp.grad.float().cpu(), grads
+
+    want_out, want_dx, want = run(lambda b: None)
+    for convert in (lambda b: enable_te_linear(b, mlp='bf16'), lambda b: enable_fused_mlp(b, 'bf16')):
+        out, dx, grads = run(convert)
+        assert float((out - want_out).abs().max()) < 3e-2 * float(want_out.abs().max()) + 1e-3
+        assert float((dx - want_dx).abs().max()) < 3e-2 * float(want_dx.abs().max()) + 1e-3
+        down = next(v for k, v in grads.items() if 'down' in k)
+        assert float((down - want['mlp.down_proj.weight']).abs().max()) < 3e-2 * float(want['mlp.down_proj.weight'].abs().max())
+    backbone = build_backbone(wl.TINY, weights).train()
+    enable_te_linear(backbone, mlp='fp8')
+    with pytest.raises(ValueError, match='forward-only'):
+        backbone.decoder.layers[0].mlp(x.clone().requires_grad_(True))
+
+
 def test_project_qk_surface(golden_dir, tiny):
     weights, _ = tiny
     g = {k: torch.from_numpy(v) for k, v in np.load(golden_dir / 'ops.npz').items() if k.startswith(('qk_', 'state_'))}

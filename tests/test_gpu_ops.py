@@ -229,3 +229,29 @@ def test_judgment_head_and_softmax(golden_dir):
         l = logits.cpu()
         want = torch.cat([om.probabilities(l[:2], temp), om.probabilities(l[2:], temp)])
         assert float((probs - want).abs().max()) < 1e-12
+
+
+@pytest.mark.parametrize('m,n,k', [(5, 128, 64), (300, 512, 256), (1030, 2560, 2048)])
+def test_linear_backward(m, n, k):
+    """dx = dy W and dW = dy^T x through the tensor-core GEMM (operands transposed first) against autograd."""
+    x, w, dy = rnd(m, k, seed=50), rnd(n, k, seed=51, std=0.05), rnd(m, n, seed=52)
+    xd, wd = x.to(DEV).requires_grad_(True), w.to(DEV).requires_grad_(True)
+    ops.linear_autograd(xd, wd).backward(dy.to(DEV))
+    xf, wf = x.float().requires_grad_(True), w.float().requires_grad_(True)
+    (xf @ wf.t()).backward(dy.float())
+    assert_close(xd.grad, xf.grad, atol=2e-2, rtol=1e-2)
+    assert_close(wd.grad, wf.grad, atol=2e-2 * (m ** 0.5), rtol=1e-2)
+    t = ops.transpose(x.to(DEV))
+    assert torch.equal(t[:, :m].cpu(), x.t()) and float(t[:, m:].abs().max() if t.shape[1] > m else 0) == 0
+
+
+@pytest.mark.parametrize('m,i,k', [(7, 256, 128), (300, 1024, 256)])
+def test_linear_geglu_backward(m, i, k):
+    x, gu, dh = rnd(m, k, seed=53), rnd(2 * i, k, seed=54, std=0.05), rnd(m, i, seed=55)
+    xd, gd = x.to(DEV).requires_grad_(True), gu.to(DEV).requires_grad_(True)
+    ops.linear_geglu_autograd(xd, gd).backward(dh.to(DEV))
+    xf, gf = x.float().requires_grad_(True), gu.float().requires_grad_(True)
+    pre = xf @ gf.t()
+    (torch.nn.functional.gelu(pre[:, :i], approximate='tanh') * pre[:, i:]).backward(dh.float())
+    assert_close(xd.grad, xf.grad, atol=3e-2, rtol=2e-2)
+    assert_close(gd.grad, gf.grad, atol=3e-2 * (m ** 0.5), rtol=2e-2)
