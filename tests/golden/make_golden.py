@@ -1,6 +1,6 @@
 """Generate tests/golden/*.npz by running the reference itself on CPU.
 
-Run next to a checkout of the reference (default /root/reference, or $BONGARD_REFERENCE):
+Run with a checkout of the reference on the import path ($BONGARD_REFERENCE names its directory):
 
     python tests/golden/make_golden.py
 
@@ -20,7 +20,7 @@ import torch
 
 ROOT = Path(__file__).resolve().parents[2]
 sys.path.insert(0, str(ROOT))
-sys.path.insert(0, os.environ.get('BONGARD_REFERENCE', '/root/reference'))
+sys.path.insert(0, os.environ.get('BONGARD_REFERENCE', str(ROOT.parent / 'reference')))
 
 from bongard_b200 import workload as wl  # noqa: E402
 
