@@ -33,6 +33,9 @@ SIGNATURES = {
     'bg_quantize_e4m3_rows': ([P, I64, P, I64, P, I64, I64, P], INT),
     'bg_quantize_e4m3_tiles': ([P, I64, P, I64, P, I64, I64, P], INT),
     'bg_gemm_fp8_block128': ([P, I64, P, P, I64, P, P, I64, I64, I64, I64, INT, P], INT),
+    'bg_mxfp8_scale_bytes': ([I64, I64], I64),
+    'bg_quantize_mxfp8': ([P, I64, P, I64, P, I64, I64, P], INT),
+    'bg_gemm_mxfp8': ([P, I64, P, P, I64, P, P, I64, I64, I64, I64, INT, P], INT),
     'bg_linear_fp8_workspace_bytes': ([I64, I64], I64),
     'bg_linear_fp8': ([P, I64, P, I64, P, P, I64, I64, I64, I64, INT, P, I64, P], INT),
     'bg_linear_fp8_static_max_bytes': ([], I64),

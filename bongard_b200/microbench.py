@@ -111,6 +111,16 @@ def mlp(args, flush):
                  lambda: ops.linear_fp8(ops.linear_fp8(x, qgu, geglu=True), qd), 6 * t * h * i)):
             ms = timed(fn, args.iters, args.warmup, flush)
             out.append(dict(op=name, tokens=t, ms=ms, tflops=flops / ms / 1e9))
+        mgu, md = ops.quantize_mxfp8(wgu), ops.quantize_mxfp8(wd)
+        xm, hm = ops.quantize_mxfp8(x), ops.quantize_mxfp8(hidden)
+        for name, fn, flops in (
+                ('quantize_mxfp8_x', lambda: ops.quantize_mxfp8(x), 0),
+                ('gemm_mxfp8_gate_up_geglu', lambda: ops.gemm_mxfp8(xm, mgu, geglu=True), 4 * t * h * i),
+                ('gemm_mxfp8_down', lambda: ops.gemm_mxfp8(hm, md), 2 * t * h * i),
+                ('geglu_mlp_mxfp8_with_quantisation',
+                 lambda: ops.linear_mxfp8(ops.linear_mxfp8(x, mgu, geglu=True), md), 6 * t * h * i)):
+            ms = timed(fn, args.iters, args.warmup, flush)
+            out.append(dict(op=name, tokens=t, ms=ms, tflops=flops / ms / 1e9))
     return out
 
 

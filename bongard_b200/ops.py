@@ -736,6 +736,53 @@ def gemm_fp8(aq, a_inv_t, weight: Fp8Weight, *, geglu=False):
     return out
 
 
+@dataclass
+class Mxfp8Tensor:
+    """E4M3 values [rows, K] with UE8M0 scales per 32 K elements in the 512-byte atom layout."""
+
+    q: torch.Tensor            # uint8 [rows, K]
+    scales: torch.Tensor       # uint8 [ceil(rows/128) * K/128 * 512]
+
+    @property
+    def shape(self):
+        return self.q.shape
+
+
+def quantize_mxfp8(x):
+    """bf16 [rows, K] -> Mxfp8Tensor (K a multiple of 128)."""
+    lib = _lib.load()
+    flat, m, k, ldx = _rows(x, 'x')
+    q = torch.empty((m, k), device=x.device, dtype=torch.uint8)
+    scales = torch.zeros(lib.bg_mxfp8_scale_bytes(m, k), device=x.device, dtype=torch.uint8)
+    _lib.check(lib.bg_quantize_mxfp8(_ptr(flat), ldx, _ptr(q), k, _ptr(scales), m, k, _stream()), 'bg_quantize_mxfp8')
+    return Mxfp8Tensor(q, scales)
+
+
+def gemm_mxfp8(a: Mxfp8Tensor, weight: Mxfp8Tensor, *, geglu=False):
+    """Quantised activations times quantised weights: [m, K] x [N, K]^T -> bf16 [m, N] (N/2 with GeGLU)."""
+    lib = _lib.load()
+    m, k = a.shape
+    rows = weight.shape[0]
+    if weight.shape[1] != k:
+        raise ValueError(f'weight has K={weight.shape[1]}, input has {k}')
+    n = rows // 2 if geglu else rows
+    out = torch.empty((m, n), device=a.q.device, dtype=BF16)
+    timer = GEMM_TIMER
+    begin = timer.start() if timer is not None else None
+    _lib.check(lib.bg_gemm_mxfp8(_ptr(a.q), k, _ptr(a.scales), _ptr(weight.q), k, _ptr(weight.scales), _ptr(out), n,
+                                 m, n, k, 1 if geglu else 0, _stream()), 'bg_gemm_mxfp8')
+    if timer is not None:
+        timer.stop(begin, (4 if geglu else 2) * m * n * k)
+    return out
+
+
+def linear_mxfp8(x, weight: Mxfp8Tensor, *, geglu=False):
+    """bf16 x [..., K] times an MXFP8 weight: dynamic 1 x 32 power-of-two activation scales, block-scaled
+    tensor-core contraction, bf16 result."""
+    out = gemm_mxfp8(quantize_mxfp8(x), weight, geglu=geglu)
+    return out.view(*x.shape[:-1], out.shape[-1])
+
+
 def linear_fp8_static(x, weight: Fp8Weight, *, geglu=False):
     """linear_fp8 without any scratch allocation: the quantised activations live in a fixed
     buffer inside the library (see bg_linear_fp8_static).  Raises B200Error when the activation

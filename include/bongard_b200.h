@@ -153,6 +153,24 @@ int bg_linear_fp8(const void* x, int64_t ldx, const void* wq, int64_t ldw, const
                   int64_t ldo, int64_t m, int64_t n, int64_t k, int epilogue, void* workspace,
                   int64_t workspace_bytes, void* stream);
 
+/* MXFP8: E4M3 values with one power-of-two (UE8M0) scale per 32 consecutive K elements, the block
+ * format the tensor cores scale themselves (tcgen05.mma kind::mxf8f6f4.block_scale).
+ *   bg_quantize_mxfp8: x [rows, k] bf16 -> q uint8 [rows, k] (row stride ldq bytes) and scales:
+ *       e = ceil(log2(amax_32 / 448)) clamped to [-127, 127], q = e4m3(x * 2^-e), scale byte = e + 127,
+ *       stored in 512-byte atoms, one per 128 rows x 128 K elements, atom (r / 128, k / 128) at
+ *       (r / 128 * (k_total / 128) + k / 128) * 512, byte (r % 32) * 16 + (r % 128) / 32 * 4 + (k / 32) % 4
+ *       (the layout tcgen05.cp moves into tensor memory unchanged); bg_mxfp8_scale_bytes gives the size,
+ *       which the caller zero-fills once (rows beyond `rows` in the last atom are never written).
+ *   bg_gemm_mxfp8: out[m, n] = sum_k (2^ea Aq)(2^ew Wq)^T, fp32 accumulate in tensor memory, bf16 out,
+ *       epilogues as bg_gemm_bf16; k and n multiples of 128.
+ * Replaces the `mxfp8` recipe of bongard/te_linear.py:32-39 and bongard/fused_mlp.py:21-34 (Transformer
+ * Engine MXFP8BlockScaling) for the forward pass. */
+int64_t bg_mxfp8_scale_bytes(int64_t rows, int64_t k);
+int bg_quantize_mxfp8(const void* x, int64_t ldx, void* q, int64_t ldq, void* scales, int64_t rows, int64_t k,
+                      void* stream);
+int bg_gemm_mxfp8(const void* aq, int64_t lda, const void* a_scales, const void* wq, int64_t ldw, const void* w_scales,
+                  void* out, int64_t ldo, int64_t m, int64_t n, int64_t k, int epilogue, void* stream);
+
 /* bg_linear_fp8 for callers that cannot supply scratch memory.  (No counterpart in the reference.)
  * The quantised activations go to a fixed buffer inside the library instead of a caller-owned
  * workspace, so the call allocates nothing; in exchange the activation is limited to

@@ -218,6 +218,45 @@ def geglu_mlp_fp8_block128(x, gate, up, down, out_dtype=torch.bfloat16):
     return linear_fp8_block128(F.gelu(g, approximate='tanh') * u, down, out_dtype)
 
 
+def quantize_mxfp8(x):
+    """MXFP8 as the `mxfp8` recipe defines it (bongard/te_linear.py:32-39 -> Transformer Engine
+    MXFP8BlockScaling; OCP Microscaling v1.0): per 32 consecutive K elements a power-of-two scale
+    2^e with e = ceil(log2(amax / 448)) clamped to [-127, 127], values e4m3(x * 2^-e).
+    Returns (values as float32 holding exact E4M3 numbers, exponents int32 [rows, K/32])."""
+    rows, k = x.shape
+    blocks = x.float().view(rows, k // 32, 32)
+    amax = blocks.abs().amax(-1)
+    mant, ex = torch.frexp(amax / 448.0)              # amax/448 = mant * 2^ex, mant in [0.5, 1)
+    e = torch.where(mant == 0.5, ex - 1, ex)
+    e = torch.where(amax > 0, e, torch.full_like(e, -127)).clamp(-127, 127)
+    scaled = blocks * torch.exp2(-e.float())[..., None]
+    q = scaled.to(torch.float8_e4m3fn).float()
+    return q.view(rows, k), e.int()
+
+
+def dequantize_mxfp8(q, e):
+    rows, k = q.shape
+    return (q.view(rows, k // 32, 32) * torch.exp2(e.float())[..., None]).view(rows, k)
+
+
+def linear_mxfp8(x, weight, out_dtype=torch.bfloat16):
+    """y = dq(x) dq(w)^T in fp32 (products of E4M3 values and powers of two are exact; only the
+    accumulation order differs from the tensor core), rounded to the activation dtype."""
+    xq, xe = quantize_mxfp8(x)
+    wq, we = quantize_mxfp8(weight)
+    return (dequantize_mxfp8(xq, xe) @ dequantize_mxfp8(wq, we).t()).to(out_dtype)
+
+
+def geglu_mlp_mxfp8(x, gate, up, down, out_dtype=torch.bfloat16):
+    """gate|up in fp32 accumulators -> gelu_tanh(g) * u -> activation dtype -> down, as the fused GEMM does."""
+    xq, xe = quantize_mxfp8(x)
+    xd = dequantize_mxfp8(xq, xe)
+    g = xd @ dequantize_mxfp8(*quantize_mxfp8(gate)).t()
+    u = xd @ dequantize_mxfp8(*quantize_mxfp8(up)).t()
+    h = (F.gelu(g, approximate='tanh') * u).to(out_dtype)
+    return linear_mxfp8(h, down, out_dtype)
+
+
 # --------------------------------------------------------------------------------------
 # judgment head and probabilities
 # --------------------------------------------------------------------------------------
