@@ -49,7 +49,7 @@ def parse():
     ap.add_argument('--seed', type=int, default=None, help='default: 4 (judged), 5 (long)')
     ap.add_argument('--workload', default='judged', choices=['judged', 'long'],
                     help="judged: 512-8192-token states, 1-24 questions; long: 32768-token states x 64 questions")
-    ap.add_argument('--linears', default='bf16', choices=['bf16', 'fp8'], help='projection / MLP GEMM precision')
+    ap.add_argument('--linears', default='bf16', choices=['bf16', 'fp8', 'mxfp8'], help='projection / MLP GEMM precision')
     ap.add_argument('--cpu-seconds', type=float, default=15.0, help='CPU baseline budget per sample')
     ap.add_argument('--encoder-pack-tokens', type=int, default=65536)
     ap.add_argument('--decoder-pack-tokens', type=int, default=16384)
@@ -328,7 +328,7 @@ def run_b200(args):
             'e2e': {'value': total_questions * args.steps / (e2e_ms / 1e3), 'unit': UNIT,
                     'h2d_bytes_per_step': batch.h2d_bytes, 'd2h_bytes_per_step': int(host.numel() * 8)},
             'gpu_launches': int(launches),
-            'roofline': {'bound': 'tensor', 'kernel': 'gemm_bf16_pair_kernel' if args.linears == 'bf16' else 'gemm_fp8_kernel', 'achieved': achieved, 'peak': pk['sustained'],
+            'roofline': {'bound': 'tensor', 'kernel': {'bf16': 'gemm_bf16_pair_kernel', 'fp8': 'gemm_fp8_kernel', 'mxfp8': 'gemm_mxfp8_kernel'}[args.linears], 'achieved': achieved, 'peak': pk['sustained'],
                          'unit': 'TFLOP/s', 'frac': achieved / pk['sustained'], 'peak_source': pk['source'] + ' sustained',
                          'launches': gemm_launches, 'share_of_step': gemm_ms / device_ms,
                          'traffic': None if GEMM_TRAFFIC_PER_FLOP is None else GEMM_TRAFFIC_PER_FLOP * gemm_flops / gemm_launches},

@@ -36,6 +36,9 @@ SIGNATURES = {
     'bg_mxfp8_scale_bytes': ([I64, I64], I64),
     'bg_quantize_mxfp8': ([P, I64, P, I64, P, I64, I64, P], INT),
     'bg_gemm_mxfp8': ([P, I64, P, P, I64, P, P, I64, I64, I64, I64, INT, P], INT),
+    'bg_rmsnorm_mxfp8': ([P, I64, P, P, P, I64, I64, F32, P], INT),
+    'bg_add_rmsnorm_mxfp8': ([P, P, P, P, P, P, I64, I64, F32, P], INT),
+    'bg_gemm_mxfp8_geglu_q': ([P, I64, P, P, I64, P, P, I64, P, I64, I64, I64, P], INT),
     'bg_linear_fp8_workspace_bytes': ([I64, I64], I64),
     'bg_linear_fp8': ([P, I64, P, I64, P, P, I64, I64, I64, I64, INT, P, I64, P], INT),
     'bg_linear_fp8_static_max_bytes': ([], I64),

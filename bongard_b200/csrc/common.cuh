@@ -10,6 +10,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <cuda_fp8.h>
 #include <stdint.h>
 
 #define BG_OK 0
@@ -366,6 +367,28 @@ __device__ __forceinline__ float gelu_tanh(float x) {
     float inner = k0 * (x + k1 * x * x * x);
     return 0.5f * x * (1.0f + fast_tanh(inner));
 }
+// ---------------------------------------------------------------- MXFP8 (E4M3 with UE8M0 scales per 32 elements)
+constexpr int MX_ATOM = 512;      // bytes of one scale atom: 128 rows x 4 consecutive 32-element blocks
+__device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+    return lo | (hi << 16);
+}
+// e = ceil(log2(amax / 448)) in [-127, 127]: the smallest power of two that brings a block inside the E4M3 range
+__device__ __forceinline__ int mx_exponent(float amax) {
+    if (!(amax > 0.f)) return -127;
+    int ex;
+    const float mant = frexpf(amax * (1.f / 448.f), &ex);      // mant in [0.5, 1)
+    const int e = mant == 0.5f ? ex - 1 : ex;
+    return e < -127 ? -127 : (e > 127 ? 127 : e);
+}
+
+// Byte offset of the scale of (row, 32-element block kblock32) in the atom layout of a matrix with k_atoms
+// 128-element column blocks.
+__device__ __forceinline__ int64_t mx_scale_offset(int64_t row, int kblock32, int k_atoms) {
+    return ((row >> 7) * k_atoms + (kblock32 >> 2)) * MX_ATOM + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (kblock32 & 3);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

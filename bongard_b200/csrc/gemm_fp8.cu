@@ -238,11 +238,6 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 }
 
 // ---------------------------------------------------------------------------- quantisation
-__device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
-    __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
-    __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
-    return uint32_t(lo) | (uint32_t(hi) << 16);
-}
 
 // 1 x 128 blocks: a half-warp per block (16 lanes x 8 elements), two blocks per warp.
 __global__ void quantize_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, uint8_t* __restrict__ q,

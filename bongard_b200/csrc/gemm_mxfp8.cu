@@ -45,6 +45,8 @@ struct MxParams {
     __nv_bfloat16* out;
     const uint8_t* a_sf;    // [ceil(m / 128)][k / 128][512]
     const uint8_t* w_sf;    // [w_rows / 128][k / 128][512]
+    uint8_t* out_q;         // GeGLU epilogue only: emit the result as MXFP8 (values [m, n], row stride ldo bytes)
+    uint8_t* out_sf;        //   and its scale atoms [ceil(m / 128)][n / 128][512]; null -> bf16 output
     int tiles_m, tiles_n;
     int32_t* status;
 };
@@ -229,6 +231,45 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                         }
                     }
                 }
+            } else if (p.out_sf != nullptr) {
+                // GeGLU result straight to MXFP8: this thread holds 128 consecutive columns of its row, i.e.
+                // four 32-blocks = the four scale bytes of one word of the scale atom (row / 128, tn).  The
+                // product is rounded to bf16 first, so the values equal quantising the bf16 output afterwards.
+                uint8_t* dst = p.out_q + int64_t(row) * p.ldo + tn * 128;
+                uint32_t scale_word = 0;
+#pragma unroll 1
+                for (int c = 0; c < 128; c += 32) {
+                    uint32_t g[32], u[32];
+                    tmem_ld32(taddr + c, g);
+                    tmem_ld32(taddr + 128 + c, u);
+                    tmem_wait_ld();
+                    float h[32];
+                    float amax = 0.f;
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        h[e] = __bfloat162float(__float2bfloat16_rn(gelu_tanh(__uint_as_float(g[e])) * __uint_as_float(u[e])));
+                        amax = fmaxf(amax, fabsf(h[e]));
+                    }
+                    const int ex = mx_exponent(amax);
+                    const float inv = exp2f(float(-ex));
+                    scale_word |= uint32_t(ex + 127) << (8 * (c >> 5));
+                    if (row < p.m) {
+#pragma unroll
+                        for (int v = 0; v < 2; ++v) {
+                            uint4 o;
+                            o.x = e4m3x4(h[v * 16 + 0] * inv, h[v * 16 + 1] * inv, h[v * 16 + 2] * inv, h[v * 16 + 3] * inv);
+                            o.y = e4m3x4(h[v * 16 + 4] * inv, h[v * 16 + 5] * inv, h[v * 16 + 6] * inv, h[v * 16 + 7] * inv);
+                            o.z = e4m3x4(h[v * 16 + 8] * inv, h[v * 16 + 9] * inv, h[v * 16 + 10] * inv, h[v * 16 + 11] * inv);
+                            o.w = e4m3x4(h[v * 16 + 12] * inv, h[v * 16 + 13] * inv, h[v * 16 + 14] * inv, h[v * 16 + 15] * inv);
+                            *reinterpret_cast<uint4*>(dst + c + v * 16) = o;
+                        }
+                    }
+                }
+                if (row < p.m) {
+                    const int64_t atom = int64_t(row >> 7) * (p.n / 128) + tn;
+                    *reinterpret_cast<uint32_t*>(p.out_sf + atom * SF_ATOM + (row & 31) * 16 + ((row & 127) >> 5) * 4) =
+                        scale_word;
+                }
             } else {
                 const int col0 = tn * 128;
                 __nv_bfloat16* dst = p.out + int64_t(row) * p.ldo + col0;
@@ -275,41 +316,40 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     }
 }
 
-__device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
-    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
-    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
-    return lo | (hi << 16);
-}
-
-// One quarter-warp (8 lanes x 4 elements) per 32-element block; a warp covers 128 consecutive K elements of
-// one row, i.e. the four scale bytes that share a 32-bit word of the scale atom.
+// A half-warp (16 lanes x 8 elements, one 16-byte load each) covers 128 consecutive K elements of one row,
+// i.e. the four scale bytes that share a 32-bit word of the scale atom; four lanes share a 32-element block.
 __global__ void quantize_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, uint8_t* __restrict__ q,
                                       int64_t ldq, uint8_t* __restrict__ sf, int64_t rows, int kblocks) {
-    const int lane = threadIdx.x & 31;
-    const int64_t unit = int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);     // (row, 128-block)
+    const int lane = threadIdx.x & 31, l16 = lane & 15;
+    const int64_t unit = (int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 2 + (lane >> 4);
     const int64_t row = unit / kblocks;
     const int kb = int(unit % kblocks);
-    if (row >= rows) return;
-    const uint2 v = *reinterpret_cast<const uint2*>(x + row * ldx + kb * 128 + lane * 4);
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-    const float2 t0 = __bfloat1622float2(h[0]), t1 = __bfloat1622float2(h[1]);
-    float amax = fmaxf(fmaxf(fabsf(t0.x), fabsf(t0.y)), fmaxf(fabsf(t1.x), fabsf(t1.y)));
+    const bool active = row < rows;
+    float f[8];
+    float amax = 0.f;
+    if (active) {
+        const uint4 v = *reinterpret_cast<const uint4*>(x + row * ldx + kb * 128 + l16 * 8);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
-    for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    // e = ceil(log2(amax / 448)): the smallest power of two that brings the block inside the E4M3 range
-    int e = -127;
-    if (amax > 0.f) {
-        const float ratio = amax * (1.f / 448.f);
-        int ex;
-        const float mant = frexpf(ratio, &ex);          // ratio = mant * 2^ex, mant in [0.5, 1)
-        e = mant == 0.5f ? ex - 1 : ex;
-        e = e < -127 ? -127 : (e > 127 ? 127 : e);
+        for (int i = 0; i < 4; ++i) {
+            const float2 t = __bfloat1622float2(h[i]);
+            f[2 * i] = t.x;
+            f[2 * i + 1] = t.y;
+            amax = fmaxf(amax, fmaxf(fabsf(t.x), fabsf(t.y)));
+        }
     }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    if (!active) return;
+    const int e = mx_exponent(amax);
     const float inv = exp2f(float(-e));
-    *reinterpret_cast<uint32_t*>(q + row * ldq + kb * 128 + lane * 4) = e4m3x4(t0.x * inv, t0.y * inv, t1.x * inv, t1.y * inv);
-    if ((lane & 7) == 0) {
+    uint2 out;
+    out.x = e4m3x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
+    out.y = e4m3x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
+    *reinterpret_cast<uint2*>(q + row * ldq + kb * 128 + l16 * 8) = out;
+    if ((l16 & 3) == 0) {
         const int64_t atom = (row >> 7) * kblocks + kb;
-        sf[atom * SF_ATOM + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (lane >> 3)] = uint8_t(e + 127);
+        sf[atom * SF_ATOM + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (l16 >> 2)] = uint8_t(e + 127);
     }
 }
 
@@ -331,27 +371,48 @@ int64_t bg_mxfp8_scale_bytes(int64_t rows, int64_t k) { return ((rows + 127) / 1
 
 int bg_quantize_mxfp8(const void* x, int64_t ldx, void* q, int64_t ldq, void* scales, int64_t rows, int64_t k,
                       void* stream) {
-    if (rows < 0 || k <= 0 || k % 128 || ldx % 4 || ldq % 4) {
+    if (rows < 0 || k <= 0 || k % 128 || ldx % 8 || ldq % 8) {
         bg_set_error("bg_quantize_mxfp8: k must be a multiple of 128 (got %lld)", (long long)k);
         return BG_ERR_SHAPE;
     }
     if (rows == 0) return BG_OK;
     const int kblocks = int(k / 128);
     const int64_t units = rows * kblocks;
-    quantize_mxfp8_kernel<<<(unsigned)((units + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+    quantize_mxfp8_kernel<<<(unsigned)((units + 15) / 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __nv_bfloat16*>(x), ldx, static_cast<uint8_t*>(q), ldq, static_cast<uint8_t*>(scales), rows,
         kblocks);
     return launched("bg_quantize_mxfp8");
 }
 
+static int gemm_mxfp8_launch(const void* aq, int64_t lda, const void* a_scales, const void* wq, int64_t ldw,
+                             const void* w_scales, void* out, int64_t ldo, void* out_scales, int64_t m, int64_t n,
+                             int64_t k, int epilogue, void* stream);
+
 int bg_gemm_mxfp8(const void* aq, int64_t lda, const void* a_scales, const void* wq, int64_t ldw, const void* w_scales,
                   void* out, int64_t ldo, int64_t m, int64_t n, int64_t k, int epilogue, void* stream) {
+    return gemm_mxfp8_launch(aq, lda, a_scales, wq, ldw, w_scales, out, ldo, nullptr, m, n, k, epilogue, stream);
+}
+
+// The gate|up GEMM with the GeGLU epilogue writing MXFP8 (values + scale atoms) for the down projection.
+int bg_gemm_mxfp8_geglu_q(const void* aq, int64_t lda, const void* a_scales, const void* wq, int64_t ldw,
+                          const void* w_scales, void* out_q, int64_t ldq, void* out_scales, int64_t m, int64_t n,
+                          int64_t k, void* stream) {
+    if (out_scales == nullptr || ldq % 16 || (reinterpret_cast<uintptr_t>(out_scales) & 15)) {
+        bg_set_error("bg_gemm_mxfp8_geglu_q: the output needs a 16-byte aligned scale tensor and a row stride multiple of 16");
+        return BG_ERR_ALIGN;
+    }
+    return gemm_mxfp8_launch(aq, lda, a_scales, wq, ldw, w_scales, out_q, ldq, out_scales, m, n, k, 1, stream);
+}
+
+static int gemm_mxfp8_launch(const void* aq, int64_t lda, const void* a_scales, const void* wq, int64_t ldw,
+                             const void* w_scales, void* out, int64_t ldo, void* out_scales, int64_t m, int64_t n,
+                             int64_t k, int epilogue, void* stream) {
     if (m < 0 || n <= 0 || k <= 0 || (epilogue != 0 && epilogue != 1)) {
         bg_set_error("bg_gemm_mxfp8: bad shape");
         return BG_ERR_SHAPE;
     }
     if (m == 0) return BG_OK;
-    if (k % 128 || n % 128 || lda % 16 || ldw % 16 || ldo % 8) {
+    if (k % 128 || n % 128 || lda % 16 || ldw % 16 || (out_scales == nullptr && ldo % 8)) {
         bg_set_error("bg_gemm_mxfp8: k and n must be multiples of 128 (got k=%lld n=%lld)", (long long)k, (long long)n);
         return BG_ERR_SHAPE;
     }
@@ -374,6 +435,8 @@ int bg_gemm_mxfp8(const void* aq, int64_t lda, const void* a_scales, const void*
     MxParams p;
     p.m = (int)m; p.n = (int)n; p.k = (int)k; p.epilogue = epilogue; p.ldo = ldo;
     p.out = static_cast<__nv_bfloat16*>(out);
+    p.out_q = static_cast<uint8_t*>(out);
+    p.out_sf = static_cast<uint8_t*>(out_scales);
     p.a_sf = static_cast<const uint8_t*>(a_scales);
     p.w_sf = static_cast<const uint8_t*>(w_scales);
     p.tiles_m = (int)((m + BM - 1) / BM);

@@ -39,11 +39,33 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return warp_sum(t);
 }
 
+// Store 8 consecutive values of a row (columns c..c+7, already rounded to bf16) as MXFP8: the four threads
+// that share a 32-element block agree on its power-of-two scale through two shuffles.  Every thread of the
+// warp must call this (inactive ones with zeros).
+__device__ __forceinline__ void store_mxfp8(const float* f, bool active, uint8_t* q, uint8_t* sf, int64_t row, int c,
+                                            int h) {
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    if (!active) return;
+    const int e = mx_exponent(amax);
+    const float inv = exp2f(float(-e));
+    uint2 o;
+    o.x = e4m3x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
+    o.y = e4m3x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
+    *reinterpret_cast<uint2*>(q + row * h + c) = o;
+    if ((c & 31) == 0) sf[mx_scale_offset(row, c >> 5, h >> 7)] = uint8_t(e + 127);
+}
+
 // out = rmsnorm(x) * (1 + w).  One block per row, one 16-byte chunk per thread.
 // Restates transformers T5Gemma2RMSNorm (modeling_t5gemma2.py:61-69): fp32 math, the gain is
 // applied before the result is rounded to bf16.
+// With out_q / out_sf the result is written as MXFP8 (contiguous [rows, h] values + scale atoms) instead of bf16.
 __global__ void rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const __nv_bfloat16* __restrict__ w,
-                               __nv_bfloat16* __restrict__ out, int64_t ldo, int h, float eps) {
+                               __nv_bfloat16* __restrict__ out, int64_t ldo, int h, float eps,
+                               uint8_t* __restrict__ out_q, uint8_t* __restrict__ out_sf) {
     __shared__ float scratch[33];
     const int64_t row = blockIdx.x;
     const int c = threadIdx.x * 8;
@@ -61,7 +83,12 @@ __global__ void rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx,
         unpack8(*reinterpret_cast<const uint4*>(w + c), g);
 #pragma unroll
         for (int i = 0; i < 8; ++i) f[i] = f[i] * r * (1.f + g[i]);
-        *reinterpret_cast<uint4*>(out + row * ldo + c) = pack8(f);
+        if (out_q == nullptr) *reinterpret_cast<uint4*>(out + row * ldo + c) = pack8(f);
+    }
+    if (out_q != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = active ? round_bf16(f[i]) : 0.f;
+        store_mxfp8(f, active, out_q, out_sf, row, c, h);
     }
 }
 
@@ -73,7 +100,8 @@ __global__ void rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx,
 // w_next == nullptr skips the second norm.
 __global__ void add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ w_post,
                                    __nv_bfloat16* __restrict__ resid, const __nv_bfloat16* __restrict__ w_next,
-                                   __nv_bfloat16* __restrict__ normed, int h, float eps) {
+                                   __nv_bfloat16* __restrict__ normed, int h, float eps,
+                                   uint8_t* __restrict__ normed_q, uint8_t* __restrict__ normed_sf) {
     __shared__ float scratch[33];
     const int64_t row = blockIdx.x;
     const int c = threadIdx.x * 8;
@@ -111,7 +139,12 @@ __global__ void add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ y, const __
         unpack8(*reinterpret_cast<const uint4*>(w_next + c), g);
 #pragma unroll
         for (int i = 0; i < 8; ++i) x[i] = x[i] * r * (1.f + g[i]);
-        *reinterpret_cast<uint4*>(normed + row * h + c) = pack8(x);
+        if (normed_q == nullptr) *reinterpret_cast<uint4*>(normed + row * h + c) = pack8(x);
+    }
+    if (normed_q != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = active ? round_bf16(x[i]) : 0.f;
+        store_mxfp8(x, active, normed_q, normed_sf, row, c, h);
     }
 }
 
@@ -400,8 +433,21 @@ int bg_rmsnorm(const void* x, int64_t ldx, const void* w, void* out, int64_t ldo
     if (rows == 0) return BG_OK;
     rmsnorm_kernel<<<(unsigned)rows, row_threads(h), 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(w),
-        static_cast<__nv_bfloat16*>(out), ldo, (int)h, eps);
+        static_cast<__nv_bfloat16*>(out), ldo, (int)h, eps, nullptr, nullptr);
     return check_launch("bg_rmsnorm");
+}
+
+int bg_rmsnorm_mxfp8(const void* x, int64_t ldx, const void* w, void* out_q, void* out_scales, int64_t rows, int64_t h,
+                     float eps, void* stream) {
+    if (rows < 0 || h <= 0 || h % 128 || h > 8192 || ldx % 8) {
+        bg_set_error("bg_rmsnorm_mxfp8: hidden size must be a multiple of 128 up to 8192 (got %lld)", (long long)h);
+        return BG_ERR_SHAPE;
+    }
+    if (rows == 0) return BG_OK;
+    rmsnorm_kernel<<<(unsigned)rows, row_threads(h), 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(w), nullptr, 0, (int)h, eps,
+        static_cast<uint8_t*>(out_q), static_cast<uint8_t*>(out_scales));
+    return check_launch("bg_rmsnorm_mxfp8");
 }
 
 int bg_add_rmsnorm(const void* y, const void* w_post, void* resid, const void* w_next, void* normed, int64_t rows,
@@ -414,8 +460,22 @@ int bg_add_rmsnorm(const void* y, const void* w_post, void* resid, const void* w
     add_rmsnorm_kernel<<<(unsigned)rows, row_threads(h), 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(w_post),
         static_cast<__nv_bfloat16*>(resid), static_cast<const __nv_bfloat16*>(w_next),
-        static_cast<__nv_bfloat16*>(normed), (int)h, eps);
+        static_cast<__nv_bfloat16*>(normed), (int)h, eps, nullptr, nullptr);
     return check_launch("bg_add_rmsnorm");
+}
+
+int bg_add_rmsnorm_mxfp8(const void* y, const void* w_post, void* resid, const void* w_next, void* normed_q,
+                         void* normed_scales, int64_t rows, int64_t h, float eps, void* stream) {
+    if (rows < 0 || h <= 0 || h % 128 || h > 8192 || w_next == nullptr) {
+        bg_set_error("bg_add_rmsnorm_mxfp8: hidden size must be a multiple of 128 up to 8192 (got %lld)", (long long)h);
+        return BG_ERR_SHAPE;
+    }
+    if (rows == 0) return BG_OK;
+    add_rmsnorm_kernel<<<(unsigned)rows, row_threads(h), 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(w_post),
+        static_cast<__nv_bfloat16*>(resid), static_cast<const __nv_bfloat16*>(w_next), nullptr, (int)h, eps,
+        static_cast<uint8_t*>(normed_q), static_cast<uint8_t*>(normed_scales));
+    return check_launch("bg_add_rmsnorm_mxfp8");
 }
 
 static int qk_norm_rope_launch(void* q, int64_t ldq, int q_heads, void* k, int64_t ldk, int k_heads,

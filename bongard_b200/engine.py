@@ -32,7 +32,7 @@ BF16 = torch.bfloat16
 
 @dataclass
 class LayerWeights:
-    wqkv: object             # bf16 tensors, or ops.Fp8Weight under linears='fp8'
+    wqkv: object             # bf16 tensors, ops.Fp8Weight under linears='fp8', ops.Mxfp8Tensor under 'mxfp8'
     wkv: object              # the k|v rows of wqkv (decoder: projects the shared state)
     wo: object
     wgu: object
@@ -45,9 +45,10 @@ class LayerWeights:
     k_norm: torch.Tensor
 
 
-def _stack_layer(w, prefix, device, fp8=False, state_kv=False):
+def _stack_layer(w, prefix, device, linears='bf16', state_kv=False):
     g = lambda name: w[prefix + name].to(device=device, dtype=BF16)   # noqa: E731
-    conv = ops.quantize_weight if fp8 else (lambda t: t)
+    fp8 = linears != 'bf16'
+    conv = {'bf16': lambda t: t, 'fp8': ops.quantize_weight, 'mxfp8': ops.quantize_mxfp8}[linears]
     wqkv = torch.cat([g('self_attn.q_proj.weight'), g('self_attn.k_proj.weight'), g('self_attn.v_proj.weight')]).contiguous()
     q_rows = w[prefix + 'self_attn.q_proj.weight'].shape[0]
     return LayerWeights(
@@ -67,9 +68,9 @@ class JudgmentEngine:
     def __init__(self, weights, shape: ModelShape, device='cuda', *, encoder_pack_tokens=65536,
                  decoder_pack_tokens=16384, linears='bf16'):
         ops.device_check()
-        if linears not in ('bf16', 'fp8'):
-            raise ValueError("linears must be 'bf16' or 'fp8'")
-        self.linears, fp8 = linears, linears == 'fp8'
+        if linears not in ('bf16', 'fp8', 'mxfp8'):
+            raise ValueError("linears must be 'bf16', 'fp8' or 'mxfp8'")
+        self.linears, fp8 = linears, linears
         self.shape, self.device = shape, torch.device(device)
         self.encoder_pack_tokens, self.decoder_pack_tokens = encoder_pack_tokens, decoder_pack_tokens
         g = lambda name: weights[name].to(device=self.device, dtype=BF16).contiguous()   # noqa: E731
@@ -186,6 +187,8 @@ class JudgmentEngine:
     def _lin(self, x, w, geglu=False):
         if isinstance(w, ops.Fp8Weight):
             return ops.linear_fp8(x, w, geglu=geglu)
+        if isinstance(w, ops.Mxfp8Tensor):
+            return ops.linear_mxfp8(x, w, geglu=geglu)
         few = self.few_rows_kernels
         return ops.linear_geglu(x, w, few_rows=few) if geglu else ops.linear(x, w, few_rows=few)
 
@@ -193,13 +196,14 @@ class JudgmentEngine:
         s = self.shape
         scale = self.embed_scale_enc if layers is self.enc else self.embed_scale_dec
         x = ops.embed(pack.ids, self.table, self.eoi, scale, s.eoi_token)
-        n = ops.rmsnorm(x, layers[0].pre_attn, s.eps)
+        mx = self.linears == 'mxfp8'          # norms hand the GEMMs MXFP8 directly: no bf16 copy of a normed row
+        n = ops.rmsnorm_mxfp8(x, layers[0].pre_attn, s.eps) if mx else ops.rmsnorm(x, layers[0].pre_attn, s.eps)
         t = x.shape[0]
         qd, kd = s.q_dim, s.kv_dim
         self.launches += 2
         for index, lw in enumerate(layers):
             fused = (self.fuse_qkv_rope and pack.longest > 0 and not self.few_rows_kernels
-                     and not isinstance(lw.wqkv, ops.Fp8Weight))
+                     and isinstance(lw.wqkv, torch.Tensor))
             if fused:
                 # QK-norm + RoPE ride in the projection's epilogue: one pass less over q and k
                 table = ops.rope_table(s.head_dim, s.layer_theta(index), pack.longest, self.device)
@@ -214,11 +218,15 @@ class JudgmentEngine:
             a = ops.varlen_attention(q, k, v, pack.plans[pack.keys[index]], s.scale,
                                      None if cross is None else cross[index])
             o = self._lin(a, lw.wo)
-            n2 = ops.add_rmsnorm_(o, lw.post_attn, x, lw.pre_ffn, s.eps)
-            h = self._lin(n2, lw.wgu, geglu=True)
-            d = self._lin(h, lw.wdown)
-            nxt = layers[index + 1].pre_attn if index + 1 < len(layers) else final_norm
-            n = ops.add_rmsnorm_(d, lw.post_ffn, x, nxt, s.eps)
+            n2 = (ops.add_rmsnorm_mxfp8_ if mx else ops.add_rmsnorm_)(o, lw.post_attn, x, lw.pre_ffn, s.eps)
+            if isinstance(lw.wgu, ops.Mxfp8Tensor):
+                d = ops.mlp_mxfp8(n2, lw.wgu, lw.wdown)        # the hidden activation stays MXFP8
+            else:
+                h = self._lin(n2, lw.wgu, geglu=True)
+                d = self._lin(h, lw.wdown)
+            last = index + 1 == len(layers)
+            nxt = final_norm if last else layers[index + 1].pre_attn
+            n = (ops.add_rmsnorm_mxfp8_ if mx and not last else ops.add_rmsnorm_)(d, lw.post_ffn, x, nxt, s.eps)
             self.launches += 7 if fused else 8
         return n
 
@@ -227,6 +235,8 @@ class JudgmentEngine:
         V = v_proj(state) (bongard/model.py:135-139)."""
         s = self.shape
         out = []
+        if self.linears == 'mxfp8':
+            state = ops.quantize_mxfp8(state)          # one quantisation serves every layer's projection
         for lw in self.dec:
             kv = self._lin(state, lw.wkv)
             k = kv[:, :s.kv_dim].view(-1, s.kv_heads, s.head_dim)

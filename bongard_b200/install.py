@@ -18,8 +18,8 @@ from .te_linear import B200MLP
 def install_b200_inference(model, *, linears='bf16'):
     """Swap the hot path of `model` (a JudgmentModel-like object with `.backbone`, or the
     Hugging Face T5Gemma2Model itself) to the B200 kernels.  Returns substitution counts."""
-    if linears not in ('bf16', 'fp8'):
-        raise ValueError("linears must be 'bf16' or 'fp8'")
+    if linears not in ('bf16', 'fp8', 'mxfp8'):
+        raise ValueError("linears must be 'bf16', 'fp8' or 'mxfp8'")
     ops.device_check()
     backbone = model.backbone if hasattr(model, 'backbone') else model
     counts = dict(encoder_attention=0, decoder_attention=0, mlp=0, norms=0)

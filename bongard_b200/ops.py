@@ -776,9 +776,69 @@ def gemm_mxfp8(a: Mxfp8Tensor, weight: Mxfp8Tensor, *, geglu=False):
     return out
 
 
+def _mx_empty(rows, k, device):
+    lib = _lib.load()
+    return Mxfp8Tensor(torch.empty((rows, k), device=device, dtype=torch.uint8),
+                       torch.zeros(lib.bg_mxfp8_scale_bytes(rows, k), device=device, dtype=torch.uint8))
+
+
+def rmsnorm_mxfp8(x, weight, eps=1e-6):
+    """rmsnorm(x) * (1 + weight) written as MXFP8 for the GEMM that consumes it."""
+    lib = _lib.load()
+    flat, rows, h, ldx = _rows(x, 'x')
+    out = _mx_empty(rows, h, x.device)
+    _lib.check(lib.bg_rmsnorm_mxfp8(_ptr(flat), ldx, _ptr(_need(weight, 'weight')), _ptr(out.q), _ptr(out.scales), rows,
+                                    h, eps, _stream()), 'bg_rmsnorm_mxfp8')
+    return out
+
+
+def add_rmsnorm_mxfp8_(y, w_post, resid, w_next, eps=1e-6):
+    """add_rmsnorm_ whose normalised output is MXFP8."""
+    lib = _lib.load()
+    _need(y, 'y'), _need(resid, 'resid')
+    if not (y.is_contiguous() and resid.is_contiguous()) or y.shape != resid.shape:
+        raise ValueError('y and resid must be contiguous and of equal shape')
+    h = y.shape[-1]
+    rows = y.numel() // h
+    out = _mx_empty(rows, h, y.device)
+    _lib.check(lib.bg_add_rmsnorm_mxfp8(_ptr(y), _ptr(_need(w_post, 'w_post')), _ptr(resid), _ptr(_need(w_next, 'w_next')),
+                                        _ptr(out.q), _ptr(out.scales), rows, h, eps, _stream()), 'bg_add_rmsnorm_mxfp8')
+    return out
+
+
+def gemm_mxfp8_geglu_q(a: Mxfp8Tensor, gate_up: Mxfp8Tensor):
+    """gelu_tanh(a gate^T) * (a up^T) written directly as MXFP8 for the down projection."""
+    lib = _lib.load()
+    m, k = a.shape
+    n = gate_up.shape[0] // 2
+    if gate_up.shape[1] != k:
+        raise ValueError(f'weight has K={gate_up.shape[1]}, input has {k}')
+    q = torch.empty((m, n), device=a.q.device, dtype=torch.uint8)
+    scales = torch.zeros(lib.bg_mxfp8_scale_bytes(m, n), device=a.q.device, dtype=torch.uint8)
+    timer = GEMM_TIMER
+    begin = timer.start() if timer is not None else None
+    _lib.check(lib.bg_gemm_mxfp8_geglu_q(_ptr(a.q), k, _ptr(a.scales), _ptr(gate_up.q), k, _ptr(gate_up.scales), _ptr(q),
+                                         n, _ptr(scales), m, n, k, _stream()), 'bg_gemm_mxfp8_geglu_q')
+    if timer is not None:
+        timer.stop(begin, 4 * m * n * k)
+    return Mxfp8Tensor(q, scales)
+
+
+def mlp_mxfp8(x, gate_up: Mxfp8Tensor, down: Mxfp8Tensor):
+    """The gated MLP on MXFP8 weights: quantise x, gate|up GEMM with the GeGLU epilogue emitting MXFP8,
+    down GEMM.  The hidden activation never exists in bf16."""
+    if isinstance(x, Mxfp8Tensor):
+        return gemm_mxfp8(gemm_mxfp8_geglu_q(x, gate_up), down)
+    flat, m, k, _ = _rows(x, 'x')
+    out = gemm_mxfp8(gemm_mxfp8_geglu_q(quantize_mxfp8(flat), gate_up), down)
+    return out.view(*x.shape[:-1], out.shape[-1])
+
+
 def linear_mxfp8(x, weight: Mxfp8Tensor, *, geglu=False):
     """bf16 x [..., K] times an MXFP8 weight: dynamic 1 x 32 power-of-two activation scales, block-scaled
     tensor-core contraction, bf16 result."""
+    if isinstance(x, Mxfp8Tensor):
+        return gemm_mxfp8(x, weight, geglu=geglu)
     out = gemm_mxfp8(quantize_mxfp8(x), weight, geglu=geglu)
     return out.view(*x.shape[:-1], out.shape[-1])
 

@@ -5,8 +5,9 @@ every text layer's MLP and / or attention projections and returns converted-modu
 `B200Linear` serves one or more stacked Hugging Face linears of the same input with ONE GEMM
 (the reference's TELinear, 41-77), `B200MLP` runs gate_up -> GeGLU -> down as two GEMMs
 (the reference's TEMLP, 79-103) with the activation fused into the first GEMM's epilogue.
-Recipes here: 'bf16' (what the reference serves in eval mode, 61-62) and 'fp8' (E4M3 with
-dynamic per-128 block scales).  Unlike the reference's modules these run the low-precision
+Recipes here: 'bf16' (what the reference serves in eval mode, 61-62), 'fp8' (E4M3 with dynamic
+per-128 block scales) and 'mxfp8' (E4M3 with power-of-two scales per 32 elements, scaled inside the
+tensor core - the reference's recipe of the same name, 32-39).  Unlike the reference's modules these run the low-precision
 recipe in eval mode too: that is the point of an inference kernel library.
 """
 
@@ -19,7 +20,7 @@ from torch import nn
 
 from . import ops
 
-RECIPES = ('bf16', 'fp8')
+RECIPES = ('bf16', 'fp8', 'mxfp8')
 ATTENTION_PROJECTIONS = ('q_proj', 'k_proj', 'v_proj', 'o_proj')
 
 
@@ -48,7 +49,8 @@ class B200Linear(nn.Module):
         key = (self.weight.data_ptr(), self.weight._version)
         if self._cache is None or self._cache[0] != key:
             w = self.weight.detach().to(torch.bfloat16).contiguous()
-            self._cache = (key, ops.quantize_weight(w) if self.bongard_recipe == 'fp8' else w)
+            prepare = {'bf16': lambda t: t, 'fp8': ops.quantize_weight, 'mxfp8': ops.quantize_mxfp8}[self.bongard_recipe]
+            self._cache = (key, prepare(w))
             self.counts['weight_preparations'] += 1
         return self._cache[1]
 
@@ -57,12 +59,14 @@ class B200Linear(nn.Module):
             # train mode: the reference goes through autograd here (bongard/te_linear.py:63-77); the bf16
             # recipe records a tensor-core backward, the fp8 recipe is an inference recipe
             if self.bongard_recipe != 'bf16':
-                raise ValueError("the 'fp8' recipe is forward-only; train with recipe 'bf16'")
+                raise ValueError(f"the '{self.bongard_recipe}' recipe is forward-only; train with recipe 'bf16'")
             w = self.weight if self.weight.dtype == torch.bfloat16 else self.weight.to(torch.bfloat16)
             return ops.linear_geglu_autograd(x, w) if geglu else ops.linear_autograd(x, w)
         w = self._operand()
         if self.bongard_recipe == 'fp8':
             return ops.linear_fp8(x, w, geglu=geglu)
+        if self.bongard_recipe == 'mxfp8':
+            return ops.linear_mxfp8(x, w, geglu=geglu)
         return ops.linear_geglu(x, w) if geglu else ops.linear(x, w)
 
 
@@ -81,6 +85,9 @@ class B200MLP(nn.Module):
         self.down = B200Linear([mlp.down_proj], recipe)
 
     def forward(self, x):
+        if self.bongard_recipe == 'mxfp8' and not (self.training and torch.is_grad_enabled() and x.requires_grad):
+            # the hidden activation goes from the GeGLU epilogue to the down projection as MXFP8
+            return ops.mlp_mxfp8(x, self.gate_up._operand(), self.down._operand())
         return self.down(self.gate_up(x, geglu=True))
 
 

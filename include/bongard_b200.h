@@ -170,6 +170,19 @@ int bg_quantize_mxfp8(const void* x, int64_t ldx, void* q, int64_t ldq, void* sc
                       void* stream);
 int bg_gemm_mxfp8(const void* aq, int64_t lda, const void* a_scales, const void* wq, int64_t ldw, const void* w_scales,
                   void* out, int64_t ldo, int64_t m, int64_t n, int64_t k, int epilogue, void* stream);
+/* bg_rmsnorm / bg_add_rmsnorm writing the normalised rows as MXFP8 (contiguous uint8 [rows, h] + scale atoms of
+ * a [rows, h] matrix, zero-filled by the caller) for the GEMM that consumes them; values equal
+ * bg_quantize_mxfp8 of the bf16 result.  h a multiple of 128. */
+int bg_rmsnorm_mxfp8(const void* x, int64_t ldx, const void* w, void* out_q, void* out_scales, int64_t rows, int64_t h,
+                     float eps, void* stream);
+int bg_add_rmsnorm_mxfp8(const void* y, const void* w_post, void* resid, const void* w_next, void* normed_q,
+                         void* normed_scales, int64_t rows, int64_t h, float eps, void* stream);
+/* bg_gemm_mxfp8 with the GeGLU epilogue, writing its result as MXFP8 (out_q uint8 [m, n], row stride ldq
+ * bytes, out_scales in the atom layout of a [m, n] matrix, zero-filled by the caller) instead of bf16:
+ * the values equal bg_quantize_mxfp8 of the bf16 result, without the two extra passes over it. */
+int bg_gemm_mxfp8_geglu_q(const void* aq, int64_t lda, const void* a_scales, const void* wq, int64_t ldw,
+                          const void* w_scales, void* out_q, int64_t ldq, void* out_scales, int64_t m, int64_t n,
+                          int64_t k, void* stream);
 
 /* bg_linear_fp8 for callers that cannot supply scratch memory.  (No counterpart in the reference.)
  * The quantised activations go to a fixed buffer inside the library instead of a caller-owned

@@ -61,3 +61,61 @@ def test_geglu_mxfp8(m, i, k):
     ops.read_status()
     want = om.geglu_mlp_mxfp8(x, gate, up, down)
     assert float((y.float().cpu() - want.float()).abs().max()) <= 3e-2 * float(want.float().abs().max()) + 1e-3
+
+
+def test_engine_with_mxfp8_linears_stays_close_to_bf16():
+    from bongard_b200 import workload as wl
+    from bongard_b200.engine import JudgmentEngine
+
+    weights = wl.make_weights(wl.TINY, 1, norm_std=0.1)
+    requests = wl.tiny_requests(1)
+    ref = torch.cat([p for a in JudgmentEngine(weights, wl.TINY).judge(requests) for p in a.values()])
+    got = torch.cat([p for a in JudgmentEngine(weights, wl.TINY, linears='mxfp8').judge(requests) for p in a.values()])
+    assert torch.isfinite(got).all()
+    assert float((got - ref).abs().max()) < 0.05
+
+
+@pytest.mark.parametrize('m,i,k', [(5, 1024, 256), (700, 10240, 2560)])
+def test_geglu_epilogue_emits_the_same_mxfp8_as_quantising_its_bf16_output(m, i, k):
+    x = rnd(m, k, seed=8)
+    gate_up = ops.quantize_mxfp8(rnd(2 * i, k, seed=9, std=0.02).to(DEV))
+    a = ops.quantize_mxfp8(x.to(DEV))
+    fused = ops.gemm_mxfp8_geglu_q(a, gate_up)
+    two_pass = ops.quantize_mxfp8(ops.gemm_mxfp8(a, gate_up, geglu=True))
+    ops.read_status()
+    assert torch.equal(fused.q, two_pass.q) and torch.equal(fused.scales, two_pass.scales)
+
+
+@pytest.mark.parametrize('rows,h', [(3, 256), (300, 2560)])
+def test_norm_kernels_emit_the_same_mxfp8_as_quantising_their_bf16_output(rows, h):
+    x, y = rnd(rows, h, seed=10).to(DEV), rnd(rows, h, seed=11).to(DEV)
+    w1, w2 = rnd(h, seed=12, std=0.1).to(DEV), rnd(h, seed=13, std=0.1).to(DEV)
+    a = ops.rmsnorm_mxfp8(x, w1)
+    b = ops.quantize_mxfp8(ops.rmsnorm(x, w1))
+    assert torch.equal(a.q, b.q) and torch.equal(a.scales, b.scales)
+    r1, r2 = x.clone(), x.clone()
+    c = ops.add_rmsnorm_mxfp8_(y, w1, r1, w2)
+    d = ops.quantize_mxfp8(ops.add_rmsnorm_(y, w1, r2, w2))
+    ops.read_status()
+    assert torch.equal(r1, r2) and torch.equal(c.q, d.q) and torch.equal(c.scales, d.scales)
+
+
+def test_converted_modules_with_the_mxfp8_recipe():
+    """enable_te_linear / enable_fused_mlp with recipe 'mxfp8' on the Hugging Face backbone."""
+    from bongard_b200 import workload as wl
+    from bongard_b200.fused_mlp import enable_fused_mlp
+    from bongard_b200.hf import build_backbone
+    from bongard_b200.te_linear import enable_te_linear
+
+    weights = wl.make_weights(wl.TINY, 1, norm_std=0.1)
+    x = rnd(2, 40, wl.TINY.hidden, seed=20).to(DEV)
+    with torch.no_grad():
+        native = build_backbone(wl.TINY, weights)
+        layer = native.decoder.layers[0]
+        want = layer.mlp(layer.pre_feedforward_layernorm(x)).float()
+        for convert in (lambda b: enable_te_linear(b, mlp='mxfp8'), lambda b: enable_fused_mlp(b, 'mxfp8')):
+            backbone = build_backbone(wl.TINY, weights)
+            convert(backbone)
+            layer = backbone.decoder.layers[0]
+            got = layer.mlp(layer.pre_feedforward_layernorm(x)).float()
+            assert float((got - want).abs().max()) < 0.08 * float(want.abs().max())
