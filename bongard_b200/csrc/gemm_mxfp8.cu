@@ -35,7 +35,7 @@ constexpr int TILE_BYTES = A_BYTES + B_BYTES;
 constexpr int SF_OFFSET = STAGES * TILE_BYTES;
 constexpr int BAR_OFFSET = SF_OFFSET + STAGES * SF_BYTES;
 constexpr int SMEM_BYTES = BAR_OFFSET + 256 + 1024;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;     // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue (two per TMEM lane quadrant)
 constexpr int GROUP_M = 16;
 constexpr int TMEM_SF = 256;      // scale columns behind the 256-column accumulator: per ring parity A at +0, W at +16
 
@@ -117,7 +117,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             mbar_init(&empty[s], 1);
         }
         mbar_init(acc_full, 1);
-        mbar_init(acc_empty, 4);
+        mbar_init(acc_empty, 8);
         mbar_fence_init();
         tma_prefetch_desc(&map_a);
         tma_prefetch_desc(&map_w);
@@ -198,8 +198,11 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             }
         }
     } else {
-        // ------------------------------------------------------------ epilogue (warps 2..5)
+        // ------------------------------------------------------------ epilogue (warps 2..9)
+        // The accumulator is single-buffered, so the epilogue is exposed: two warps per lane quadrant, each
+        // draining half of the columns, halve it.
         const int part = warp & 3;
+        const int half = (warp - 2) >> 2;
         const int row_in_tile = part * 32 + lane;
         int local = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
@@ -213,7 +216,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 const int col0 = tn * BN;
                 __nv_bfloat16* dst = p.out + int64_t(row) * p.ldo + col0;
 #pragma unroll 1
-                for (int c = 0; c < BN; c += 32) {
+                for (int c = half * (BN / 2); c < (half + 1) * (BN / 2); c += 32) {
                     uint32_t r[32];
                     tmem_ld32(taddr + c, r);
                     tmem_wait_ld();
@@ -232,13 +235,13 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     }
                 }
             } else if (p.out_sf != nullptr) {
-                // GeGLU result straight to MXFP8: this thread holds 128 consecutive columns of its row, i.e.
-                // four 32-blocks = the four scale bytes of one word of the scale atom (row / 128, tn).  The
-                // product is rounded to bf16 first, so the values equal quantising the bf16 output afterwards.
+                // GeGLU result straight to MXFP8: a row's 128 columns of this tile are four 32-blocks = the four
+                // scale bytes of one word of the scale atom (row / 128, tn); this warp writes its half of them.
+                // The product is rounded to bf16 first, so the values equal quantising the bf16 output afterwards.
                 uint8_t* dst = p.out_q + int64_t(row) * p.ldo + tn * 128;
                 uint32_t scale_word = 0;
 #pragma unroll 1
-                for (int c = 0; c < 128; c += 32) {
+                for (int c = half * 64; c < (half + 1) * 64; c += 32) {
                     uint32_t g[32], u[32];
                     tmem_ld32(taddr + c, g);
                     tmem_ld32(taddr + 128 + c, u);
@@ -252,7 +255,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     }
                     const int ex = mx_exponent(amax);
                     const float inv = exp2f(float(-ex));
-                    scale_word |= uint32_t(ex + 127) << (8 * (c >> 5));
+                    scale_word |= uint32_t(ex + 127) << (8 * ((c >> 5) & 1));
                     if (row < p.m) {
 #pragma unroll
                         for (int v = 0; v < 2; ++v) {
@@ -267,14 +270,15 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 }
                 if (row < p.m) {
                     const int64_t atom = int64_t(row >> 7) * (p.n / 128) + tn;
-                    *reinterpret_cast<uint32_t*>(p.out_sf + atom * SF_ATOM + (row & 31) * 16 + ((row & 127) >> 5) * 4) =
-                        scale_word;
+                    // this warp's two 32-blocks are half of the row's scale word
+                    *reinterpret_cast<uint16_t*>(p.out_sf + atom * SF_ATOM + (row & 31) * 16 + ((row & 127) >> 5) * 4 +
+                                                 half * 2) = uint16_t(scale_word);
                 }
             } else {
                 const int col0 = tn * 128;
                 __nv_bfloat16* dst = p.out + int64_t(row) * p.ldo + col0;
 #pragma unroll 1
-                for (int c = 0; c < 128; c += 32) {
+                for (int c = half * 64; c < (half + 1) * 64; c += 32) {
                     uint32_t g[32], u[32];
                     tmem_ld32(taddr + c, g);
                     tmem_ld32(taddr + 128 + c, u);
