@@ -119,3 +119,16 @@ def test_converted_modules_with_the_mxfp8_recipe():
             layer = backbone.decoder.layers[0]
             got = layer.mlp(layer.pre_feedforward_layernorm(x)).float()
             assert float((got - want).abs().max()) < 0.08 * float(want.abs().max())
+
+
+def test_mxfp8_rejects_bad_shapes_and_handles_empty_input():
+    w = ops.quantize_mxfp8(rnd(256, 256, seed=30).to(DEV))
+    with pytest.raises(ValueError):
+        ops.quantize_mxfp8(rnd(4, 200, seed=31).to(DEV))                     # K not a multiple of 128
+    with pytest.raises(ValueError):
+        ops.gemm_mxfp8(ops.quantize_mxfp8(rnd(4, 128, seed=32).to(DEV)), w)   # K mismatch
+    empty = ops.linear_mxfp8(torch.zeros(0, 256, device=DEV, dtype=torch.bfloat16), w)
+    assert empty.shape == (0, 256)
+    # an all-zero activation quantises to zeros with the smallest scale and gives an all-zero product
+    z = ops.linear_mxfp8(torch.zeros(3, 256, device=DEV, dtype=torch.bfloat16), w)
+    assert float(z.abs().max()) == 0
