@@ -91,7 +91,14 @@ int32_t* bg_status_word() {
     return ptr;
 }
 
+static int g_programmatic_launch = 0;
+int bg_programmatic_launch() { return g_programmatic_launch; }
+
 extern "C" {
+
+// 1: launch the kernels of the serving chain (GEMMs, attention, norms, head) with programmatic stream
+// serialization, so that a kernel's prologue overlaps the tail of its predecessor; 0 (default): plain launches.
+void bg_set_programmatic_launch(int enable) { g_programmatic_launch = enable ? 1 : 0; }
 
 const char* bg_last_error_string() { return g_error; }
 

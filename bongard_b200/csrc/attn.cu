@@ -88,6 +88,10 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const int kvh = blockIdx.y;
     const int G = p.q_heads / p.kv_heads;
 
+    // Programmatic dependent launch: wait for the predecessor before the first global read (the tile record);
+    // the successor may start its own prologue right away.
+    pdl_wait();
+    pdl_launch_dependents();
     const int32_t* t = p.tiles + int64_t(blockIdx.x) * 8;
     const int q_start = t[0], q_count = t[1], own_lo = t[2], own_hi = t[3], lo_max = t[4], hi_min = t[5];
     const int pre_start = t[6], pre_len = t[7];
@@ -344,8 +348,8 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
         configured = true;
     }
     dim3 grid((unsigned)n_tiles, (unsigned)p.kv_heads);
-    varlen_attention_kernel<D><<<grid, THREADS, Smem<D>::TOTAL, stream>>>(mq, mk, mv, mck, mcv, p);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_kernel(varlen_attention_kernel<D>, grid, dim3(THREADS), Smem<D>::TOTAL, stream, 0, mq, mk, mv,
+                                  mck, mcv, p);
     if (e != cudaSuccess) {
         bg_set_error("bg_varlen_attention: launch: %s", cudaGetErrorString(e));
         return BG_ERR_LAUNCH;

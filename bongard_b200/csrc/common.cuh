@@ -28,6 +28,7 @@ int bg_make_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, int rank, co
                        const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
                        CUtensorMapSwizzle swizzle);
 int bg_num_sms();
+int bg_programmatic_launch();  // 1 when kernels are launched with programmatic stream serialization
 int32_t* bg_status_word();  // device pointer, zero unless a bounded wait ran out
 
 #ifdef __CUDACC__
@@ -367,6 +368,14 @@ __device__ __forceinline__ float gelu_tanh(float x) {
     float inner = k0 * (x + k1 * x * x * x);
     return 0.5f * x * (1.0f + fast_tanh(inner));
 }
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with programmatic stream serialization may start while its predecessor in the stream
+// is still running; it runs its prologue (barrier init, TMEM allocation, descriptor prefetch) and then
+// waits here, before its first access to global memory, until the predecessor has completed and its
+// writes are visible.  Without the launch attribute both instructions do nothing.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------- MXFP8 (E4M3 with UE8M0 scales per 32 elements)
 constexpr int MX_ATOM = 512;      // bytes of one scale atom: 128 rows x 4 consecutive 32-element blocks
 __device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
@@ -398,6 +407,36 @@ __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
+}
+
+// Launch `kernel`, optionally as a cluster of `cluster_x` CTAs (0: whatever the kernel declares) and, when
+// enabled through bg_set_programmatic_launch, with programmatic stream serialization - only for kernels that
+// call pdl_wait() before they touch global memory.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 int cluster_x, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[2];
+    int n = 0;
+    if (cluster_x > 0) {
+        attrs[n].id = cudaLaunchAttributeClusterDimension;
+        attrs[n].val.clusterDim.x = (unsigned)cluster_x;
+        attrs[n].val.clusterDim.y = 1;
+        attrs[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    if (bg_programmatic_launch()) {
+        attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    cfg.attrs = attrs;
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 }  // namespace bg

@@ -89,6 +89,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();                   // the predecessor in the stream has finished; from here on global memory may be touched
+    pdl_launch_dependents();      // the successor may start its own prologue
 
     const int num_tiles = p.tiles_m * p.tiles_n;
     const int kblocks = (p.k + BK - 1) / BK;
@@ -294,8 +296,8 @@ extern "C" int bg_gemm_bf16(const void* a, int64_t lda, const void* w, int64_t l
     }
     const int tiles = p.tiles_m * p.tiles_n;
     const int grid = tiles < bg_num_sms() ? tiles : bg_num_sms();
-    gemm_bf16_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(map_a, map_w, p);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_kernel(gemm_bf16_kernel, dim3((unsigned)grid), dim3(THREADS), SMEM_BYTES,
+                                  static_cast<cudaStream_t>(stream), 0, map_a, map_w, p);
     if (e != cudaSuccess) {
         bg_set_error("bg_gemm_bf16: launch: %s", cudaGetErrorString(e));
         return BG_ERR_LAUNCH;

@@ -104,6 +104,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     cluster_sync();               // both CTAs' barriers are initialised before anyone signals across
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();                   // the predecessor in the stream has finished; from here on global memory may be touched
+    pdl_launch_dependents();      // the successor may start its own prologue
     float* gains = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 256);   // [2][256]: q, k
     if (p.epilogue == 2 && warp >= 2) {
         for (int i = threadIdx.x - 64; i < 2 * p.head_dim; i += 128) {
@@ -433,8 +435,8 @@ static int pair_launch(PairParams p, const CUtensorMap& map_a, const CUtensorMap
     }
     const int tiles = p.tiles_m * p.tiles_n;
     const int pairs = tiles < max_pairs ? tiles : max_pairs;
-    gemm_bf16_pair_kernel<<<2 * pairs, THREADS, SMEM_BYTES, stream>>>(map_a, map_w, p);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_kernel(gemm_bf16_pair_kernel, dim3((unsigned)(2 * pairs)), dim3(THREADS), SMEM_BYTES, stream,
+                                  0, map_a, map_w, p);
     if (e != cudaSuccess) {
         bg_set_error("bg_gemm_bf16: launch(pair): %s", cudaGetErrorString(e));
         return BG_ERR_LAUNCH;

@@ -104,6 +104,8 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();                   // the predecessor in the stream has finished; from here on global memory may be touched
+    pdl_launch_dependents();      // the successor may start its own prologue
 
     const int part = warp & 3;
     const int row_in_tile = part * 32 + lane;
@@ -377,19 +379,8 @@ extern "C" int bg_gemm_bf16_skinny(const void* a, int64_t lda, const void* w, in
 
     p.max_units = (units + best_ks - 1) / best_ks;
 
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(tiles * best_ks));
-    cfg.blockDim = dim3(THREADS);
-    cfg.dynamicSmemBytes = SMEM_BYTES;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = (unsigned)best_ks;
-    attr.val.clusterDim.y = 1;
-    attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_skinny_kernel, map_a, map_w, p);
+    cudaError_t e = launch_kernel(gemm_bf16_skinny_kernel, dim3((unsigned)(tiles * best_ks)), dim3(THREADS), SMEM_BYTES,
+                                  stream, best_ks, map_a, map_w, p);
     if (e != cudaSuccess) {
         cudaGetLastError();
         bg_set_error("bg_gemm_bf16_skinny: launch (%d tiles x %d): %s", tiles, best_ks, cudaGetErrorString(e));

@@ -66,6 +66,8 @@ __device__ __forceinline__ void store_mxfp8(const float* f, bool active, uint8_t
 __global__ void rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const __nv_bfloat16* __restrict__ w,
                                __nv_bfloat16* __restrict__ out, int64_t ldo, int h, float eps,
                                uint8_t* __restrict__ out_q, uint8_t* __restrict__ out_sf) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float scratch[33];
     const int64_t row = blockIdx.x;
     const int c = threadIdx.x * 8;
@@ -102,6 +104,8 @@ __global__ void add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ y, const __
                                    __nv_bfloat16* __restrict__ resid, const __nv_bfloat16* __restrict__ w_next,
                                    __nv_bfloat16* __restrict__ normed, int h, float eps,
                                    uint8_t* __restrict__ normed_q, uint8_t* __restrict__ normed_sf) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float scratch[33];
     const int64_t row = blockIdx.x;
     const int c = threadIdx.x * 8;
@@ -162,6 +166,8 @@ __global__ void qk_norm_rope_kernel(__nv_bfloat16* __restrict__ q, int64_t ldq, 
                                     const __nv_bfloat16* __restrict__ cos_table,
                                     const __nv_bfloat16* __restrict__ sin_table, int64_t tokens, float eps,
                                     int rotate) {
+    pdl_wait();
+    pdl_launch_dependents();
     constexpr int E = D / 32;  // elements per lane
     const int lane = threadIdx.x & 31;
     const int64_t token = int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -239,6 +245,8 @@ __global__ void rope_table_kernel(float2* __restrict__ table, int64_t rows, int 
 __global__ void embed_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                              const __nv_bfloat16* __restrict__ eoi, __nv_bfloat16* __restrict__ out, int h,
                              float scale, int64_t eoi_token, int64_t vocab) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int64_t row = blockIdx.x;
     const int c = threadIdx.x * 8;
     if (c >= h) return;
@@ -271,6 +279,8 @@ judgment_head_kernel(const __nv_bfloat16* __restrict__ hidden, int64_t ldh,
                      const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ cmat,
                      const __nv_bfloat16* __restrict__ gmat, float* __restrict__ logits, int h,
                      int rank) {
+    pdl_wait();
+    pdl_launch_dependents();
     extern __shared__ float sh[];      // h floats of the candidate row, h floats of the decision row
     __shared__ float scratch[33];
     __shared__ float warp_acc[8];
@@ -383,6 +393,8 @@ __global__ void geglu_backward_kernel(const __nv_bfloat16* __restrict__ gu, cons
 // Per-question temperature softmax in float64 (bongard/inference.py:54-73), one thread per question.
 __global__ void candidate_softmax_kernel(const float* __restrict__ logits, const int32_t* __restrict__ offsets,
                                          double* __restrict__ probs, int questions, double temperature) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int q = blockIdx.x * blockDim.x + threadIdx.x;
     if (q >= questions) return;
     const int lo = offsets[q], hi = offsets[q + 1];
@@ -431,9 +443,9 @@ int bg_rmsnorm(const void* x, int64_t ldx, const void* w, void* out, int64_t ldo
         return BG_ERR_SHAPE;
     }
     if (rows == 0) return BG_OK;
-    rmsnorm_kernel<<<(unsigned)rows, row_threads(h), 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(w),
-        static_cast<__nv_bfloat16*>(out), ldo, (int)h, eps, nullptr, nullptr);
+    launch_kernel(rmsnorm_kernel, dim3((unsigned)rows), dim3(row_threads(h)), 0, static_cast<cudaStream_t>(stream), 0,
+                  static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(w),
+                  static_cast<__nv_bfloat16*>(out), ldo, (int)h, eps, (uint8_t*)nullptr, (uint8_t*)nullptr);
     return check_launch("bg_rmsnorm");
 }
 
@@ -444,9 +456,10 @@ int bg_rmsnorm_mxfp8(const void* x, int64_t ldx, const void* w, void* out_q, voi
         return BG_ERR_SHAPE;
     }
     if (rows == 0) return BG_OK;
-    rmsnorm_kernel<<<(unsigned)rows, row_threads(h), 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(w), nullptr, 0, (int)h, eps,
-        static_cast<uint8_t*>(out_q), static_cast<uint8_t*>(out_scales));
+    launch_kernel(rmsnorm_kernel, dim3((unsigned)rows), dim3(row_threads(h)), 0, static_cast<cudaStream_t>(stream), 0,
+                  static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(w),
+                  (__nv_bfloat16*)nullptr, (int64_t)0, (int)h, eps, static_cast<uint8_t*>(out_q),
+                  static_cast<uint8_t*>(out_scales));
     return check_launch("bg_rmsnorm_mxfp8");
 }
 
@@ -457,10 +470,10 @@ int bg_add_rmsnorm(const void* y, const void* w_post, void* resid, const void* w
         return BG_ERR_SHAPE;
     }
     if (rows == 0) return BG_OK;
-    add_rmsnorm_kernel<<<(unsigned)rows, row_threads(h), 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(w_post),
-        static_cast<__nv_bfloat16*>(resid), static_cast<const __nv_bfloat16*>(w_next),
-        static_cast<__nv_bfloat16*>(normed), (int)h, eps, nullptr, nullptr);
+    launch_kernel(add_rmsnorm_kernel, dim3((unsigned)rows), dim3(row_threads(h)), 0, static_cast<cudaStream_t>(stream), 0,
+                  static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(w_post),
+                  static_cast<__nv_bfloat16*>(resid), static_cast<const __nv_bfloat16*>(w_next),
+                  static_cast<__nv_bfloat16*>(normed), (int)h, eps, (uint8_t*)nullptr, (uint8_t*)nullptr);
     return check_launch("bg_add_rmsnorm");
 }
 
@@ -471,10 +484,11 @@ int bg_add_rmsnorm_mxfp8(const void* y, const void* w_post, void* resid, const v
         return BG_ERR_SHAPE;
     }
     if (rows == 0) return BG_OK;
-    add_rmsnorm_kernel<<<(unsigned)rows, row_threads(h), 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(w_post),
-        static_cast<__nv_bfloat16*>(resid), static_cast<const __nv_bfloat16*>(w_next), nullptr, (int)h, eps,
-        static_cast<uint8_t*>(normed_q), static_cast<uint8_t*>(normed_scales));
+    launch_kernel(add_rmsnorm_kernel, dim3((unsigned)rows), dim3(row_threads(h)), 0, static_cast<cudaStream_t>(stream), 0,
+                  static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(w_post),
+                  static_cast<__nv_bfloat16*>(resid), static_cast<const __nv_bfloat16*>(w_next),
+                  (__nv_bfloat16*)nullptr, (int)h, eps, static_cast<uint8_t*>(normed_q),
+                  static_cast<uint8_t*>(normed_scales));
     return check_launch("bg_add_rmsnorm_mxfp8");
 }
 
@@ -502,13 +516,13 @@ static int qk_norm_rope_launch(void* q, int64_t ldq, int q_heads, void* k, int64
     auto* st = static_cast<const __nv_bfloat16*>(sin_table);
     if (qp == nullptr) q_heads = 0;
     if (head_dim == 64)
-        qk_norm_rope_kernel<64><<<grid, warps * 32, 0, s>>>(qp, ldq, q_heads, kp, ldk, k_heads, qw, kw, positions,
+        launch_kernel(qk_norm_rope_kernel<64>, dim3(grid), dim3(warps * 32), 0, s, 0, qp, ldq, q_heads, kp, ldk, k_heads, qw, kw, positions,
                                                              inv_freq, ct, st, tokens, eps, rotate);
     else if (head_dim == 128)
-        qk_norm_rope_kernel<128><<<grid, warps * 32, 0, s>>>(qp, ldq, q_heads, kp, ldk, k_heads, qw, kw, positions,
+        launch_kernel(qk_norm_rope_kernel<128>, dim3(grid), dim3(warps * 32), 0, s, 0, qp, ldq, q_heads, kp, ldk, k_heads, qw, kw, positions,
                                                               inv_freq, ct, st, tokens, eps, rotate);
     else
-        qk_norm_rope_kernel<256><<<grid, warps * 32, 0, s>>>(qp, ldq, q_heads, kp, ldk, k_heads, qw, kw, positions,
+        launch_kernel(qk_norm_rope_kernel<256>, dim3(grid), dim3(warps * 32), 0, s, 0, qp, ldq, q_heads, kp, ldk, k_heads, qw, kw, positions,
                                                               inv_freq, ct, st, tokens, eps, rotate);
     return check_launch("bg_qk_norm_rope");
 }
@@ -574,7 +588,7 @@ int bg_embed(const int64_t* ids, const void* table, const void* eoi_embedding, v
         return BG_ERR_SHAPE;
     }
     if (rows == 0) return BG_OK;
-    embed_kernel<<<(unsigned)rows, row_threads(h), 0, static_cast<cudaStream_t>(stream)>>>(
+    launch_kernel(embed_kernel, dim3((unsigned)rows), dim3(row_threads(h)), 0, static_cast<cudaStream_t>(stream), 0, 
         ids, static_cast<const __nv_bfloat16*>(table), static_cast<const __nv_bfloat16*>(eoi_embedding),
         static_cast<__nv_bfloat16*>(out), (int)h, scale, eoi_token, vocab);
     return check_launch("bg_embed");
@@ -594,7 +608,7 @@ int bg_judgment_head(const void* hidden, int64_t ldh, const int32_t* cand_rows, 
         cudaFuncSetAttribute(judgment_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
         configured = true;
     }
-    judgment_head_kernel<<<dim3((unsigned)candidates, HEAD_SPLIT), 256, smem, static_cast<cudaStream_t>(stream)>>>(
+    launch_kernel(judgment_head_kernel, dim3((unsigned)candidates, HEAD_SPLIT), dim3(256), smem, static_cast<cudaStream_t>(stream), 0, 
         static_cast<const __nv_bfloat16*>(hidden), ldh, cand_rows, dec_rows, static_cast<const __nv_bfloat16*>(w),
         static_cast<const __nv_bfloat16*>(cmat), static_cast<const __nv_bfloat16*>(gmat), logits, (int)h, rank);
     return check_launch("bg_judgment_head");
@@ -607,7 +621,7 @@ int bg_candidate_softmax(const float* logits, const int32_t* offsets, double* pr
         return BG_ERR_SHAPE;
     }
     if (questions == 0) return BG_OK;
-    candidate_softmax_kernel<<<(unsigned)((questions + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+    launch_kernel(candidate_softmax_kernel, dim3((unsigned)((questions + 127) / 128)), dim3(128), 0, static_cast<cudaStream_t>(stream), 0, 
         logits, offsets, probs, (int)questions, temperature);
     return check_launch("bg_candidate_softmax");
 }

@@ -86,6 +86,7 @@ class JudgmentEngine:
         # The serving path lets stacks of up to 256 tokens use the split-K weight-streaming GEMM.  The
         # packed engine keeps it off, so that where a pack boundary falls never changes a result bit.
         self.few_rows_kernels = False
+        self.programmatic_launch = False   # set by the serving path (serving.Predictor)
         # Opt-in: apply QK-norm + RoPE inside the q|k|v GEMM epilogue (bg_gemm_bf16_qkv_rope).  Alone the
         # fused projection is 6 % faster than projection + separate kernel, but inside the power-capped
         # step the extra epilogue arithmetic slows the GEMM by as much as the separate pass cost.

@@ -178,7 +178,7 @@ def serve(args, flush):
 
     shape = wl.SHAPES[args.shape]
     engine = JudgmentEngine(wl.make_weights_device(shape, 4, DEV), shape)
-    served = Predictor(engine, graphs=not args.no_graphs)
+    served = Predictor(engine, graphs=not args.no_graphs, programmatic_launch=not args.no_pdl)
 
     def clock(request):
         torch.cuda.synchronize()
@@ -223,6 +223,7 @@ def main():
     ap.add_argument('--requests', type=int, default=40)
     ap.add_argument('--backward', action='store_true', help='attention: also time the backward passes')
     ap.add_argument('--few-rows', action='store_true', help='linear/mlp: allow the split-K kernel for <= 256 tokens')
+    ap.add_argument('--no-pdl', action='store_true', help='serve: plain launches instead of programmatic dependent launch')
     ap.add_argument('--no-graphs', action='store_true', help='serve: launch every kernel eagerly')
     ap.add_argument('--variant', default='global', choices=['global', 'window'])
     ap.add_argument('--sequences', type=int, default=16)

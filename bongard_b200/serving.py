@@ -29,7 +29,7 @@ from dataclasses import dataclass
 import numpy as np
 import torch
 
-from . import ops
+from . import _lib, ops
 from .engine import DevicePack, JudgmentEngine
 
 BF16 = torch.bfloat16
@@ -111,11 +111,16 @@ class _Stage:
 
     def __init__(self, body, use_graph, engine):
         def fn():
+            # latency settings: the few-row GEMM for small stacks, and launches that let a kernel's prologue
+            # overlap its predecessor's tail (captured into the graph as programmatic edges)
             previous, engine.few_rows_kernels = engine.few_rows_kernels, True
+            lib = _lib.load()
+            lib.bg_set_programmatic_launch(1 if engine.programmatic_launch else 0)
             try:
                 return body()
             finally:
                 engine.few_rows_kernels = previous
+                lib.bg_set_programmatic_launch(0)
 
         self.fn, self.graph, self.out = fn, None, None
         self.out = fn()                       # eager warm-up: lazy library init, allocator warm
@@ -137,8 +142,10 @@ class Predictor:
     """`predict(request)` for one `workload.Request`: {question id: float64 probabilities}."""
 
     def __init__(self, engine: JudgmentEngine, *, state_cache_mib=1024, graphs=True, state_bucket=256,
-                 question_bucket=128, fine_bucket=32, max_graph_state=16384, max_graph_question=8192):
+                 question_bucket=128, fine_bucket=32, max_graph_state=16384, max_graph_question=8192,
+                 programmatic_launch=True):
         self.engine, self.graphs = engine, bool(graphs)
+        engine.programmatic_launch = bool(programmatic_launch)
         self.cache = StateCache(int(state_cache_mib) * 2 ** 20)
         self.state_bucket, self.question_bucket = int(state_bucket), int(question_bucket)
         self.fine_bucket = int(fine_bucket)   # granularity up to 256 tokens (see _bucket)

@@ -44,6 +44,13 @@ int bg_device_check(void);
  * bounded wait that ran out (1xx BF16 GEMM, 2xx attention, 3xx FP8 GEMM). */
 int bg_read_status(void* stream);
 
+/* Programmatic dependent launch for the latency path: with enable = 1 the kernels of the serving chain
+ * (bg_gemm_bf16, bg_gemm_bf16_skinny, bg_varlen_attention, the norm / RoPE / embedding / head kernels) are
+ * launched with programmatic stream serialization: a kernel may start while its predecessor in the stream is
+ * still running, sets up its barriers and tensor memory, and waits (griddepcontrol.wait) before its first
+ * access to global memory.  Default 0 (plain launches); process-wide.  No counterpart in the reference. */
+void bg_set_programmatic_launch(int enable);
+
 /* out[r, :] = rmsnorm(x[r, :]) * (1 + w), fp32 math, rounded once.
  * Replaces HF:61-69 T5Gemma2RMSNorm.forward / bongard/mps_inference.py:70-83 MPSRMSNorm. */
 int bg_rmsnorm(const void* x, int64_t ldx, const void* w, void* out, int64_t ldo, int64_t rows, int64_t h,
