@@ -249,6 +249,15 @@ class JudgmentEngine:
 
     def execute(self, staged, *, keep_hidden=False):
         """Run a staged batch; returns candidate logits fp32 [n_candidates] (device)."""
+        from . import _lib
+        lib = _lib.load()
+        lib.bg_set_programmatic_launch(1 if self.programmatic_launch else 0)
+        try:
+            return self._execute(staged, keep_hidden)
+        finally:
+            lib.bg_set_programmatic_launch(0)
+
+    def _execute(self, staged, keep_hidden):
         logits, hidden_rows = [], []
         for enc, decs in staged:
             state = self._stack(self.enc, self.enc_norm, enc)
