@@ -49,8 +49,8 @@ def parse():
     ap.add_argument('--seed', type=int, default=None, help='default: 4 (judged), 5 (long)')
     ap.add_argument('--workload', default='judged', choices=['judged', 'long'],
                     help="judged: 512-8192-token states, 1-24 questions; long: 32768-token states x 64 questions")
-    ap.add_argument('--plain-launches', action='store_true',
-                    help='launch kernels without programmatic stream serialization')
+    ap.add_argument('--programmatic-launches', action='store_true',
+                    help='launch kernels with programmatic stream serialization (no effect on throughput: 297.5 vs 297.1)')
     ap.add_argument('--linears', default='bf16', choices=['bf16', 'fp8', 'mxfp8'], help='projection / MLP GEMM precision')
     ap.add_argument('--cpu-seconds', type=float, default=15.0, help='CPU baseline budget per sample')
     ap.add_argument('--encoder-pack-tokens', type=int, default=65536)
@@ -237,7 +237,7 @@ def run_b200(args):
     weights = wl.make_weights_device(shape, args.seed, device)
     engine = JudgmentEngine(weights, shape, device, linears=args.linears, encoder_pack_tokens=args.encoder_pack_tokens,
                             decoder_pack_tokens=args.decoder_pack_tokens)
-    engine.programmatic_launch = not args.plain_launches
+    engine.programmatic_launch = args.programmatic_launches
     del weights
     requests = make_requests(shape, args.seed + rank, args.requests, args.workload)
     questions = sum(len(r.questions) for r in requests)
