@@ -5,6 +5,7 @@
     python -m bongard_b200.microbench linear [--tokens 32768]
     python -m bongard_b200.microbench glue [--tokens 32768]
     python -m bongard_b200.microbench serve [--shape 4b-4b] [--requests 40] [--no-graphs]
+    python -m bongard_b200.microbench dropin [--shape 4b-4b] [--requests 32] [--group 8]
 
 attention: packed encoder self-attention, lengths uniform in 256-4096 (seed 2), 8 query / 4 KV
 heads of 256, QK-norm + RoPE applied by the glue kernel first; FLOPs = 4 D Hq (visible pairs).
@@ -16,6 +17,10 @@ short requests one at a time (distinct states of 256-1024 tokens, one question e
 p95 after one pass that captures the buckets), and 32 questions on one 2048-token state as one
 request against 32 separate requests (the two workloads the reference quotes latencies for,
 README.md:185-186, there on other hardware and real requests).
+dropin: the Hugging Face backbone with the hot-path modules substituted (`install_b200_inference`)
+driven through the reference's packed call sequence (`hf.PackedJudge.forward_packed`, decoder groups
+of 8 questions as the reference forms them), against `JudgmentEngine` on the same weights and
+requests: questions/s of both and the largest difference between their probabilities.
 """
 
 from __future__ import annotations
@@ -216,11 +221,58 @@ def serve(args, flush):
     return out
 
 
+def dropin(args, flush):
+    import time
+
+    from transformers import T5Gemma2Model
+
+    from . import install
+    from .engine import JudgmentEngine
+    from .hf import PackedJudge, hf_config
+
+    shape = wl.SHAPES[args.shape]
+    torch.manual_seed(7)
+    with torch.device(DEV):
+        backbone = T5Gemma2Model(hf_config(shape)).to(torch.bfloat16).eval()
+    weights = {k: v for k, v in backbone.state_dict().items()}
+    g = torch.Generator(device=DEV).manual_seed(8)
+    for name, dims in wl.weight_names(shape):
+        if name.startswith('head.'):
+            weights[name] = (torch.randn(dims, device=DEV, generator=g) * 0.02).bfloat16()
+    requests = wl.judged_requests(23, vocab=shape.vocab, requests=args.requests)
+    questions = sum(len(r.questions) for r in requests)
+    engine = JudgmentEngine(weights, shape)
+    counts = install.install_b200_inference(backbone)
+    judge = PackedJudge(backbone, weights)
+
+    def clock(fn):
+        fn()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out = fn()
+        torch.cuda.synchronize()
+        return out, time.perf_counter() - t0
+
+    packed, t_dropin = clock(lambda: judge.forward_packed(requests, args.group))
+    probs_engine, t_engine = clock(lambda: engine.judge(requests))
+    a = torch.cat([torch.softmax(v['logits'].double(), 0).cpu() for r in packed for v in r.values()])
+    b = torch.cat([p for r in probs_engine for p in r.values()])
+    # rounding floor of the model itself: the same engine with another summation order in one GEMM per layer
+    engine.fuse_qkv_rope = True
+    c = torch.cat([p for r in engine.judge(requests) for p in r.values()])
+    engine.fuse_qkv_rope = False
+    return dict(op='dropin_vs_engine', shape=shape.name, questions_per_decoder_call=args.group, requests=len(requests), questions=questions,
+                substituted=counts, dropin_questions_per_s=questions / t_dropin, engine_questions_per_s=questions / t_engine,
+                max_abs_prob_diff=float((a - b).abs().max()), mean_abs_prob_diff=float((a - b).abs().mean()),
+                floor_max_abs_prob_diff=float((c - b).abs().max()), floor_mean_abs_prob_diff=float((c - b).abs().mean()))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument('op', choices=['attention', 'mlp', 'linear', 'glue', 'serve'])
+    ap.add_argument('op', choices=['attention', 'mlp', 'linear', 'glue', 'serve', 'dropin'])
     ap.add_argument('--shape', default='4b-4b', choices=sorted(wl.SHAPES))
     ap.add_argument('--requests', type=int, default=40)
+    ap.add_argument('--group', type=int, default=8, help='dropin: questions per decoder call (the reference\'s branch batch size)')
     ap.add_argument('--backward', action='store_true', help='attention: also time the backward passes')
     ap.add_argument('--few-rows', action='store_true', help='linear/mlp: allow the split-K kernel for <= 256 tokens')
     ap.add_argument('--no-pdl', action='store_true', help='serve: plain launches instead of programmatic dependent launch')
@@ -235,7 +287,7 @@ def main():
     args = ap.parse_args()
     ops.device_check()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV) if args.flush else None
-    result = {'attention': attention, 'mlp': mlp, 'linear': linear, 'glue': glue, 'serve': serve}[args.op](args, flush)
+    result = {'attention': attention, 'mlp': mlp, 'linear': linear, 'glue': glue, 'serve': serve, 'dropin': dropin}[args.op](args, flush)
     ops.read_status()
     for row in result if isinstance(result, list) else [result]:
         print(json.dumps(row))
