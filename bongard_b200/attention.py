@@ -102,12 +102,17 @@ def qk_norm_rope(q, k, q_norm, k_norm, position_embeddings):
     """The fused surface of bongard/flash_attention.py:76-125 (metal_qk_norm_rope):
     q [B,L,Hq,D], k [B,L,Hkv,D] -> q' [B,Hq,L,D], k' [B,Hkv,L,D]."""
     b, l, hq, d = q.shape
-    q2, k2 = q.reshape(b * l, hq, d).clone(), k.reshape(b * l, k.shape[2], d).clone()
     cos, sin = position_embeddings
     cos = cos.expand(b, l, d).reshape(-1, d).to(torch.bfloat16)
     sin = sin.expand(b, l, d).reshape(-1, d).to(torch.bfloat16)
-    ops.qk_norm_rope_table_(q2, k2, q_norm.weight.detach().to(torch.bfloat16), k_norm.weight.detach().to(torch.bfloat16),
-                            cos, sin, q_norm.eps)
+    q2, k2 = q.reshape(b * l, hq, d), k.reshape(b * l, k.shape[2], d)
+    if torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, q_norm.weight, k_norm.weight)):
+        # unlike the reference's fused form (no-grad only, flash_attention.py:83-106) this one is differentiable
+        q2, k2 = ops.qk_norm_rope_table_autograd(q2, k2, q_norm.weight, k_norm.weight, cos, sin, q_norm.eps)
+    else:
+        q2, k2 = q2.clone(), k2.clone()
+        ops.qk_norm_rope_table_(q2, k2, q_norm.weight.detach().to(torch.bfloat16),
+                                k_norm.weight.detach().to(torch.bfloat16), cos, sin, q_norm.eps)
     return q2.view(b, l, hq, d).transpose(1, 2), k2.view(b, l, -1, d).transpose(1, 2)
 
 
@@ -133,6 +138,8 @@ class B200RMSNorm(nn.Module):
     def forward(self, x):
         if x.stride(-1) != 1:
             x = x.contiguous()
+        if torch.is_grad_enabled() and (x.requires_grad or self.weight.requires_grad):
+            return ops.rmsnorm_autograd(x, self.weight, self.eps)
         return ops.rmsnorm(x, self.weight.detach().to(torch.bfloat16), self.eps)
 
 

@@ -27,11 +27,8 @@ class B200FusedMLP(nn.Module):
 
     def forward(self, x):
         if self.training and torch.is_grad_enabled() and (x.requires_grad or self.layer_norm_weight.requires_grad):
-            # train mode: the norm in PyTorch so that autograd sees it (transformers modeling_t5gemma2.py:61-69),
-            # the projections through their tensor-core backward
-            xf = x.float()
-            n = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps) * (1.0 + self.layer_norm_weight.float()))
-            return self.mlp(n.to(x.dtype))
+            # train mode: norm and projections record their backward kernels
+            return self.mlp(ops.rmsnorm_autograd(x, self.layer_norm_weight, self.eps))
         n = ops.rmsnorm(x if x.stride(-1) == 1 else x.contiguous(), self.layer_norm_weight.detach().to(torch.bfloat16),
                         self.eps)
         return self.mlp(n)

@@ -171,6 +171,14 @@ def glue(args, flush):
     freqs = ops.inv_freq(256, 1e4, DEV)
     ms = timed(lambda: ops.qk_norm_rope_(q, k, gain, gain, positions, freqs), args.iters, args.warmup, flush)
     out.append(dict(op='qk_norm_rope', tokens=t, ms=ms, gbs=2 * t * 3072 * 2 / ms / 1e6))
+    # backward of the two norms: input + upstream gradient in, input gradient out
+    ms = timed(lambda: ops.rmsnorm_backward(x, w, y), args.iters, args.warmup, flush)
+    out.append(dict(op='rmsnorm_backward', tokens=t, ms=ms, gbs=3 * t * h * 2 / ms / 1e6))
+    xq, xk = q.contiguous(), k.contiguous()
+    dq, dk = randn(t, 8, 256, seed=13), randn(t, 4, 256, seed=14)
+    ms = timed(lambda: ops.qk_norm_rope_backward(xq, xk, gain, gain, dq, dk, positions=positions, freqs=freqs),
+               args.iters, args.warmup, flush)
+    out.append(dict(op='qk_norm_rope_backward', tokens=t, ms=ms, gbs=3 * t * 3072 * 2 / ms / 1e6))
     return out
 
 

@@ -312,6 +312,108 @@ class _LinearGeglu(torch.autograd.Function):
         return dx, dw
 
 
+def rmsnorm_backward(x, weight, dy, eps=1e-6):
+    """(dx bf16 like x, dw fp32 [h]) of y = rmsnorm(x) * (1 + weight)."""
+    lib = _lib.load()
+    flat, rows, h, ldx = _rows(x, 'x')
+    dflat, drows, dh, lddy = _rows(dy.to(BF16), 'dy')
+    if (drows, dh) != (rows, h):
+        raise ValueError('dy must have the shape of x')
+    dx = torch.empty((rows, h), device=x.device, dtype=BF16)
+    dw = torch.empty((h,), device=x.device, dtype=torch.float32)
+    need = lib.bg_rmsnorm_backward_workspace_bytes(rows, h)
+    work = torch.empty((max(need, 4),), device=x.device, dtype=torch.uint8)
+    _lib.check(lib.bg_rmsnorm_backward(_ptr(flat), ldx, _ptr(_need(weight, 'weight')), _ptr(dflat), lddy, _ptr(dx), h,
+                                       _ptr(dw), _ptr(work), need, rows, h, eps, _stream()), 'bg_rmsnorm_backward')
+    return dx.view(x.shape), dw
+
+
+class _RmsNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps):
+        w = weight.detach().to(BF16)
+        ctx.save_for_backward(x, w)
+        ctx.eps, ctx.weight_dtype = eps, weight.dtype
+        return rmsnorm(x, w, eps)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dx, dw = rmsnorm_backward(x, w, dy.contiguous(), ctx.eps)
+        return dx, dw.to(ctx.weight_dtype), None
+
+
+def rmsnorm_autograd(x, weight, eps=1e-6):
+    """rmsnorm() that records its backward (input and gain gradients from one kernel pass)."""
+    return _RmsNorm.apply(x if x.stride(-1) == 1 else x.contiguous(), weight, eps)
+
+
+def qk_norm_rope_backward(xq, xk, q_weight, k_weight, dyq, dyk, *, positions=None, freqs=None, cos=None, sin=None,
+                          eps=1e-6, rotate=True):
+    """Backward of qk_norm_rope_ / qk_norm_rope_table_: xq [T,Hq,D] and xk [T,Hkv,D] (or None) are the inputs
+    the forward normalised, dyq / dyk the gradients of its outputs.  Returns (dxq, dxk, dq_weight, dk_weight)
+    with fp32 gain gradients; the k entries are None when xk is None."""
+    lib = _lib.load()
+    tokens, hq, d = xq.shape
+
+    def token_major(t, name):
+        _need(t, name)
+        if t.stride(-1) != 1 or t.stride(1) != d:
+            t = t.contiguous()
+        return t
+
+    xq, dyq = token_major(xq, 'xq'), token_major(dyq.to(BF16), 'dyq')
+    dxq = torch.empty((tokens, hq, d), device=xq.device, dtype=BF16)
+    dqw = torch.empty((d,), device=xq.device, dtype=torch.float32)
+    hk = 0
+    dxk = dkw = None
+    if xk is not None:
+        hk = xk.shape[1]
+        xk, dyk = token_major(xk, 'xk'), token_major(dyk.to(BF16), 'dyk')
+        dxk = torch.empty((tokens, hk, d), device=xq.device, dtype=BF16)
+        dkw = torch.empty((d,), device=xq.device, dtype=torch.float32)
+    if rotate and cos is None:
+        _need(positions, 'positions', torch.int32), _need(freqs, 'inv_freq', torch.float32)
+    if cos is not None:
+        cos, sin = _need(cos, 'cos').contiguous(), _need(sin, 'sin').contiguous()
+        if cos.shape != (tokens, d) or sin.shape != (tokens, d):
+            raise ValueError(f'cos/sin must be [{tokens}, {d}]')
+    need = lib.bg_qk_norm_rope_backward_workspace_bytes(tokens, d)
+    work = torch.empty((max(need, 4),), device=xq.device, dtype=torch.uint8)
+    stride = lambda t: t.stride(0) if t is not None else 0
+    _lib.check(lib.bg_qk_norm_rope_backward(
+        _ptr(xq), stride(xq), _ptr(dyq), stride(dyq), _ptr(dxq), stride(dxq), hq,
+        _ptr(xk), stride(xk), _ptr(dyk) if xk is not None else 0, stride(dyk) if xk is not None else 0, _ptr(dxk),
+        stride(dxk), hk, _ptr(_need(q_weight, 'q_weight')), _ptr(k_weight), _ptr(positions) if positions is not None else 0,
+        _ptr(freqs) if freqs is not None else 0, _ptr(cos), _ptr(sin), _ptr(dqw), _ptr(dkw), _ptr(work), need, tokens, d,
+        eps, 1 if rotate else 0, _stream()), 'bg_qk_norm_rope_backward')
+    return dxq, dxk, dqw, dkw
+
+
+class _QkNormRopeTable(torch.autograd.Function):
+    """Out-of-place QK-norm + RoPE over caller-supplied bf16 cos / sin tables, with its backward."""
+
+    @staticmethod
+    def forward(ctx, q, k, q_weight, k_weight, cos, sin, eps):
+        qw, kw = q_weight.detach().to(BF16), k_weight.detach().to(BF16)
+        ctx.save_for_backward(q, k, qw, kw, cos, sin)
+        ctx.eps, ctx.dtypes = eps, (q_weight.dtype, k_weight.dtype)
+        q2, k2 = q.clone(memory_format=torch.contiguous_format), k.clone(memory_format=torch.contiguous_format)
+        qk_norm_rope_table_(q2, k2, qw, kw, cos, sin, eps)
+        return q2, k2
+
+    @staticmethod
+    def backward(ctx, dq, dk):
+        q, k, qw, kw, cos, sin = ctx.saved_tensors
+        dxq, dxk, dqw, dkw = qk_norm_rope_backward(q, k, qw, kw, dq, dk, cos=cos, sin=sin, eps=ctx.eps)
+        return dxq, dxk, dqw.to(ctx.dtypes[0]), dkw.to(ctx.dtypes[1]), None, None, None
+
+
+def qk_norm_rope_table_autograd(q, k, q_weight, k_weight, cos, sin, eps=1e-6):
+    """(q', k') = QK-norm + RoPE of q [T,Hq,D], k [T,Hkv,D] (not in place), recording the backward."""
+    return _QkNormRopeTable.apply(q, k, q_weight, k_weight, cos, sin, eps)
+
+
 def linear_autograd(x, weight):
     """linear() that records its backward."""
     return _Linear.apply(x, weight)

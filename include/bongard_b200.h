@@ -132,6 +132,30 @@ int bg_gemm_bf16_skinny(const void* a, int64_t lda, const void* w, int64_t ldw, 
 int bg_transpose_bf16(const void* src, int64_t lds, void* dst, int64_t ldd, int64_t rows, int64_t cols, void* stream);
 int bg_geglu_backward(const void* gu, const void* dh, void* dgu, int64_t rows, int64_t inter, void* stream);
 
+/* Backward of the norms the reference trains through with autograd (transformers T5Gemma2RMSNorm,
+ * modeling_t5gemma2.py:55-69; QK-norm + RoPE: bongard/attention.py:172-180).  fp32 math, bf16 in and out,
+ * gain gradients as fp32 vectors summed in a fixed order (no atomics).  The workspace holds one partial
+ * gain-gradient row per block (per warp for the QK form); its size comes from the companion function.
+ *   bg_rmsnorm_backward: y = x r (1 + w), r = rsqrt(mean(x^2) + eps):
+ *       dx = r g - x r^3 mean(g x) with g = dy (1 + w);  dw[h] = sum_rows dy x r.
+ *   bg_qk_norm_rope_backward: xq [tokens, q_heads, D] / xk [tokens, k_heads, D] are the inputs the forward
+ *       normalised (it runs in place: keep a copy), dyq / dyk the gradients of its outputs; the rotation is
+ *       undone first (da[j] = dy[j] cos[j] - sign(j) (dy sin)[partner(j)]), then the per-head norm backward.
+ *       Angles as in the forward: positions + inv_freq, or bf16 cos / sin tables [tokens, D]; rotate = 0 for
+ *       the state keys.  k_heads = 0 (xk NULL) handles q alone; dk_weight may then be NULL. */
+int64_t bg_rmsnorm_backward_workspace_bytes(int64_t rows, int64_t h);
+int bg_rmsnorm_backward(const void* x, int64_t ldx, const void* w, const void* dy, int64_t lddy, void* dx,
+                        int64_t lddx, float* dw, void* workspace, int64_t workspace_bytes, int64_t rows, int64_t h,
+                        float eps, void* stream);
+int64_t bg_qk_norm_rope_backward_workspace_bytes(int64_t tokens, int head_dim);
+int bg_qk_norm_rope_backward(const void* xq, int64_t ldxq, const void* dyq, int64_t lddyq, void* dxq, int64_t lddxq,
+                             int q_heads, const void* xk, int64_t ldxk, const void* dyk, int64_t lddyk, void* dxk,
+                             int64_t lddxk, int k_heads, const void* q_weight, const void* k_weight,
+                             const int32_t* positions, const float* inv_freq, const void* cos_table,
+                             const void* sin_table, float* dq_weight, float* dk_weight, void* workspace,
+                             int64_t workspace_bytes, int64_t tokens, int head_dim, float eps, int rotate,
+                             void* stream);
+
 /* E4M3 quantisation with dynamic per-block scales: scale = 448 / max(amax, 1e-12), values clamped
  * to +-448 and rounded to nearest; the INVERSE scales are stored as fp32.
  *   rows : 1 x 128 blocks of x [m, k] -> q (uint8 [m, k], row stride ldq bytes), inv_scale_t [k/128, m].

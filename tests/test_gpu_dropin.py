@@ -196,6 +196,9 @@ def test_converted_mlp_trains_like_the_native_one(tiny):
         assert float((dx - want_dx).abs().max()) < 3e-2 * float(want_dx.abs().max()) + 1e-3
         down = next(v for k, v in grads.items() if 'down' in k)
         assert float((down - want['mlp.down_proj.weight']).abs().max()) < 3e-2 * float(want['mlp.down_proj.weight'].abs().max())
+        if 'mlp.layer_norm_weight' in grads:      # the fused module owns the pre-norm: its gain gradient comes from the norm-backward kernel
+            gain = want['pre_feedforward_layernorm.weight']
+            assert float((grads['mlp.layer_norm_weight'] - gain).abs().max()) < 3e-2 * float(gain.abs().max())
     backbone = build_backbone(wl.TINY, weights).train()
     enable_te_linear(backbone, mlp='fp8')
     with pytest.raises(ValueError, match='forward-only'):
@@ -263,3 +266,47 @@ def test_padded_dense_encoder_batch_matches_packed(tiny):
         a, b = dense[i, :len(st)].float(), packed[offset:offset + len(st)].float()
         assert float((a - b).abs().max()) <= 3e-2 + 2e-2 * float(b.abs().max())
         offset += len(st)
+
+
+def test_substituted_norm_and_qk_norm_rope_are_differentiable(tiny):
+    """The substituted RMSNorm and the fused QK-norm + RoPE surface record their backward kernels: gradients
+    for the input and the gains agree with the native modules / the fp32 oracle."""
+    weights, _ = tiny
+    backbone = build_backbone(wl.TINY, weights).train()
+    native = backbone.decoder.layers[0].pre_self_attn_layernorm
+    with torch.no_grad():
+        native.weight.normal_(0, 0.2, generator=torch.Generator(device=DEV).manual_seed(1))
+    x = torch.randn(2, 70, wl.TINY.hidden, generator=torch.Generator().manual_seed(6)).bfloat16().to(DEV)
+    dy = torch.randn(2, 70, wl.TINY.hidden, generator=torch.Generator().manual_seed(7)).bfloat16().to(DEV)
+
+    def grads(module):
+        module.zero_grad()
+        inp = x.clone().requires_grad_(True)
+        module(inp).backward(dy)
+        return inp.grad.float().cpu(), module.weight.grad.float().cpu()
+
+    want_dx, want_dw = grads(native)
+    got_dx, got_dw = grads(b200_attention.B200RMSNorm(native))
+    assert float((got_dx - want_dx).abs().max()) < 2e-2 * float(want_dx.abs().max()) + 1e-3
+    assert float((got_dw - want_dw).abs().max()) < 2e-2 * float(want_dw.abs().max()) + 1e-3
+    with torch.no_grad():                         # inference keeps the plain kernel and records nothing
+        assert not b200_attention.B200RMSNorm(native)(x).requires_grad
+
+    attn = backbone.encoder.text_model.layers[0].self_attn
+    d, hq, hkv, l = wl.TINY.head_dim, wl.TINY.q_heads, wl.TINY.kv_heads, 90
+    gen = torch.Generator().manual_seed(8)
+    q = torch.randn(1, l, hq, d, generator=gen).bfloat16()
+    k = torch.randn(1, l, hkv, d, generator=gen).bfloat16()
+    dq, dk = torch.randn(1, hq, l, d, generator=gen).bfloat16(), torch.randn(1, hkv, l, d, generator=gen).bfloat16()
+    cos, sin = om.rope_tables(torch.arange(l), d, 1e4, torch.bfloat16)
+    qd, kd = q.to(DEV).requires_grad_(True), k.to(DEV).requires_grad_(True)
+    attn.zero_grad()
+    oq, ok = b200_attention.qk_norm_rope(qd, kd, attn.q_norm, attn.k_norm, (cos.to(DEV)[None], sin.to(DEV)[None]))
+    torch.autograd.backward([oq, ok], [dq.to(DEV), dk.to(DEV)])
+    qf, kf = q[0].float().requires_grad_(True), k[0].float().requires_grad_(True)
+    qw, kw = (n.weight.detach().float().cpu().requires_grad_(True) for n in (attn.q_norm, attn.k_norm))
+    wq, wk = om.qk_norm_rope(qf, kf, qw, kw, cos.float(), sin.float())
+    torch.autograd.backward([wq, wk], [dq[0].transpose(0, 1).float(), dk[0].transpose(0, 1).float()])
+    for got, want in ((qd.grad[0], qf.grad), (kd.grad[0], kf.grad), (attn.q_norm.weight.grad, qw.grad),
+                      (attn.k_norm.weight.grad, kw.grad)):
+        assert float((got.float().cpu() - want).abs().max()) < 2e-2 * float(want.abs().max()) + 2e-3

@@ -255,3 +255,72 @@ def test_linear_geglu_backward(m, i, k):
     (torch.nn.functional.gelu(pre[:, :i], approximate='tanh') * pre[:, i:]).backward(dh.float())
     assert_close(xd.grad, xf.grad, atol=3e-2, rtol=2e-2)
     assert_close(gd.grad, gf.grad, atol=3e-2 * (m ** 0.5), rtol=2e-2)
+
+
+@pytest.mark.parametrize('rows,h', [(1, 256), (7, 256), (700, 2560), (1300, 8192), (0, 256)])
+def test_rmsnorm_backward(rows, h):
+    """Input and gain gradients of the zero-centred RMSNorm against autograd of the oracle in fp32."""
+    x, w, dy = rnd(rows, h, seed=60), rnd(h, seed=61, std=0.2), rnd(rows, h, seed=62)
+    xd, wd = x.to(DEV).requires_grad_(True), w.to(DEV).requires_grad_(True)
+    ops.rmsnorm_autograd(xd, wd).backward(dy.to(DEV))
+    xf, wf = x.float().requires_grad_(True), w.float().requires_grad_(True)
+    om.rmsnorm(xf, wf).backward(dy.float())
+    assert xd.grad.dtype == torch.bfloat16 and wd.grad.dtype == torch.bfloat16
+    assert_close(xd.grad, xf.grad, atol=1e-2, rtol=8e-3)
+    assert_close(wd.grad, wf.grad, atol=1e-2 * max(rows, 1) ** 0.5, rtol=8e-3)
+    # the fp32 gain gradient itself, and that a second run gives the same bits (no atomics)
+    dx, dw = ops.rmsnorm_backward(x.to(DEV), w.to(DEV), dy.to(DEV))
+    assert_close(dw, wf.grad, atol=2e-3 * max(rows, 1) ** 0.5, rtol=2e-3)
+    dx2, dw2 = ops.rmsnorm_backward(x.to(DEV), w.to(DEV), dy.to(DEV))
+    assert torch.equal(dx, dx2) and torch.equal(dw, dw2)
+
+
+@pytest.mark.parametrize('d,hq,hkv,theta', [(64, 4, 2, 1e4), (256, 8, 4, 1e6), (128, 2, 1, 1e4)])
+def test_qk_norm_rope_backward(d, hq, hkv, theta):
+    """Backward of QK-norm + RoPE (both angle sources, and the no-rotation form of the state keys)
+    against autograd of the oracle in fp32."""
+    lengths = [5, 130, 1, 700, 2300]
+    t = sum(lengths)
+    q, k = rnd(t, hq, d, seed=63), rnd(t, hkv, d, seed=64)
+    qw, kw = rnd(d, seed=65, std=0.2), rnd(d, seed=66, std=0.2)
+    dq, dk = rnd(t, hq, d, seed=67), rnd(t, hkv, d, seed=68)
+    positions = torch.cat([torch.arange(n) for n in lengths])
+    cos, sin = om.rope_tables(positions, d, theta, torch.float32)
+    qf, kf, qwf, kwf = (v.float().requires_grad_(True) for v in (q, k, qw, kw))
+    oq, ok = om.qk_norm_rope(qf, kf, qwf, kwf, cos, sin)
+    torch.autograd.backward([oq, ok], [dq.float(), dk.float()])
+    tol_w = 1e-2 * (t * hq) ** 0.5
+
+    got = ops.qk_norm_rope_backward(q.to(DEV), k.to(DEV), qw.to(DEV), kw.to(DEV), dq.to(DEV), dk.to(DEV),
+                                    positions=positions.int().to(DEV), freqs=ops.inv_freq(d, theta, DEV))
+    assert_close(got[0], qf.grad, atol=1.5e-2, rtol=8e-3)
+    assert_close(got[1], kf.grad, atol=1.5e-2, rtol=8e-3)
+    assert_close(got[2], qwf.grad, atol=tol_w, rtol=8e-3)
+    assert_close(got[3], kwf.grad, atol=tol_w, rtol=8e-3)
+    again = ops.qk_norm_rope_backward(q.to(DEV), k.to(DEV), qw.to(DEV), kw.to(DEV), dq.to(DEV), dk.to(DEV),
+                                      positions=positions.int().to(DEV), freqs=ops.inv_freq(d, theta, DEV))
+    assert all(torch.equal(a, b) for a, b in zip(got, again))
+
+    # bf16 tables through the autograd surface (strided q / k views of one projection output)
+    cos16, sin16 = cos.bfloat16(), sin.bfloat16()
+    qkv = torch.cat([q.reshape(t, -1), k.reshape(t, -1)], 1).to(DEV).requires_grad_(True)
+    qwd, kwd = qw.to(DEV).requires_grad_(True), kw.to(DEV).requires_grad_(True)
+    o = ops.qk_norm_rope_table_autograd(qkv[:, :hq * d].view(t, hq, d), qkv[:, hq * d:].view(t, hkv, d), qwd, kwd,
+                                        cos16.to(DEV), sin16.to(DEV))
+    torch.autograd.backward(list(o), [dq.to(DEV), dk.to(DEV)])
+    qf2, kf2, qwf2, kwf2 = (v.float().requires_grad_(True) for v in (q, k, qw, kw))
+    o2 = om.qk_norm_rope(qf2, kf2, qwf2, kwf2, cos16.float(), sin16.float())
+    torch.autograd.backward(list(o2), [dq.float(), dk.float()])
+    assert_close(o[0], o2[0], atol=1.5e-2, rtol=8e-3)
+    assert_close(qkv.grad[:, :hq * d].view(t, hq, d), qf2.grad, atol=1.5e-2, rtol=8e-3)
+    assert_close(qkv.grad[:, hq * d:].view(t, hkv, d), kf2.grad, atol=1.5e-2, rtol=8e-3)
+    assert_close(qwd.grad, qwf2.grad, atol=tol_w, rtol=8e-3)
+    assert_close(kwd.grad, kwf2.grad, atol=tol_w, rtol=8e-3)
+
+    # normalise only, one tensor (the decoder's state keys)
+    kf3, kwf3 = k.float().requires_grad_(True), kw.float().requires_grad_(True)
+    om.rmsnorm(kf3, kwf3).backward(dk.float())
+    dxk, none_k, dkw, none_w = ops.qk_norm_rope_backward(k.to(DEV), None, kw.to(DEV), None, dk.to(DEV), None, rotate=False)
+    assert none_k is None and none_w is None
+    assert_close(dxk, kf3.grad, atol=1e-2, rtol=8e-3)
+    assert_close(dkw, kwf3.grad, atol=tol_w, rtol=8e-3)
