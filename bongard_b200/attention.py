@@ -62,6 +62,8 @@ def fused_qkv(module, hidden_states, *, positions=None, position_embeddings=None
     tables the rotary module produced."""
     x = hidden_states.reshape(-1, hidden_states.shape[-1])
     d = module.head_dim
+    if needs_grad(module, hidden_states):
+        return _fused_qkv_trainable(module, x, positions, position_embeddings)
     qkv = _linear(x, stacked_weight(module, ('q_proj', 'k_proj', 'v_proj'), '_b200_wqkv'))
     qd, kd = module.q_proj.weight.shape[0], module.k_proj.weight.shape[0]
     t = x.shape[0]
@@ -78,7 +80,46 @@ def fused_qkv(module, hidden_states, *, positions=None, position_embeddings=None
     return q, k, v
 
 
+def needs_grad(module, *tensors):
+    """True when autograd would record this call: gradients are enabled and an input or one of the
+    module's own parameters requires them.  The kernels then run through their autograd forms."""
+    if not torch.is_grad_enabled():
+        return False
+    return any(t is not None and t.requires_grad for t in tensors) or any(p.requires_grad for p in module.parameters())
+
+
+def _trainable_weight(module, names):
+    """The stacked projection weight as a differentiable concatenation of the native parameters
+    (the reference stacks them into one trainable parameter, bongard/te_linear.py:47-55)."""
+    if any(_recipe(getattr(module, n)) == 'fp8' for n in names):
+        raise ValueError('FP8 projections are forward-only; train with the bf16 recipe')
+    weights = [_weight(getattr(module, n)) for n in names]
+    w = weights[0] if len(weights) == 1 else torch.cat(weights)
+    return w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
+
+
+def _fused_qkv_trainable(module, x, positions, position_embeddings):
+    d = module.head_dim
+    qkv = ops.linear_autograd(x, _trainable_weight(module, ('q_proj', 'k_proj', 'v_proj')))
+    qd, kd = module.q_proj.weight.shape[0], module.k_proj.weight.shape[0]
+    t = x.shape[0]
+    q = qkv[:, :qd].view(t, qd // d, d)
+    k = qkv[:, qd:qd + kd].view(t, kd // d, d)
+    v = qkv[:, qd + kd:].view(t, kd // d, d)
+    if positions is not None:
+        q, k = ops.qk_norm_rope_autograd(q, k, module.q_norm.weight, module.k_norm.weight, positions,
+                                         ops.inv_freq(d, _theta(module), x.device), module.q_norm.eps)
+    else:
+        cos, sin = position_embeddings
+        q, k = ops.qk_norm_rope_table_autograd(q, k, module.q_norm.weight, module.k_norm.weight,
+                                               cos.reshape(-1, d).to(torch.bfloat16), sin.reshape(-1, d).to(torch.bfloat16),
+                                               module.q_norm.eps)
+    return q, k, v.contiguous()     # q and k are fresh contiguous tensors now: v has to share k's strides
+
+
 def project_out(module, attended, hidden_shape):
+    if needs_grad(module, attended):
+        return ops.linear_autograd(attended, _trainable_weight(module, ('o_proj',))).view(*hidden_shape[:-1], -1)
     return _linear(attended, stacked_weight(module, ('o_proj',), '_b200_wo')).view(*hidden_shape[:-1], -1)
 
 

@@ -390,28 +390,41 @@ def qk_norm_rope_backward(xq, xk, q_weight, k_weight, dyq, dyk, *, positions=Non
     return dxq, dxk, dqw, dkw
 
 
-class _QkNormRopeTable(torch.autograd.Function):
-    """Out-of-place QK-norm + RoPE over caller-supplied bf16 cos / sin tables, with its backward."""
+class _QkNormRope(torch.autograd.Function):
+    """Out-of-place QK-norm + RoPE with its backward; angles from bf16 cos / sin tables [T, D] or from
+    positions (int32 [T]) and inverse frequencies."""
 
     @staticmethod
-    def forward(ctx, q, k, q_weight, k_weight, cos, sin, eps):
+    def forward(ctx, q, k, q_weight, k_weight, cos, sin, positions, freqs, eps):
         qw, kw = q_weight.detach().to(BF16), k_weight.detach().to(BF16)
-        ctx.save_for_backward(q, k, qw, kw, cos, sin)
+        ctx.save_for_backward(q, k, qw, kw)
+        # angle sources carry no gradient and may be cached tensors made under inference mode: kept as attributes
+        ctx.angles = (cos, sin, positions, freqs)
         ctx.eps, ctx.dtypes = eps, (q_weight.dtype, k_weight.dtype)
         q2, k2 = q.clone(memory_format=torch.contiguous_format), k.clone(memory_format=torch.contiguous_format)
-        qk_norm_rope_table_(q2, k2, qw, kw, cos, sin, eps)
+        if cos is not None:
+            qk_norm_rope_table_(q2, k2, qw, kw, cos, sin, eps)
+        else:
+            qk_norm_rope_(q2, k2, qw, kw, positions, freqs, eps)
         return q2, k2
 
     @staticmethod
     def backward(ctx, dq, dk):
-        q, k, qw, kw, cos, sin = ctx.saved_tensors
-        dxq, dxk, dqw, dkw = qk_norm_rope_backward(q, k, qw, kw, dq, dk, cos=cos, sin=sin, eps=ctx.eps)
-        return dxq, dxk, dqw.to(ctx.dtypes[0]), dkw.to(ctx.dtypes[1]), None, None, None
+        q, k, qw, kw = ctx.saved_tensors
+        cos, sin, positions, freqs = ctx.angles
+        dxq, dxk, dqw, dkw = qk_norm_rope_backward(q, k, qw, kw, dq, dk, positions=positions, freqs=freqs, cos=cos,
+                                                   sin=sin, eps=ctx.eps)
+        return dxq, dxk, dqw.to(ctx.dtypes[0]), dkw.to(ctx.dtypes[1]), None, None, None, None, None
 
 
 def qk_norm_rope_table_autograd(q, k, q_weight, k_weight, cos, sin, eps=1e-6):
     """(q', k') = QK-norm + RoPE of q [T,Hq,D], k [T,Hkv,D] (not in place), recording the backward."""
-    return _QkNormRopeTable.apply(q, k, q_weight, k_weight, cos, sin, eps)
+    return _QkNormRope.apply(q, k, q_weight, k_weight, cos.contiguous(), sin.contiguous(), None, None, eps)
+
+
+def qk_norm_rope_autograd(q, k, q_weight, k_weight, positions, freqs, eps=1e-6):
+    """As qk_norm_rope_table_autograd with the angles positions * inv_freq computed in the kernels."""
+    return _QkNormRope.apply(q, k, q_weight, k_weight, None, None, positions, freqs, eps)
 
 
 def linear_autograd(x, weight):

@@ -102,17 +102,21 @@ def _project(module, hidden_states, layout_positions, position_embeddings):
 
 def encoder_attention(module, hidden_states, position_embeddings, layout):
     """bongard/packing.py:201-210: projections, QK-norm + RoPE, packed attention, o_proj."""
+    from .attention import needs_grad, project_out
+
     q, k, v = _project(module, hidden_states, layout.positions32, position_embeddings)
     group = q.shape[1] // k.shape[1]
-    out = ops.varlen_attention(q, k, v, layout.plan(module.sliding_window, group, q.shape[-1]), module.scaling)
-    from .attention import project_out
-
+    if needs_grad(module, hidden_states):
+        out = ops.varlen_attention_autograd(q, k, v, layout.plan(module.sliding_window, group, q.shape[-1], backward=True),
+                                            module.scaling)
+    else:
+        out = ops.varlen_attention(q, k, v, layout.plan(module.sliding_window, group, q.shape[-1]), module.scaling)
     return project_out(module, out, hidden_states.shape), None
 
 
 def decoder_attention(module, hidden_states, position_embeddings, cache, layout, packed_cross=None):
     """bongard/packing.py:213-225: as above with the owner's state K/V as key prefix."""
-    from .attention import as_token_major, project_out
+    from .attention import as_token_major, needs_grad, project_out
 
     q, k, v = _project(module, hidden_states, layout.positions32, position_embeddings)
     if packed_cross is None:
@@ -120,5 +124,9 @@ def decoder_attention(module, hidden_states, position_embeddings, cache, layout,
         packed_cross = (cross.keys, cross.values)
     ck, cv = as_token_major(packed_cross[0]), as_token_major(packed_cross[1])
     group = q.shape[1] // k.shape[1]
-    out = ops.varlen_attention(q, k, v, layout.plan(module.sliding_window, group, q.shape[-1]), module.scaling, (ck, cv))
+    if needs_grad(module, hidden_states, ck, cv):
+        out = ops.varlen_attention_autograd(q, k, v, layout.plan(module.sliding_window, group, q.shape[-1], backward=True),
+                                            module.scaling, (ck, cv))
+    else:
+        out = ops.varlen_attention(q, k, v, layout.plan(module.sliding_window, group, q.shape[-1]), module.scaling, (ck, cv))
     return project_out(module, out, hidden_states.shape), None, None

@@ -215,7 +215,8 @@ def test_project_qk_surface(golden_dir, tiny):
         attn.q_norm.weight.copy_(g['qk_qnorm']); attn.k_norm.weight.copy_(g['qk_knorm'])  # noqa: E702
     hidden = g['qk_hidden'].bfloat16().to(DEV)[None]
     pe = (g['qk_cos'].bfloat16().to(DEV)[None], g['qk_sin'].bfloat16().to(DEV)[None])
-    q, k = b200_attention.project_qk(attn, hidden, pe, 'b200')
+    with torch.no_grad():
+        q, k = b200_attention.project_qk(attn, hidden, pe, 'b200')
     assert q.shape == (1, 4, hidden.shape[1], 64) and k.shape == (1, 2, hidden.shape[1], 64)
     assert float((q[0].transpose(0, 1).float().cpu() - g['qk_q']).abs().max()) < 6e-2
     assert float((k[0].transpose(0, 1).float().cpu() - g['qk_k']).abs().max()) < 6e-2
@@ -310,3 +311,73 @@ def test_substituted_norm_and_qk_norm_rope_are_differentiable(tiny):
     for got, want in ((qd.grad[0], qf.grad), (kd.grad[0], kf.grad), (attn.q_norm.weight.grad, qw.grad),
                       (attn.k_norm.weight.grad, kw.grad)):
         assert float((got.float().cpu() - want).abs().max()) < 2e-2 * float(want.abs().max()) + 2e-3
+
+
+@pytest.mark.parametrize('decoder', [False, True])
+@pytest.mark.parametrize('layer_index', [0, 1])
+def test_packed_attention_module_trains(tiny, decoder, layer_index):
+    """With gradients enabled the substituted attention modules run their projections, QK-norm + RoPE
+    and the packed attention through the backward kernels: gradients of the input, of every projection,
+    of the QK gains and (decoder) of the shared state K/V against autograd of the fp32 oracle."""
+    weights, _ = tiny
+    shape = wl.TINY
+    backbone = build_backbone(shape, weights).train()
+    install_b200_inference(backbone)
+    stack = backbone.decoder if decoder else backbone.encoder.text_model
+    module = stack.layers[layer_index].self_attn
+    with torch.no_grad():
+        for norm, seed in ((module.q_norm, 1), (module.k_norm, 2)):
+            norm.weight.normal_(0, 0.2, generator=torch.Generator(device=DEV).manual_seed(seed))
+    lengths = [70, 200, 33]
+    t = sum(lengths)
+    gen = torch.Generator().manual_seed(11 + layer_index)
+    hidden = torch.randn(t, shape.hidden, generator=gen).bfloat16()
+    dout = torch.randn(t, shape.hidden, generator=gen).bfloat16()
+    owners, state_lengths = [1, 1, 0], [90, 150]      # questions of one owner are consecutive (backward plan)
+    ck = torch.randn(sum(state_lengths), shape.kv_heads, shape.head_dim, generator=gen).bfloat16()
+    cv = torch.randn(sum(state_lengths), shape.kv_heads, shape.head_dim, generator=gen).bfloat16()
+
+    module.zero_grad()
+    hd = hidden.to(DEV).requires_grad_(True)
+    if decoder:
+        layout = packing.packed_layout(lengths, [], DEV, owners=owners, state_lengths=state_lengths)
+        ckd, cvd = ck.to(DEV).requires_grad_(True), cv.to(DEV).requires_grad_(True)
+        out = packing.decoder_attention(module, hd[None], None, None, layout, (ckd, cvd))[0]
+    else:
+        layout = packing.packed_layout(lengths, [], DEV)
+        out = packing.encoder_attention(module, hd[None], None, layout)[0]
+    out.backward(dout.to(DEV)[None])
+
+    leaf = lambda v: v.detach().float().cpu().requires_grad_(True)
+    hf_, wq, wk, wv, wo = leaf(hidden), leaf(module.q_proj.weight), leaf(module.k_proj.weight), leaf(module.v_proj.weight), leaf(module.o_proj.weight)
+    gq, gk = leaf(module.q_norm.weight), leaf(module.k_norm.weight)
+    ckf, cvf = leaf(ck), leaf(cv)
+    q = om.linear(hf_, wq).view(t, shape.q_heads, shape.head_dim)
+    k = om.linear(hf_, wk).view(t, shape.kv_heads, shape.head_dim)
+    v = om.linear(hf_, wv).view(t, shape.kv_heads, shape.head_dim)
+    positions = torch.cat([torch.arange(n) for n in lengths])
+    cos, sin = om.rope_tables(positions, shape.head_dim, shape.layer_theta(layer_index), torch.float32)
+    q, k = om.qk_norm_rope(q, k, gq, gk, cos, sin, shape.eps)
+    window = shape.layer_window(layer_index)
+    if decoder:
+        attended, _ = om.varlen_attention(q, k, v, lengths, shape.scale, window, cross=(ckf, cvf), owners=owners,
+                                          state_lengths=state_lengths)
+    else:
+        attended, _ = om.varlen_attention(q, k, v, lengths, shape.scale, window)
+    want = om.linear(attended.reshape(t, -1), wo)
+    want.backward(dout.float())
+
+    def close(got, ref, what):
+        got, ref = got.detach().float().cpu().reshape(ref.shape), ref.detach()
+        err, scale = float((got - ref).abs().max()), float(ref.abs().max())
+        assert err < 4e-2 * scale + 2e-3, (what, err, scale)
+
+    close(out[0], want, 'out')
+    close(hd.grad, hf_.grad, 'dhidden')
+    for name, ref in (('q_proj', wq), ('k_proj', wk), ('v_proj', wv), ('o_proj', wo)):
+        close(getattr(module, name).weight.grad, ref.grad, name)
+    close(module.q_norm.weight.grad, gq.grad, 'q gain')
+    close(module.k_norm.weight.grad, gk.grad, 'k gain')
+    if decoder:
+        close(ckd.grad, ckf.grad, 'state k')
+        close(cvd.grad, cvf.grad, 'state v')
