@@ -381,3 +381,45 @@ def test_packed_attention_module_trains(tiny, decoder, layer_index):
     if decoder:
         close(ckd.grad, ckf.grad, 'state k')
         close(cvd.grad, cvf.grad, 'state v')
+
+
+def test_substituted_encoder_trains_like_the_native_one(tiny):
+    """Whole encoder, train mode: the backbone with every hot-path module substituted, driven packed, gives
+    the native backbone's parameter gradients (native: one dense sequence at a time, PyTorch autograd)."""
+    weights, _ = tiny
+    shape = wl.TINY
+    lengths = [70, 200]
+    gen = torch.Generator().manual_seed(21)
+    ids = [torch.randint(2, shape.vocab, (n,), generator=gen) for n in lengths]
+    dys = [torch.randn(n, shape.hidden, generator=gen).bfloat16().to(DEV) for n in lengths]
+
+    native = build_backbone(shape, weights).train()
+    for tokens, dy in zip(ids, dys):
+        out = native.encoder(input_ids=tokens.to(DEV)[None], use_cache=False).last_hidden_state
+        (out[0].float() * dy.float()).sum().backward()
+    want = {n: p.grad.float().cpu() for n, p in native.encoder.named_parameters() if p.grad is not None}
+
+    ours = build_backbone(shape, weights).train()
+    install_b200_inference(ours)
+    layout = packing.packed_layout(lengths, [], DEV)
+    empty = torch.empty(0, device=DEV)
+    out = ours.encoder(input_ids=torch.cat(ids).to(DEV)[None], position_ids=layout.positions,
+                       attention_mask={'full_attention': empty, 'sliding_attention': empty}, packed_layout=layout,
+                       use_cache=False).last_hidden_state
+    (out[0].float() * torch.cat(dys).float()).sum().backward()
+    got = {n: p.grad.float().cpu() for n, p in ours.encoder.named_parameters() if p.grad is not None}
+    # the converted MLP stacks gate and up into one trainable weight: back to the Hugging Face names
+    for name in [n for n in got if n.endswith('mlp.gate_up.weight')]:
+        layer = name[:-len('gate_up.weight')]
+        got[layer + 'gate_proj.weight'], got[layer + 'up_proj.weight'] = got[name].split(shape.intermediate)
+        got[layer + 'down_proj.weight'] = got[layer + 'down.weight']
+
+    checked = 0
+    for name, ref in want.items():
+        if 'vision' in name or float(ref.abs().max()) == 0:
+            continue
+        assert name in got, (name, sorted(got))
+        err, scale = float((got[name] - ref).abs().max()), float(ref.abs().max())
+        assert err < 6e-2 * scale + 1e-3, (name, err, scale)
+        checked += 1
+    assert checked >= 2 * 11       # per layer: 4 projections, 2 QK gains, 3 MLP weights, 4 norms (some tied names aside)
