@@ -6,6 +6,7 @@
     python -m bongard_b200.microbench glue [--tokens 32768]
     python -m bongard_b200.microbench serve [--shape 4b-4b] [--requests 40] [--no-graphs]
     python -m bongard_b200.microbench dropin [--shape 4b-4b] [--requests 32] [--group 8]
+    python -m bongard_b200.microbench train [--layers 2] [--train-sequences 8] [--length 4096]
 
 attention: packed encoder self-attention, lengths uniform in 256-4096 (seed 2), 8 query / 4 KV
 heads of 256, QK-norm + RoPE applied by the glue kernel first; FLOPs = 4 D Hq (visible pairs).
@@ -21,6 +22,9 @@ dropin: the Hugging Face backbone with the hot-path modules substituted (`instal
 driven through the reference's packed call sequence (`hf.PackedJudge.forward_packed`, decoder groups
 of 8 questions as the reference forms them), against `JudgmentEngine` on the same weights and
 requests: questions/s of both and the largest difference between their probabilities.
+train: forward + backward of the first encoder layers at the 4B width in train mode, the substituted
+modules on one pack against the native Hugging Face modules on the same sequences as a dense batch
+(PyTorch autograd, SDPA): time per step and model TFLOP/s of each.
 """
 
 from __future__ import annotations
@@ -275,11 +279,68 @@ def dropin(args, flush):
                 floor_max_abs_prob_diff=float((c - b).abs().max()), floor_mean_abs_prob_diff=float((c - b).abs().mean()))
 
 
+def train(args, flush):
+    import dataclasses
+
+    from transformers import T5Gemma2Model
+
+    from . import install, packing
+    from .hf import hf_config
+
+    full = wl.SHAPES['4b-4b']
+    shape = dataclasses.replace(full, layers=args.layers, layer_types=full.layer_types[:args.layers])
+    n, length = args.train_sequences, args.length
+    t = n * length
+    torch.manual_seed(9)
+    with torch.device(DEV):
+        backbone = T5Gemma2Model(hf_config(shape)).to(torch.bfloat16).train()
+    ids = torch.randint(2, shape.vocab, (n, length), device=DEV)
+    dy = randn(n, length, shape.hidden, seed=15)
+
+    # model FLOPs of one step: 2 per multiply-add, forward + 2x backward for the linears; attention forward
+    # 4 D Hq pairs, backward 2.5x that (five contractions against two)
+    per_token = 2 * (shape.hidden * (shape.q_dim + 2 * shape.kv_dim) + shape.q_dim * shape.hidden
+                     + 3 * shape.hidden * shape.intermediate)
+    flops = 0.0
+    for index in range(shape.layers):
+        window = shape.layer_window(index)
+        pairs = n * (length * length if window is None else
+                     sum(min(length, i + window // 2 + 1) - max(0, i - (window + 1) // 2 + 1) for i in range(length)))
+        flops += 3 * per_token * t + 3.5 * 4 * shape.head_dim * shape.q_heads * pairs
+
+    def step_native():
+        backbone.zero_grad(set_to_none=True)
+        out = backbone.encoder(input_ids=ids, use_cache=False).last_hidden_state
+        out.backward(dy)
+
+    ms_native = timed(step_native, args.iters, args.warmup, flush)
+    counts = install.install_b200_inference(backbone)
+    layout = packing.packed_layout([length] * n, [], DEV)
+    empty = torch.empty(0, device=DEV)
+    flat_ids, flat_dy = ids.reshape(1, t), dy.reshape(1, t, shape.hidden)
+
+    def step_ours():
+        backbone.zero_grad(set_to_none=True)
+        out = backbone.encoder(input_ids=flat_ids, position_ids=layout.positions,
+                               attention_mask={'full_attention': empty, 'sliding_attention': empty},
+                               packed_layout=layout, use_cache=False).last_hidden_state
+        out.backward(flat_dy)
+
+    ms_ours = timed(step_ours, args.iters, args.warmup, flush)
+    return dict(op='encoder_layers_forward_backward', layers=shape.layers, layer_types=list(shape.layer_types),
+                sequences=n, length=length, substituted=counts, model_tflop=flops / 1e12,
+                native_ms=ms_native, native_tflops=flops / ms_native / 1e9,
+                substituted_ms=ms_ours, substituted_tflops=flops / ms_ours / 1e9)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument('op', choices=['attention', 'mlp', 'linear', 'glue', 'serve', 'dropin'])
+    ap.add_argument('op', choices=['attention', 'mlp', 'linear', 'glue', 'serve', 'dropin', 'train'])
     ap.add_argument('--shape', default='4b-4b', choices=sorted(wl.SHAPES))
     ap.add_argument('--requests', type=int, default=40)
+    ap.add_argument('--layers', type=int, default=2, help='train: encoder layers')
+    ap.add_argument('--train-sequences', type=int, default=8, help='train: sequences per step')
+    ap.add_argument('--length', type=int, default=4096, help='train: tokens per sequence')
     ap.add_argument('--group', type=int, default=8, help='dropin: questions per decoder call (the reference\'s branch batch size)')
     ap.add_argument('--backward', action='store_true', help='attention: also time the backward passes')
     ap.add_argument('--few-rows', action='store_true', help='linear/mlp: allow the split-K kernel for <= 256 tokens')
@@ -295,7 +356,7 @@ def main():
     args = ap.parse_args()
     ops.device_check()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV) if args.flush else None
-    result = {'attention': attention, 'mlp': mlp, 'linear': linear, 'glue': glue, 'serve': serve, 'dropin': dropin}[args.op](args, flush)
+    result = {'attention': attention, 'mlp': mlp, 'linear': linear, 'glue': glue, 'serve': serve, 'dropin': dropin, 'train': train}[args.op](args, flush)
     ops.read_status()
     for row in result if isinstance(result, list) else [result]:
         print(json.dumps(row))
