@@ -7,7 +7,7 @@ import torch
 
 pytestmark = pytest.mark.gpu
 
-from bongard_b200 import flash_varlen, ops, packing, workload as wl  # noqa: E402
+from bongard_b200 import flash_varlen, packing, workload as wl  # noqa: E402
 from bongard_b200 import attention as b200_attention  # noqa: E402
 from bongard_b200.engine import JudgmentEngine  # noqa: E402
 from bongard_b200.float8_training import enable_float8  # noqa: E402
