@@ -309,14 +309,18 @@ class B200DecoderAttention(nn.Module):
         # first use: project the state the way bongard/model.py:135-139 project_state_kv does
         state = encoder_hidden_states
         d = self.head_dim
-        wkv = stacked_weight(self, ('k_proj', 'v_proj'), '_b200_wkv')
         kd = self.k_proj.weight.shape[0]
-        kv = _linear(state.reshape(-1, state.shape[-1]), wkv)
-        k = kv[:, :kd].view(-1, kd // d, d)
-        ops.qk_norm_rope_(None, k, None, self.k_norm.weight.detach().to(torch.bfloat16), None, None, self.k_norm.eps,
-                          rotate=False)
         shape = (state.shape[0], state.shape[1], kd // d, d)
-        keys = kv[:, :kd].view(shape).transpose(1, 2)
+        if needs_grad(self, state):
+            # train mode: the projection and the key norm record their backward kernels
+            kv = ops.linear_autograd(state.reshape(-1, state.shape[-1]), _trainable_weight(self, ('k_proj', 'v_proj')))
+            keys = ops.rmsnorm_autograd(kv[:, :kd].reshape(-1, d), self.k_norm.weight, self.k_norm.eps)
+            keys = keys.view(shape).transpose(1, 2)
+        else:
+            kv = _linear(state.reshape(-1, state.shape[-1]), stacked_weight(self, ('k_proj', 'v_proj'), '_b200_wkv'))
+            ops.qk_norm_rope_(None, kv[:, :kd].view(-1, kd // d, d), None, self.k_norm.weight.detach().to(torch.bfloat16),
+                              None, None, self.k_norm.eps, rotate=False)
+            keys = kv[:, :kd].view(shape).transpose(1, 2)
         values = kv[:, kd:].view(shape).transpose(1, 2)
         if cache is not None:
             cache.cross_attention_cache.update(keys, values, self.layer_idx)

@@ -423,3 +423,38 @@ def test_substituted_encoder_trains_like_the_native_one(tiny):
         assert err < 6e-2 * scale + 1e-3, (name, err, scale)
         checked += 1
     assert checked >= 2 * 11       # per layer: 4 projections, 2 QK gains, 3 MLP weights, 4 norms (some tied names aside)
+
+
+def test_state_projection_trains(tiny):
+    """The decoder's shared state K/V (bongard/model.py:135-139 project_state_kv: K = k_norm(k_proj(state)) without
+    rotation, V = v_proj(state)) is differentiable in train mode: state, both projections and the key gain."""
+    weights, _ = tiny
+    shape = wl.TINY
+    backbone = build_backbone(shape, weights).train()
+    install_b200_inference(backbone)
+    module = backbone.decoder.layers[1].self_attn
+    with torch.no_grad():
+        module.k_norm.weight.normal_(0, 0.2, generator=torch.Generator(device=DEV).manual_seed(3))
+    gen = torch.Generator().manual_seed(31)
+    s = 150
+    state = torch.randn(1, s, shape.hidden, generator=gen).bfloat16()
+    dk = torch.randn(1, shape.kv_heads, s, shape.head_dim, generator=gen).bfloat16()
+    dv = torch.randn(1, shape.kv_heads, s, shape.head_dim, generator=gen).bfloat16()
+    module.zero_grad()
+    sd = state.to(DEV).requires_grad_(True)
+    keys, values = module._cross(None, sd, None)
+    torch.autograd.backward([keys, values], [dk.to(DEV), dv.to(DEV)])
+    with torch.no_grad():
+        keys_inference, values_inference = module._cross(None, state.to(DEV), None)
+    assert float((keys - keys_inference).abs().max()) < 2e-2 and torch.equal(values, values_inference)
+
+    leaf = lambda v: v.detach().float().cpu().requires_grad_(True)
+    sf, wk, wv, gk = leaf(state), leaf(module.k_proj.weight), leaf(module.v_proj.weight), leaf(module.k_norm.weight)
+    k = om.rmsnorm(om.linear(sf[0], wk).view(s, shape.kv_heads, shape.head_dim), gk, shape.eps)
+    v = om.linear(sf[0], wv).view(s, shape.kv_heads, shape.head_dim)
+    torch.autograd.backward([k, v], [dk[0].transpose(0, 1).float(), dv[0].transpose(0, 1).float()])
+    for got, ref, what in ((sd.grad, sf.grad, 'state'), (module.k_proj.weight.grad, wk.grad, 'k_proj'),
+                           (module.v_proj.weight.grad, wv.grad, 'v_proj'), (module.k_norm.weight.grad, gk.grad, 'k gain')):
+        got = got.float().cpu().reshape(ref.shape)
+        err, scale = float((got - ref).abs().max()), float(ref.abs().max())
+        assert err < 4e-2 * scale + 2e-3, (what, err, scale)
