@@ -40,6 +40,9 @@ struct PairParams {
     int tiles_m, tiles_n;         // in units of 256-row pair tiles
     int group_m;
     int32_t* status;
+    // epilogue 3 (split-K): work item = (tile, K slice); fp32 partial tiles [split_k, m, n] summed by a second kernel
+    int split_k;
+    float* partial;
     // epilogue 2 (q|k|v projection with QK-norm + RoPE)
     int q_dim, kv_dim, head_dim, table_rows;
     float eps;
@@ -117,7 +120,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     }
 
     const int pairs = gridDim.x >> 1, pair = blockIdx.x >> 1;
-    const int num_tiles = p.tiles_m * p.tiles_n;
+    // With split-K the work list is num_tiles * split_k items: item i covers K-blocks
+    // [slice * kblocks / split_k, (slice + 1) * kblocks / split_k) of tile i % tiles, slice = i / tiles.
+    const int mn_tiles = p.tiles_m * p.tiles_n;
+    const int num_tiles = mn_tiles * p.split_k;
     const int kblocks = (p.k + BK - 1) / BK;
 
     if (warp == 0) {
@@ -126,12 +132,14 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             uint32_t phase = 0;
             for (int tile = pair; tile < num_tiles; tile += pairs) {
                 int tm, tn;
-                tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+                tile_coords(tile % mn_tiles, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+                const int slice = tile / mn_tiles;
+                const int kb0 = slice * kblocks / p.split_k, kb1 = (slice + 1) * kblocks / p.split_k;
                 const int row0 = tm * 2 * BM + rank * BM;
                 // this CTA's half of the weight panel: plain -> columns [256 tn + 128 rank, +128);
                 // GeGLU -> rank 0 loads 128 gate rows, rank 1 the matching 128 up rows.
                 const int w0 = p.epilogue == 1 ? (rank == 0 ? tn * 128 : p.n + tn * 128) : tn * BN + rank * 128;
-                for (int kb = 0; kb < kblocks; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(&empty[stage], phase ^ 1, ab, 111)) break;
                     uint8_t* sa = smem + stage * STAGE_BYTES;
                     const uint32_t leader_full = map_to_cta(smem_u32(&full[stage]), 0);
@@ -153,7 +161,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                 if (!mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, ab, 112)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
-                for (int kb = 0; kb < kblocks; ++kb) {
+                const int slice = tile / mn_tiles;
+                const int kb0 = slice * kblocks / p.split_k, kb1 = (slice + 1) * kblocks / p.split_k;
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(&full[stage], phase, ab, 113)) break;
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
@@ -162,7 +172,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     for (int kk = 0; kk < BK / 16; ++kk) {
                         uint64_t da = smem_desc_sw128(sa + kk * 32, 16, 1024);
                         uint64_t db = smem_desc_sw128(sb + kk * 32, 16, 1024);
-                        mma_bf16_ss_pair(d_tmem, da, db, idesc, (kb | kk) != 0);
+                        mma_bf16_ss_pair(d_tmem, da, db, idesc, kb != kb0 || kk != 0);
                     }
                     const uint32_t e = smem_u32(&empty[stage]);
                     mma_commit_pair(map_to_cta(e, 0));
@@ -180,7 +190,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         int local = 0;
         for (int tile = pair; tile < num_tiles; tile += pairs, ++local) {
             int tm, tn;
-            tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+            tile_coords(tile % mn_tiles, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
             const int buf = local & 1;
             if (!mbar_wait(&acc_full[buf], (local >> 1) & 1, ab, 114)) break;
             tc_fence_after();
@@ -272,6 +282,23 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                         }
                     }
                 }
+            } else if (p.epilogue == 3) {
+                // split-K: this item's fp32 partial sums, unrounded
+                const int col0 = tn * BN;
+                float* dst = p.partial + (int64_t(tile / mn_tiles) * p.m + row) * p.n + col0;
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(taddr + c, r);
+                    tmem_wait_ld();
+                    if (row < p.m) {
+#pragma unroll
+                        for (int v = 0; v < 8; ++v) {
+                            if (col0 + c + v * 4 < p.n)
+                                *reinterpret_cast<uint4*>(dst + c + v * 4) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+                        }
+                    }
+                }
             } else if (p.epilogue == 0) {
                 const int col0 = tn * BN;
                 __nv_bfloat16* dst = p.out + int64_t(row) * p.ldo + col0;
@@ -341,6 +368,27 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     }
 }
 
+// out[r, c] = bf16(sum over slices of partial[slice, r, c]); eight columns per thread (n % 8 == 0).
+__global__ void sum_partials_kernel(const float* __restrict__ partial, int split, int64_t m, int64_t n,
+                                    __nv_bfloat16* __restrict__ out, int64_t ldo) {
+    pdl_wait();
+    const int64_t i = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
+    if (i >= m * n) return;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < split; ++s) {
+        const float4 a = *reinterpret_cast<const float4*>(partial + s * m * n + i);
+        const float4 b = *reinterpret_cast<const float4*>(partial + s * m * n + i + 4);
+        acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+        acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+    }
+    uint4 o;
+    o.x = pack_bf16(acc[0], acc[1]);
+    o.y = pack_bf16(acc[2], acc[3]);
+    o.z = pack_bf16(acc[4], acc[5]);
+    o.w = pack_bf16(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + (i / n) * ldo + i % n) = o;
+}
+
 }  // namespace
 
 static int pair_launch(PairParams p, const CUtensorMap& map_a, const CUtensorMap& map_w, void* out, int64_t ldo,
@@ -389,9 +437,37 @@ extern "C" int bg_gemm_bf16_qkv_rope(const void* a, int64_t lda, const void* w, 
     return pair_launch(p, map_a, map_w, out, ldo, m, n, k, 2, static_cast<cudaStream_t>(stream));
 }
 
+// Number of CTA pairs that can be resident at once (pairs must sit inside one GPC, so it can be
+// fewer than SMs / 2); the persistent grid is sized to it so that every pair starts immediately.
+static int resident_pairs() {
+    static int max_pairs = 0;
+    if (!max_pairs) {
+        cudaFuncSetAttribute(gemm_bf16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * (bg_num_sms() / 2));
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = SMEM_BYTES;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_pair_kernel, &cfg) != cudaSuccess || n <= 0) {
+            cudaGetLastError();
+            n = bg_num_sms() / 2;
+        }
+        max_pairs = n < bg_num_sms() / 2 ? n : bg_num_sms() / 2;
+    }
+    return max_pairs;
+}
+
 static int pair_launch(PairParams p, const CUtensorMap& map_a, const CUtensorMap& map_w, void* out, int64_t ldo,
                        int64_t m, int64_t n, int64_t k, int epilogue, cudaStream_t stream) {
     p.m = (int)m; p.n = (int)n; p.k = (int)k; p.epilogue = epilogue; p.ldo = ldo;
+    if (p.split_k < 1) p.split_k = 1;
     p.out = static_cast<__nv_bfloat16*>(out);
     p.tiles_m = (int)((m + 2 * BM - 1) / (2 * BM));
     p.tiles_n = epilogue == 1 ? (int)(n / 128) : (int)((n + BN - 1) / BN);
@@ -411,34 +487,89 @@ static int pair_launch(PairParams p, const CUtensorMap& map_a, const CUtensorMap
         }
         configured = true;
     }
-    // Number of CTA pairs that can be resident at once (pairs must sit inside one GPC, so it can be
-    // fewer than SMs / 2); the persistent grid is sized to it so that every pair starts immediately.
-    static int max_pairs = 0;
-    if (!max_pairs) {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(2 * (bg_num_sms() / 2));
-        cfg.blockDim = dim3(THREADS);
-        cfg.dynamicSmemBytes = SMEM_BYTES;
-        cudaLaunchAttribute attr;
-        attr.id = cudaLaunchAttributeClusterDimension;
-        attr.val.clusterDim.x = 2;
-        attr.val.clusterDim.y = 1;
-        attr.val.clusterDim.z = 1;
-        cfg.attrs = &attr;
-        cfg.numAttrs = 1;
-        int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_pair_kernel, &cfg) != cudaSuccess || n <= 0) {
-            cudaGetLastError();
-            n = bg_num_sms() / 2;
-        }
-        max_pairs = n < bg_num_sms() / 2 ? n : bg_num_sms() / 2;
-    }
-    const int tiles = p.tiles_m * p.tiles_n;
+    const int max_pairs = resident_pairs();
+    const int tiles = p.tiles_m * p.tiles_n * p.split_k;
     const int pairs = tiles < max_pairs ? tiles : max_pairs;
     cudaError_t e = launch_kernel(gemm_bf16_pair_kernel, dim3((unsigned)(2 * pairs)), dim3(THREADS), SMEM_BYTES, stream,
                                   0, map_a, map_w, p);
     if (e != cudaSuccess) {
         bg_set_error("bg_gemm_bf16: launch(pair): %s", cudaGetErrorString(e));
+        return BG_ERR_LAUNCH;
+    }
+    return BG_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Split-K for problems whose 256 x 256 output tiles fill less than half of the machine (a few hundred
+// rows against a narrow weight with a long contraction: the down projection of a short request).
+// Each (tile, K slice) is one work item of the same persistent kernel; slices write fp32 partial tiles
+// to the caller's workspace and a second kernel sums them in slice order and rounds once.
+
+static int splitk_choice(int64_t m, int64_t n, int64_t k) {
+    if (m <= 0 || n <= 0 || k < 4096 || n % 8) return 1;
+    const int64_t tiles = ((m + 2 * BM - 1) / (2 * BM)) * ((n + BN - 1) / BN);
+    const int pairs = resident_pairs();
+    if (tiles >= pairs) return 1;
+    // time ~ waves of the persistent grid x the length of one item: ceil(tiles * s / pairs) / s, plus the
+    // partial-sum traffic; a split has to save at least 15 % to be taken
+    const int64_t kblocks = (k + BK - 1) / BK;
+    int best = 1;
+    double best_cost = 1.0;
+    for (int split = 2; split <= 4 && kblocks >= 16 * split; ++split) {
+        const double cost = double((tiles * split + pairs - 1) / pairs) / split + 0.03 * (split - 1);
+        if (cost < best_cost - 1e-9 && cost <= 0.85) {
+            best = split;
+            best_cost = cost;
+        }
+    }
+    return best;
+}
+
+extern "C" int bg_gemm_bf16_splitk_choice(int64_t m, int64_t n, int64_t k) { return splitk_choice(m, n, k); }
+
+extern "C" int64_t bg_gemm_bf16_splitk_workspace_bytes(int64_t m, int64_t n, int split) {
+    return (m <= 0 || n <= 0 || split < 2) ? 0 : int64_t(split) * m * n * int64_t(sizeof(float));
+}
+
+extern "C" int bg_gemm_bf16_splitk(const void* a, int64_t lda, const void* w, int64_t ldw, void* out, int64_t ldo,
+                                   int64_t m, int64_t n, int64_t k, int split, void* workspace,
+                                   int64_t workspace_bytes, void* stream) {
+    const int64_t kblocks = (k + BK - 1) / BK;
+    if (m < 0 || n <= 0 || k <= 0 || n % 8 || split < 2 || split > 8 || kblocks < 4 * split) {
+        bg_set_error("bg_gemm_bf16_splitk: bad shape (n must be a multiple of 8, 2 <= split <= 8 slices of at least 4 K-blocks)");
+        return BG_ERR_SHAPE;
+    }
+    if (m == 0) return BG_OK;
+    if ((k % 8) || (lda % 8) || (ldw % 8) || (ldo % 8) ||
+        ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out) |
+          reinterpret_cast<uintptr_t>(workspace)) & 15)) {
+        bg_set_error("bg_gemm_bf16_splitk: pointers must be 16-byte aligned, k and leading dimensions multiples of 8");
+        return BG_ERR_ALIGN;
+    }
+    if (workspace == nullptr || workspace_bytes < bg_gemm_bf16_splitk_workspace_bytes(m, n, split)) {
+        bg_set_error("bg_gemm_bf16_splitk: the workspace is too small");
+        return BG_ERR_WORKSPACE;
+    }
+    CUtensorMap map_a, map_w;
+    uint64_t dims_a[2] = {(uint64_t)k, (uint64_t)m}, str_a[1] = {(uint64_t)lda * 2};
+    uint64_t dims_w[2] = {(uint64_t)k, (uint64_t)n}, str_w[1] = {(uint64_t)ldw * 2};
+    uint32_t box_a[2] = {BK, BM}, box_w[2] = {BK, 128};
+    int rc = bg_make_tensor_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a, dims_a, str_a, box_a,
+                                CU_TENSOR_MAP_SWIZZLE_128B);
+    if (!rc) rc = bg_make_tensor_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, dims_w, str_w, box_w,
+                                     CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    PairParams p = {};
+    p.split_k = split;
+    p.partial = static_cast<float*>(workspace);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    rc = pair_launch(p, map_a, map_w, out, ldo, m, n, k, 3, s);
+    if (rc) return rc;
+    const int64_t groups = m * n / 8;
+    cudaError_t e = launch_kernel(sum_partials_kernel, dim3((unsigned)((groups + 255) / 256)), dim3(256), 0, s, 0,
+                                  static_cast<const float*>(workspace), split, m, n, static_cast<__nv_bfloat16*>(out), ldo);
+    if (e != cudaSuccess) {
+        bg_set_error("bg_gemm_bf16_splitk: launch(sum): %s", cudaGetErrorString(e));
         return BG_ERR_LAUNCH;
     }
     return BG_OK;

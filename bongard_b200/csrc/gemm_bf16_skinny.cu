@@ -104,7 +104,21 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    pdl_wait();                   // the predecessor in the stream has finished; from here on global memory may be touched
+    // The weights do not depend on the predecessor in the stream (only the activations do), so the first ring
+    // fill of weight tiles is requested before the wait for it: under a programmatic launch the ~2 us from the
+    // first request to the first byte overlap the predecessor's tail.  Each stage's barrier is armed for the
+    // stage's full byte count here; the activation tiles join after the wait.
+    const int w0 = p.epilogue == 1 ? tile * p.half : tile * p.bn;
+    const int prefilled = min(p.stages, kb_hi - kb_lo);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < prefilled; ++s) {
+            uint8_t* sb = smem + s * p.stage_bytes + p.row_tiles * TILE_BYTES;
+            mbar_expect_tx(&full[s], uint32_t(p.row_tiles * BM + p.bn) * BK * 2);
+            tma_load_2d(sb, &map_w, &full[s], (kb_lo + s) * BK, w0);
+            if (p.epilogue == 1) tma_load_2d(sb + p.half * BK * 2, &map_w, &full[s], (kb_lo + s) * BK, p.n + w0);
+        }
+    }
+    pdl_wait();                   // the predecessor in the stream has finished; from here on every global buffer may be touched
     pdl_launch_dependents();      // the successor may start its own prologue
 
     const int part = warp & 3;
@@ -131,15 +145,17 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0;
-            const int w0 = p.epilogue == 1 ? tile * p.half : tile * p.bn;
             for (int kb = kb_lo; kb < kb_hi; ++kb) {
                 if (!mbar_wait(&empty[stage], phase ^ 1, ab, 301)) break;
                 uint8_t* sa = smem + stage * p.stage_bytes;
                 uint8_t* sb = sa + p.row_tiles * TILE_BYTES;
-                mbar_expect_tx(&full[stage], uint32_t(p.row_tiles * BM + p.bn) * BK * 2);
+                const bool weights_requested = kb - kb_lo < prefilled;       // armed and requested before the wait above
+                if (!weights_requested) mbar_expect_tx(&full[stage], uint32_t(p.row_tiles * BM + p.bn) * BK * 2);
                 for (int t = 0; t < p.row_tiles; ++t)
                     tma_load_2d(sa + t * TILE_BYTES, &map_a, &full[stage], kb * BK, t * BM);
-                if (p.epilogue == 1) {
+                if (weights_requested) {
+                    // nothing more to ask for
+                } else if (p.epilogue == 1) {
                     tma_load_2d(sb, &map_w, &full[stage], kb * BK, w0);
                     tma_load_2d(sb + p.half * BK * 2, &map_w, &full[stage], kb * BK, p.n + w0);
                 } else {

@@ -194,6 +194,7 @@ def serve(args, flush):
     from .serving import Predictor
 
     shape = wl.SHAPES[args.shape]
+    ops.SPLIT_K = not args.no_split_k
     engine = JudgmentEngine(wl.make_weights_device(shape, 4, DEV), shape)
     served = Predictor(engine, graphs=not args.no_graphs, programmatic_launch=not args.no_pdl)
 
@@ -338,6 +339,7 @@ def main():
     ap.add_argument('op', choices=['attention', 'mlp', 'linear', 'glue', 'serve', 'dropin', 'train'])
     ap.add_argument('--shape', default='4b-4b', choices=sorted(wl.SHAPES))
     ap.add_argument('--requests', type=int, default=40)
+    ap.add_argument('--no-split-k', action='store_true', help='serve: no K slices for under-filled projections')
     ap.add_argument('--layers', type=int, default=2, help='train: encoder layers')
     ap.add_argument('--train-sequences', type=int, default=8, help='train: sequences per step')
     ap.add_argument('--length', type=int, default=4096, help='train: tokens per sequence')

@@ -158,6 +158,9 @@ def embed(ids, table, eoi_embedding, scale, eoi_token=256_000):
     return out
 
 
+SPLIT_K = True      # latency path: allow K slices for under-filled problems (microbench turns it off to compare)
+
+
 def _gemm(lib, few_rows, m, n, k, epilogue):
     """The entry point for a contraction: the weight-streaming kernel when the caller allows it
     (`few_rows`) and the shape is one it takes, else the throughput kernels."""
@@ -167,9 +170,10 @@ def _gemm(lib, few_rows, m, n, k, epilogue):
 
 
 def linear(x, weight, out=None, *, few_rows=False):
-    """x [..., K] @ weight[N, K].T -> [..., N] on the tensor cores.  `few_rows=True` lets inputs of
-    up to 256 rows take the split-K weight-streaming kernel (latency path; its fp32 summation
-    order differs from the throughput kernels)."""
+    """x [..., K] @ weight[N, K].T -> [..., N] on the tensor cores.  `few_rows=True` is the latency path:
+    inputs of up to 256 rows take the weight-streaming cluster split-K kernel, a few hundred rows against a
+    narrow weight with a long contraction take the CTA-pair kernel with K slices as extra work items
+    (fp32 summation order differs from the throughput kernels in both)."""
     lib = _lib.load()
     flat, m, k, lda = _rows(x, 'x')
     _need(weight, 'weight')
@@ -180,8 +184,16 @@ def linear(x, weight, out=None, *, few_rows=False):
         out = torch.empty((m, n), device=x.device, dtype=BF16)
     timer = GEMM_TIMER
     begin = timer.start() if timer is not None else None
-    fn, name = _gemm(lib, few_rows, m, n, k, 0)
-    _lib.check(fn(_ptr(flat), lda, _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), m, n, k, 0, _stream()), name)
+    split = lib.bg_gemm_bf16_splitk_choice(m, n, k) if few_rows and SPLIT_K and m > 256 else 1
+    if split > 1:
+        # a few hundred rows against a narrow weight: K slices as extra work items, fp32 partials summed once
+        need = lib.bg_gemm_bf16_splitk_workspace_bytes(m, n, split)
+        work = torch.empty((need,), device=x.device, dtype=torch.uint8)
+        _lib.check(lib.bg_gemm_bf16_splitk(_ptr(flat), lda, _ptr(weight), weight.stride(0), _ptr(out), out.stride(0),
+                                           m, n, k, split, _ptr(work), need, _stream()), 'bg_gemm_bf16_splitk')
+    else:
+        fn, name = _gemm(lib, few_rows, m, n, k, 0)
+        _lib.check(fn(_ptr(flat), lda, _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), m, n, k, 0, _stream()), name)
     if timer is not None:
         timer.stop(begin, 2 * m * n * k)
     return out.view(*x.shape[:-1], n)

@@ -121,6 +121,18 @@ int bg_gemm_bf16_skinny_supported(int64_t m, int64_t n, int64_t k, int epilogue)
 int bg_gemm_bf16_skinny(const void* a, int64_t lda, const void* w, int64_t ldw, void* out, int64_t ldo, int64_t m,
                         int64_t n, int64_t k, int epilogue, void* stream);
 
+/* Split-K form of bg_gemm_bf16 (plain epilogue) for problems whose 256 x 256 output tiles fill less than
+ * half of the GPU: a few hundred rows against a narrow weight with a long contraction (the down projection
+ * of a short request on the single-request path, bongard/inference.py:283-340).  Each (tile, K slice) is a
+ * work item of the CTA-pair kernel; slices write fp32 partial tiles into the caller's workspace and a second
+ * kernel sums them in slice order and rounds once to bf16.
+ *   bg_gemm_bf16_splitk_choice: the number of slices worth using for a shape (1 = use bg_gemm_bf16).
+ *   bg_gemm_bf16_splitk_workspace_bytes: split * m * n * 4. */
+int bg_gemm_bf16_splitk_choice(int64_t m, int64_t n, int64_t k);
+int64_t bg_gemm_bf16_splitk_workspace_bytes(int64_t m, int64_t n, int split);
+int bg_gemm_bf16_splitk(const void* a, int64_t lda, const void* w, int64_t ldw, void* out, int64_t ldo, int64_t m,
+                        int64_t n, int64_t k, int split, void* workspace, int64_t workspace_bytes, void* stream);
+
 /* Helpers for the backward of the bf16 linears (the reference trains through them with autograd:
  * bongard/te_linear.py:59-77 TELinear.forward, 98-103 TEMLP.forward, bongard/fused_mlp.py:62-79).
  * With y = x W^T: dx = dy W and dW = dy^T x contract over dimensions that are not contiguous in dy, W

@@ -324,3 +324,32 @@ def test_qk_norm_rope_backward(d, hq, hkv, theta):
     assert none_k is None and none_w is None
     assert_close(dxk, kf3.grad, atol=1e-2, rtol=8e-3)
     assert_close(dkw, kwf3.grad, atol=tol_w, rtol=8e-3)
+
+
+@pytest.mark.parametrize('m,n,k', [(300, 2560, 10240), (640, 2560, 10240), (1000, 2560, 10240), (513, 1024, 4096),
+                                   (700, 2048, 8200)])
+def test_linear_split_k(m, n, k):
+    """A few hundred rows against a narrow weight with a long contraction: K slices as extra work items of the
+    CTA-pair kernel, fp32 partials summed once.  Against fp32, against the unsplit kernel, and repeatable."""
+    from bongard_b200 import _lib
+
+    lib = _lib.load()
+    split = lib.bg_gemm_bf16_splitk_choice(m, n, k)
+    assert split >= 2, 'the shape is meant to take the split-K path'
+    x, w = rnd(m, k, seed=70), rnd(n, k, seed=71, std=0.02)
+    xd, wd = x.to(DEV), w.to(DEV)
+    got = ops.linear(xd, wd, few_rows=True)
+    assert_close(got, x.float() @ w.float().t())
+    assert_close(got, ops.linear(xd, wd).float(), atol=2e-3, rtol=8e-3)
+    assert torch.equal(got, ops.linear(xd, wd, few_rows=True))
+    # strided input and output views
+    big = torch.zeros(m, n + 64, device=DEV, dtype=torch.bfloat16)
+    wide = torch.cat([xd, xd], 1)
+    ops.linear(wide[:, k:], wd, out=big[:, 64:], few_rows=True)
+    assert torch.equal(big[:, 64:], got) and float(big[:, :64].abs().max()) == 0
+    # the entry point's own checks
+    work = torch.empty(lib.bg_gemm_bf16_splitk_workspace_bytes(m, n, split), device=DEV, dtype=torch.uint8)
+    args = (xd.data_ptr(), k, wd.data_ptr(), k, got.data_ptr(), n, m, n, k)
+    assert lib.bg_gemm_bf16_splitk(*args, split, work.data_ptr(), work.numel() - 16, None) == -5      # workspace
+    assert lib.bg_gemm_bf16_splitk(*args, 1, work.data_ptr(), work.numel(), None) == -1               # split < 2
+    assert lib.bg_gemm_bf16_splitk_choice(8192, 2560, 10240) == 1 and lib.bg_gemm_bf16_splitk_choice(640, 2560, 2048) == 1
