@@ -43,6 +43,7 @@ struct PairParams {
     // epilogue 3 (split-K): work item = (tile, K slice); fp32 partial tiles [split_k, m, n] summed by a second kernel
     int split_k;
     float* partial;
+    int mn_major;                 // host side only: selects the MN-major instantiation
     // epilogue 2 (q|k|v projection with QK-norm + RoPE)
     int q_dim, kv_dim, head_dim, table_rows;
     float eps;
@@ -66,6 +67,11 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
     tn = in_group / rows;
 }
 
+// MN = true is the weight-gradient form: out[M, N] = sum_k At[k, M] * Wt[k, N] with both operands stored
+// with the contraction as the ROW index (dW = dy^T x straight from dy [tokens, out] and x [tokens, in]).
+// A stage then holds, per operand, two slabs of 64 contraction rows x 64 elements (128 B, swizzled) instead of
+// 128 rows x 64 contraction elements, and the MMA descriptors say "MN-major".
+template <bool MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                       const PairParams p) {
@@ -144,15 +150,22 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     uint8_t* sa = smem + stage * STAGE_BYTES;
                     const uint32_t leader_full = map_to_cta(smem_u32(&full[stage]), 0);
                     if (leader) mbar_expect_tx(&full[stage], 2 * STAGE_BYTES);
-                    tma_load_2d_pair(sa, &map_a, leader_full, kb * BK, row0);
-                    tma_load_2d_pair(sa + A_BYTES, &map_w, leader_full, kb * BK, w0);
+                    if constexpr (MN) {
+                        tma_load_2d_pair(sa, &map_a, leader_full, row0, kb * BK);
+                        tma_load_2d_pair(sa + A_BYTES / 2, &map_a, leader_full, row0 + 64, kb * BK);
+                        tma_load_2d_pair(sa + A_BYTES, &map_w, leader_full, w0, kb * BK);
+                        tma_load_2d_pair(sa + A_BYTES + B_BYTES / 2, &map_w, leader_full, w0 + 64, kb * BK);
+                    } else {
+                        tma_load_2d_pair(sa, &map_a, leader_full, kb * BK, row0);
+                        tma_load_2d_pair(sa + A_BYTES, &map_w, leader_full, kb * BK, w0);
+                    }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0 && leader) {
-            constexpr uint32_t idesc = instr_desc(2 * BM, BN, 1, 1, 0, 0);
+            constexpr uint32_t idesc = instr_desc(2 * BM, BN, 1, 1, MN ? 1 : 0, MN ? 1 : 0);
             int stage = 0;
             uint32_t phase = 0;
             int local = 0;
@@ -170,8 +183,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     const uint32_t sb = sa + A_BYTES;
 #pragma unroll
                     for (int kk = 0; kk < BK / 16; ++kk) {
-                        uint64_t da = smem_desc_sw128(sa + kk * 32, 16, 1024);
-                        uint64_t db = smem_desc_sw128(sb + kk * 32, 16, 1024);
+                        // K-major: 32 B along the swizzled row per 16-deep step; MN-major: 16 contraction rows of
+                        // 128 B per step, slabs of 64 elements 8 KB apart
+                        uint64_t da = MN ? smem_desc_sw128(sa + kk * 2048, A_BYTES / 2, 1024) : smem_desc_sw128(sa + kk * 32, 16, 1024);
+                        uint64_t db = MN ? smem_desc_sw128(sb + kk * 2048, B_BYTES / 2, 1024) : smem_desc_sw128(sb + kk * 32, 16, 1024);
                         mma_bf16_ss_pair(d_tmem, da, db, idesc, kb != kb0 || kk != 0);
                     }
                     const uint32_t e = smem_u32(&empty[stage]);
@@ -442,7 +457,7 @@ extern "C" int bg_gemm_bf16_qkv_rope(const void* a, int64_t lda, const void* w, 
 static int resident_pairs() {
     static int max_pairs = 0;
     if (!max_pairs) {
-        cudaFuncSetAttribute(gemm_bf16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaFuncSetAttribute(gemm_bf16_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2 * (bg_num_sms() / 2));
         cfg.blockDim = dim3(THREADS);
@@ -455,7 +470,7 @@ static int resident_pairs() {
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
         int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_pair_kernel, &cfg) != cudaSuccess || n <= 0) {
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_pair_kernel<false>, &cfg) != cudaSuccess || n <= 0) {
             cudaGetLastError();
             n = bg_num_sms() / 2;
         }
@@ -480,7 +495,9 @@ static int pair_launch(PairParams p, const CUtensorMap& map_a, const CUtensorMap
     if (!p.status) return BG_ERR_DRIVER;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(gemm_bf16_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) {
             bg_set_error("bg_gemm_bf16: cudaFuncSetAttribute(pair): %s", cudaGetErrorString(e));
             return BG_ERR_LAUNCH;
@@ -490,8 +507,10 @@ static int pair_launch(PairParams p, const CUtensorMap& map_a, const CUtensorMap
     const int max_pairs = resident_pairs();
     const int tiles = p.tiles_m * p.tiles_n * p.split_k;
     const int pairs = tiles < max_pairs ? tiles : max_pairs;
-    cudaError_t e = launch_kernel(gemm_bf16_pair_kernel, dim3((unsigned)(2 * pairs)), dim3(THREADS), SMEM_BYTES, stream,
-                                  0, map_a, map_w, p);
+    cudaError_t e = p.mn_major ? launch_kernel(gemm_bf16_pair_kernel<true>, dim3((unsigned)(2 * pairs)), dim3(THREADS),
+                                               SMEM_BYTES, stream, 0, map_a, map_w, p)
+                               : launch_kernel(gemm_bf16_pair_kernel<false>, dim3((unsigned)(2 * pairs)), dim3(THREADS),
+                                               SMEM_BYTES, stream, 0, map_a, map_w, p);
     if (e != cudaSuccess) {
         bg_set_error("bg_gemm_bf16: launch(pair): %s", cudaGetErrorString(e));
         return BG_ERR_LAUNCH;
@@ -573,4 +592,31 @@ extern "C" int bg_gemm_bf16_splitk(const void* a, int64_t lda, const void* w, in
         return BG_ERR_LAUNCH;
     }
     return BG_OK;
+}
+
+// out[m, n] = sum_k at[k, m] * wt[k, n]: both operands with the contraction as the row index.  This is the
+// weight gradient dW = dy^T x taken straight from dy [tokens, out features] and x [tokens, in features].
+extern "C" int bg_gemm_bf16_tn(const void* at, int64_t ldat, const void* wt, int64_t ldwt, void* out, int64_t ldo,
+                               int64_t m, int64_t n, int64_t k, void* stream) {
+    if (m <= 0 || n <= 0 || k <= 0) {
+        bg_set_error("bg_gemm_bf16_tn: bad shape");
+        return BG_ERR_SHAPE;
+    }
+    if ((m % 8) || (n % 8) || (ldat % 8) || (ldwt % 8) || (ldo % 8) || ldat < m || ldwt < n || ldo < n ||
+        ((reinterpret_cast<uintptr_t>(at) | reinterpret_cast<uintptr_t>(wt) | reinterpret_cast<uintptr_t>(out)) & 15)) {
+        bg_set_error("bg_gemm_bf16_tn: pointers must be 16-byte aligned, m, n and the leading dimensions multiples of 8");
+        return BG_ERR_ALIGN;
+    }
+    CUtensorMap map_a, map_w;
+    uint64_t dims_a[2] = {(uint64_t)m, (uint64_t)k}, str_a[1] = {(uint64_t)ldat * 2};
+    uint64_t dims_w[2] = {(uint64_t)n, (uint64_t)k}, str_w[1] = {(uint64_t)ldwt * 2};
+    uint32_t box[2] = {64, BK};
+    int rc = bg_make_tensor_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, at, dims_a, str_a, box,
+                                CU_TENSOR_MAP_SWIZZLE_128B);
+    if (!rc) rc = bg_make_tensor_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, wt, dims_w, str_w, box,
+                                     CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    PairParams p = {};
+    p.mn_major = 1;
+    return pair_launch(p, map_a, map_w, out, ldo, m, n, k, 0, static_cast<cudaStream_t>(stream));
 }

@@ -284,8 +284,32 @@ def linear_backward(x, weight, dy, *, need_dx=True, need_dw=True):
     if need_dx:
         dx = linear(dy2, transpose(weight)).view(x.shape)             # contraction over N
     if need_dw:
-        dw = linear(transpose(dy2), transpose(flat))                 # contraction over the rows, zero padded
+        dw = linear_tn(dy2, flat)                                     # contraction over the rows, operands as they lie
     return dx, dw
+
+
+def linear_tn(at, wt):
+    """at [R, M], wt [R, N] -> at.T @ wt [M, N]: the contraction runs over the rows of both operands, which the
+    tensor core reads as MN-major tiles (no transposed copies).  Shapes the entry point does not take (M or N
+    not a multiple of 8, misaligned views) go through explicit transposes."""
+    lib = _lib.load()
+    _need(at, 'at'), _need(wt, 'wt')
+    if at.ndim != 2 or wt.ndim != 2 or at.shape[0] != wt.shape[0] or at.stride(1) != 1 or wt.stride(1) != 1:
+        raise ValueError('linear_tn takes two 2-D tensors with contiguous rows and the same number of rows')
+    r, m = at.shape
+    n = wt.shape[1]
+    direct = (m % 8 == 0 and n % 8 == 0 and at.stride(0) % 8 == 0 and wt.stride(0) % 8 == 0
+              and at.data_ptr() % 16 == 0 and wt.data_ptr() % 16 == 0 and r > 0)
+    if not direct:
+        return linear(transpose(at), transpose(wt))
+    out = torch.empty((m, n), device=at.device, dtype=BF16)
+    timer = GEMM_TIMER
+    begin = timer.start() if timer is not None else None
+    _lib.check(lib.bg_gemm_bf16_tn(_ptr(at), at.stride(0), _ptr(wt), wt.stride(0), _ptr(out), n, m, n, r, _stream()),
+               'bg_gemm_bf16_tn')
+    if timer is not None:
+        timer.stop(begin, 2 * m * n * r)
+    return out
 
 
 class _Linear(torch.autograd.Function):

@@ -353,3 +353,22 @@ def test_linear_split_k(m, n, k):
     assert lib.bg_gemm_bf16_splitk(*args, split, work.data_ptr(), work.numel() - 16, None) == -5      # workspace
     assert lib.bg_gemm_bf16_splitk(*args, 1, work.data_ptr(), work.numel(), None) == -1               # split < 2
     assert lib.bg_gemm_bf16_splitk_choice(8192, 2560, 10240) == 1 and lib.bg_gemm_bf16_splitk_choice(640, 2560, 2048) == 1
+
+
+@pytest.mark.parametrize('r,m,n', [(64, 256, 256), (1000, 512, 384), (5000, 2560, 1024), (777, 264, 136), (4096, 128, 4096)])
+def test_linear_tn(r, m, n):
+    """at.T @ wt with the contraction over the rows of both operands (MN-major tensor-core tiles) against fp32,
+    and against the same product through explicit transposes."""
+    at, wt = rnd(r, m, seed=80), rnd(r, n, seed=81, std=0.05)
+    ad, wd = at.to(DEV), wt.to(DEV)
+    got = ops.linear_tn(ad, wd)
+    want = at.float().t() @ wt.float()
+    assert_close(got, want, atol=2e-2 * (r ** 0.5) * 0.05 + 2e-2, rtol=1e-2)
+    via = ops.linear(ops.transpose(ad), ops.transpose(wd))
+    assert_close(got, via.float(), atol=2e-3 * float(want.abs().max()), rtol=8e-3)
+    # strided views of wider tensors
+    wide_a, wide_w = torch.cat([ad, ad], 1), torch.cat([wd, wd], 1)
+    assert torch.equal(ops.linear_tn(wide_a[:, m:], wide_w[:, :n]), got)
+    # a shape the entry point does not take falls back to transposes
+    odd = ops.linear_tn(ad[:, :m - 4], wd)
+    assert_close(odd, want[:m - 4], atol=2e-2 * (r ** 0.5) * 0.05 + 2e-2, rtol=1e-2)
