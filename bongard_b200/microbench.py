@@ -157,6 +157,13 @@ def linear(args, flush):
 
             ms = timed(two_kernels, args.iters, args.warmup, flush)
             out.append(dict(op='gemm_bf16_qkv_then_norm_rope', tokens=t, ms=ms, tflops=2 * t * n * k / ms / 1e9))
+        # the weight gradient dW = dy^T x: operands read in place (MN-major tiles) against transposed copies first
+        dy = randn(t, n, seed=16)
+        ms = timed(lambda: ops.linear_tn(dy, x), args.iters, args.warmup, flush)
+        out.append(dict(op=f'gemm_bf16_tn_{name}_weight_gradient', tokens=t, ms=ms, tflops=2 * t * n * k / ms / 1e9))
+        ms = timed(lambda: ops.linear(ops.transpose(dy), ops.transpose(x)), args.iters, args.warmup, flush)
+        out.append(dict(op=f'gemm_bf16_{name}_weight_gradient_via_transposes', tokens=t, ms=ms,
+                        tflops=2 * t * n * k / ms / 1e9))
     return out
 
 
