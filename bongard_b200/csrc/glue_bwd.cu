@@ -115,6 +115,13 @@ __global__ void column_sum_kernel(const float* __restrict__ partial, int64_t par
     else if (out1 != nullptr) out1[c - split] = acc;
 }
 
+// E consecutive bf16 values as 32-bit words (kept in registers: unpacked with shifts, packed with cvt).
+template <int E>
+struct alignas(2 * E) Raw {
+    uint32_t w[E / 2];
+};
+constexpr int HB = 4;     // heads whose loads are issued together
+
 // Backward of QK-norm + RoPE (forward: bongard/attention.py:172-180, fused form bongard/qk_norm_rope.metal:4-33).
 // Forward per head: a = x * r * (1 + w);  y[i] = a[i] cos[i] + sign(i) a[partner(i)] sin[i], sign = -1 for
 // i < D/2, partner(i) = (i + D/2) mod D.  Backward:
@@ -122,13 +129,6 @@ __global__ void column_sum_kernel(const float* __restrict__ partial, int64_t par
 // One warp walks tokens warp_id, warp_id + n_warps, ...; lane l owns elements [l*D/32, (l+1)*D/32) and its
 // partner lives in lane l ^ 16.  x is the input the forward normalised (the forward itself runs in place, so
 // the caller keeps a copy).  Gain gradients: one partial row of 2*D floats (query gain | key gain) per warp.
-// E consecutive bf16 values as 32-bit words (kept in registers: unpacked with shifts, packed with cvt)
-template <int E>
-struct alignas(2 * E) Raw {
-    uint32_t w[E / 2];
-};
-constexpr int HB = 4;
-
 template <int D>
 __global__ void __launch_bounds__(256, 2) qk_norm_rope_backward_kernel(const __nv_bfloat16* __restrict__ xq, int64_t ldxq,
                                              const __nv_bfloat16* __restrict__ dyq, int64_t lddyq,
