@@ -35,7 +35,7 @@ SIGNATURES = {
     'bg_rope_table': ([P, I64, INT, P, P], INT),
     'bg_gemm_bf16_qkv_rope': ([P, I64, P, I64, P, I64, I64, I64, INT, INT, INT, P, P, P, P, I64, F32, P], INT),
     'bg_gemm_bf16_skinny_supported': ([I64, I64, I64, INT], INT),
-    'bg_gemm_bf16_tn': ([P, I64, P, I64, P, I64, I64, I64, I64, P], INT),
+    'bg_gemm_bf16_tn': ([P, I64, P, I64, P, I64, I64, I64, I64, INT, P, I64, P], INT),
     'bg_gemm_bf16_splitk_choice': ([I64, I64, I64], INT),
     'bg_gemm_bf16_splitk_workspace_bytes': ([I64, I64, INT], I64),
     'bg_gemm_bf16_splitk': ([P, I64, P, I64, P, I64, I64, I64, I64, INT, P, I64, P], INT),

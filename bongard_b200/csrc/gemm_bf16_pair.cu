@@ -528,14 +528,15 @@ static int splitk_choice(int64_t m, int64_t n, int64_t k) {
     if (m <= 0 || n <= 0 || k < 4096 || n % 8) return 1;
     const int64_t tiles = ((m + 2 * BM - 1) / (2 * BM)) * ((n + BN - 1) / BN);
     const int pairs = resident_pairs();
-    if (tiles >= pairs) return 1;
-    // time ~ waves of the persistent grid x the length of one item: ceil(tiles * s / pairs) / s, plus the
-    // partial-sum traffic; a split has to save at least 15 % to be taken
+    if (tiles > 3 * pairs) return 1;
+    // time ~ waves of the persistent grid x the length of one item: ceil(tiles * s / pairs) / s against
+    // ceil(tiles / pairs) unsplit, plus the partial-sum traffic; a split has to save at least 15 % to be taken
     const int64_t kblocks = (k + BK - 1) / BK;
+    const double unsplit = double((tiles + pairs - 1) / pairs);
     int best = 1;
     double best_cost = 1.0;
     for (int split = 2; split <= 4 && kblocks >= 16 * split; ++split) {
-        const double cost = double((tiles * split + pairs - 1) / pairs) / split + 0.03 * (split - 1);
+        const double cost = double((tiles * split + pairs - 1) / pairs) / split / unsplit + 0.03 * (split - 1);
         if (cost < best_cost - 1e-9 && cost <= 0.85) {
             best = split;
             best_cost = cost;
@@ -597,15 +598,23 @@ extern "C" int bg_gemm_bf16_splitk(const void* a, int64_t lda, const void* w, in
 // out[m, n] = sum_k at[k, m] * wt[k, n]: both operands with the contraction as the row index.  This is the
 // weight gradient dW = dy^T x taken straight from dy [tokens, out features] and x [tokens, in features].
 extern "C" int bg_gemm_bf16_tn(const void* at, int64_t ldat, const void* wt, int64_t ldwt, void* out, int64_t ldo,
-                               int64_t m, int64_t n, int64_t k, void* stream) {
-    if (m <= 0 || n <= 0 || k <= 0) {
+                               int64_t m, int64_t n, int64_t k, int split, void* workspace, int64_t workspace_bytes,
+                               void* stream) {
+    if (m <= 0 || n <= 0 || k <= 0 || split > 8) {
         bg_set_error("bg_gemm_bf16_tn: bad shape");
         return BG_ERR_SHAPE;
     }
+    if (split < 2) split = 1;
     if ((m % 8) || (n % 8) || (ldat % 8) || (ldwt % 8) || (ldo % 8) || ldat < m || ldwt < n || ldo < n ||
-        ((reinterpret_cast<uintptr_t>(at) | reinterpret_cast<uintptr_t>(wt) | reinterpret_cast<uintptr_t>(out)) & 15)) {
+        ((reinterpret_cast<uintptr_t>(at) | reinterpret_cast<uintptr_t>(wt) | reinterpret_cast<uintptr_t>(out)) & 15) ||
+        (split > 1 && (reinterpret_cast<uintptr_t>(workspace) & 15))) {
         bg_set_error("bg_gemm_bf16_tn: pointers must be 16-byte aligned, m, n and the leading dimensions multiples of 8");
         return BG_ERR_ALIGN;
+    }
+    if (split > 1 && ((k + BK - 1) / BK < 4 * split || workspace == nullptr ||
+                      workspace_bytes < bg_gemm_bf16_splitk_workspace_bytes(m, n, split))) {
+        bg_set_error("bg_gemm_bf16_tn: K slices need at least 4 K-blocks each and a workspace of split * m * n * 4 bytes");
+        return BG_ERR_WORKSPACE;
     }
     CUtensorMap map_a, map_w;
     uint64_t dims_a[2] = {(uint64_t)m, (uint64_t)k}, str_a[1] = {(uint64_t)ldat * 2};
@@ -618,5 +627,18 @@ extern "C" int bg_gemm_bf16_tn(const void* at, int64_t ldat, const void* wt, int
     if (rc) return rc;
     PairParams p = {};
     p.mn_major = 1;
-    return pair_launch(p, map_a, map_w, out, ldo, m, n, k, 0, static_cast<cudaStream_t>(stream));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (split == 1) return pair_launch(p, map_a, map_w, out, ldo, m, n, k, 0, s);
+    p.split_k = split;
+    p.partial = static_cast<float*>(workspace);
+    rc = pair_launch(p, map_a, map_w, out, ldo, m, n, k, 3, s);
+    if (rc) return rc;
+    const int64_t groups = m * n / 8;
+    cudaError_t e = launch_kernel(sum_partials_kernel, dim3((unsigned)((groups + 255) / 256)), dim3(256), 0, s, 0,
+                                  static_cast<const float*>(workspace), split, m, n, static_cast<__nv_bfloat16*>(out), ldo);
+    if (e != cudaSuccess) {
+        bg_set_error("bg_gemm_bf16_tn: launch(sum): %s", cudaGetErrorString(e));
+        return BG_ERR_LAUNCH;
+    }
+    return BG_OK;
 }

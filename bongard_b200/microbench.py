@@ -335,10 +335,13 @@ def train(args, flush):
         out.backward(flat_dy)
 
     ms_ours = timed(step_ours, args.iters, args.warmup, flush)
+    ops.SPLIT_K = False          # the same step without K slices in the small weight-gradient GEMMs
+    ms_unsplit = timed(step_ours, args.iters, args.warmup, flush)
+    ops.SPLIT_K = True
     return dict(op='encoder_layers_forward_backward', layers=shape.layers, layer_types=list(shape.layer_types),
                 sequences=n, length=length, substituted=counts, model_tflop=flops / 1e12,
                 native_ms=ms_native, native_tflops=flops / ms_native / 1e9,
-                substituted_ms=ms_ours, substituted_tflops=flops / ms_ours / 1e9)
+                substituted_ms=ms_ours, substituted_tflops=flops / ms_ours / 1e9, substituted_without_k_slices_ms=ms_unsplit)
 
 
 def main():

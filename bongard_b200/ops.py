@@ -305,8 +305,11 @@ def linear_tn(at, wt):
     out = torch.empty((m, n), device=at.device, dtype=BF16)
     timer = GEMM_TIMER
     begin = timer.start() if timer is not None else None
-    _lib.check(lib.bg_gemm_bf16_tn(_ptr(at), at.stride(0), _ptr(wt), wt.stride(0), _ptr(out), n, m, n, r, _stream()),
-               'bg_gemm_bf16_tn')
+    split = lib.bg_gemm_bf16_splitk_choice(m, n, r) if SPLIT_K else 1
+    need = lib.bg_gemm_bf16_splitk_workspace_bytes(m, n, split)
+    work = torch.empty((need,), device=at.device, dtype=torch.uint8) if need else None
+    _lib.check(lib.bg_gemm_bf16_tn(_ptr(at), at.stride(0), _ptr(wt), wt.stride(0), _ptr(out), n, m, n, r, split,
+                                   _ptr(work), need, _stream()), 'bg_gemm_bf16_tn')
     if timer is not None:
         timer.stop(begin, 2 * m * n * r)
     return out

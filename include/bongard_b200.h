@@ -145,9 +145,12 @@ int bg_transpose_bf16(const void* src, int64_t lds, void* dst, int64_t ldd, int6
 /* out[m, n] = sum_k at[k, m] * wt[k, n] (bf16 in and out, fp32 accumulate): both operands carry the contraction
  * as their ROW index, so the weight gradient dW = dy^T x is taken straight from dy [tokens, out features] and
  * x [tokens, in features] - the tensor core reads MN-major tiles, nothing is transposed.  m, n and the
- * leading dimensions must be multiples of 8 and the pointers 16-byte aligned. */
+ * leading dimensions must be multiples of 8 and the pointers 16-byte aligned.  split >= 2 cuts the contraction
+ * into that many slices (bg_gemm_bf16_splitk_choice(m, n, k) says when that pays: a weight gradient has few output
+ * tiles and a long contraction) and needs a workspace of bg_gemm_bf16_splitk_workspace_bytes(m, n, split);
+ * split <= 1 ignores the workspace. */
 int bg_gemm_bf16_tn(const void* at, int64_t ldat, const void* wt, int64_t ldwt, void* out, int64_t ldo, int64_t m,
-                    int64_t n, int64_t k, void* stream);
+                    int64_t n, int64_t k, int split, void* workspace, int64_t workspace_bytes, void* stream);
 int bg_geglu_backward(const void* gu, const void* dh, void* dgu, int64_t rows, int64_t inter, void* stream);
 
 /* Backward of the norms the reference trains through with autograd (transformers T5Gemma2RMSNorm,

@@ -352,7 +352,7 @@ def test_linear_split_k(m, n, k):
     args = (xd.data_ptr(), k, wd.data_ptr(), k, got.data_ptr(), n, m, n, k)
     assert lib.bg_gemm_bf16_splitk(*args, split, work.data_ptr(), work.numel() - 16, None) == -5      # workspace
     assert lib.bg_gemm_bf16_splitk(*args, 1, work.data_ptr(), work.numel(), None) == -1               # split < 2
-    assert lib.bg_gemm_bf16_splitk_choice(8192, 2560, 10240) == 1 and lib.bg_gemm_bf16_splitk_choice(640, 2560, 2048) == 1
+    assert lib.bg_gemm_bf16_splitk_choice(32768, 2560, 10240) == 1 and lib.bg_gemm_bf16_splitk_choice(640, 2560, 2048) == 1
 
 
 @pytest.mark.parametrize('r,m,n', [(64, 256, 256), (1000, 512, 384), (5000, 2560, 1024), (777, 264, 136), (4096, 128, 4096)])
