@@ -26,6 +26,7 @@ SIGNATURES = {
     'bg_gemm_bf16': ([P, I64, P, I64, P, I64, I64, I64, I64, INT, P], INT),
     'bg_transpose_bf16': ([P, I64, P, I64, I64, I64, P], INT),
     'bg_geglu_backward': ([P, P, P, I64, I64, P], INT),
+    'bg_geglu_forward': ([P, P, I64, I64, P], INT),
     'bg_rmsnorm_backward_workspace_bytes': ([I64, I64], I64),
     'bg_rmsnorm_backward': ([P, I64, P, P, I64, P, I64, P, P, I64, I64, I64, F32, P], INT),
     'bg_qk_norm_rope_backward_workspace_bytes': ([I64, INT], I64),

@@ -104,6 +104,22 @@ __global__ void rmsnorm_backward_kernel(const __nv_bfloat16* __restrict__ x, int
     }
 }
 
+// h = gelu_tanh(g) * u for gu = [g | u] ([rows, 2 inter] bf16): the activation as its own pass, for the training
+// forward that keeps gu for the backward instead of recomputing it (transformers modeling_t5gemma2.py:87-91
+// computes it from the bf16 projections the same way).
+__global__ void geglu_forward_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ h, int64_t rows,
+                                     int64_t inter) {
+    const int64_t i = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
+    if (i >= rows * inter) return;
+    const int64_t row = i / inter, col = i % inter;
+    float g[8], u[8], o[8];
+    unpack8(*reinterpret_cast<const uint4*>(gu + row * 2 * inter + col), g);
+    unpack8(*reinterpret_cast<const uint4*>(gu + row * 2 * inter + inter + col), u);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = gelu_tanh(g[e]) * u[e];
+    *reinterpret_cast<uint4*>(h + i) = pack8(o);
+}
+
 // Sum of the partial rows in row order: columns below `split` go to out0, the others to out1.
 __global__ void column_sum_kernel(const float* __restrict__ partial, int64_t parts, int64_t cols, int64_t split,
                                   float* __restrict__ out0, float* __restrict__ out1) {
@@ -273,6 +289,18 @@ int64_t qk_blocks(int64_t tokens, int head_dim) {
 }  // namespace
 
 extern "C" {
+
+int bg_geglu_forward(const void* gu, void* h, int64_t rows, int64_t inter, void* stream) {
+    if (rows < 0 || inter <= 0 || inter % 8) {
+        bg_set_error("bg_geglu_forward: the intermediate size must be a multiple of 8");
+        return BG_ERR_SHAPE;
+    }
+    if (rows == 0) return BG_OK;
+    const int64_t groups = rows * inter / 8;
+    geglu_forward_kernel<<<(unsigned)((groups + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(h), rows, inter);
+    return check_launch("bg_geglu_forward");
+}
 
 int64_t bg_rmsnorm_backward_workspace_bytes(int64_t rows, int64_t h) {
     return rows <= 0 ? 0 : norm_blocks(rows, h) * h * int64_t(sizeof(float));

@@ -338,10 +338,14 @@ def train(args, flush):
     ops.SPLIT_K = False          # the same step without K slices in the small weight-gradient GEMMs
     ms_unsplit = timed(step_ours, args.iters, args.warmup, flush)
     ops.SPLIT_K = True
+    ops.GEGLU_KEEP_PREACTIVATIONS = False   # fused GEMM + GeGLU forward, pre-activations recomputed in the backward
+    ms_recompute = timed(step_ours, args.iters, args.warmup, flush)
+    ops.GEGLU_KEEP_PREACTIVATIONS = True
     return dict(op='encoder_layers_forward_backward', layers=shape.layers, layer_types=list(shape.layer_types),
                 sequences=n, length=length, substituted=counts, model_tflop=flops / 1e12,
                 native_ms=ms_native, native_tflops=flops / ms_native / 1e9,
-                substituted_ms=ms_ours, substituted_tflops=flops / ms_ours / 1e9, substituted_without_k_slices_ms=ms_unsplit)
+                substituted_ms=ms_ours, substituted_tflops=flops / ms_ours / 1e9, substituted_without_k_slices_ms=ms_unsplit,
+                substituted_recomputing_geglu_ms=ms_recompute)
 
 
 def main():

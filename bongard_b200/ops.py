@@ -328,22 +328,42 @@ class _Linear(torch.autograd.Function):
         return dx, dw
 
 
+GEGLU_KEEP_PREACTIVATIONS = True
+
+
 class _LinearGeglu(torch.autograd.Function):
-    """h = gelu_tanh(x Wg^T) * (x Wu^T).  The pre-activations are recomputed in the backward (one more
-    GEMM) instead of being kept: they are four times the size of x."""
+    """h = gelu_tanh(x Wg^T) * (x Wu^T).  With GEGLU_KEEP_PREACTIVATIONS (default) the forward writes the bf16
+    pre-activations [g | u] with the plain GEMM, forms h in a second pass and keeps [g | u] for the backward,
+    as the native module does; without it the fused GEMM + GeGLU epilogue runs and the backward recomputes
+    [g | u] with one more GEMM (they are four times the size of x)."""
 
     @staticmethod
     def forward(ctx, x, gate_up):
-        ctx.save_for_backward(x, gate_up)
-        return linear_geglu(x, gate_up)
-
-    @staticmethod
-    def backward(ctx, dh):
-        x, gate_up = ctx.saved_tensors
+        if not GEGLU_KEEP_PREACTIVATIONS:
+            ctx.save_for_backward(x, gate_up)
+            ctx.kept = False
+            return linear_geglu(x, gate_up)
         lib = _lib.load()
         flat, m, k, _ = _rows(x, 'x')
         inter = gate_up.shape[0] // 2
         gu = linear(flat, gate_up)
+        h = torch.empty((m, inter), device=x.device, dtype=BF16)
+        _lib.check(lib.bg_geglu_forward(_ptr(gu), _ptr(h), m, inter, _stream()), 'bg_geglu_forward')
+        ctx.save_for_backward(x, gate_up, gu)
+        ctx.kept = True
+        return h.view(*x.shape[:-1], inter)
+
+    @staticmethod
+    def backward(ctx, dh):
+        lib = _lib.load()
+        if ctx.kept:
+            x, gate_up, gu = ctx.saved_tensors
+            flat, m, k, _ = _rows(x, 'x')
+        else:
+            x, gate_up = ctx.saved_tensors
+            flat, m, k, _ = _rows(x, 'x')
+            gu = linear(flat, gate_up)
+        inter = gate_up.shape[0] // 2
         dh2 = dh.reshape(m, inter).contiguous()
         dgu = torch.empty_like(gu)
         _lib.check(lib.bg_geglu_backward(_ptr(gu), _ptr(dh2), _ptr(dgu), m, inter, _stream()), 'bg_geglu_backward')

@@ -152,6 +152,10 @@ int bg_transpose_bf16(const void* src, int64_t lds, void* dst, int64_t ldd, int6
 int bg_gemm_bf16_tn(const void* at, int64_t ldat, const void* wt, int64_t ldwt, void* out, int64_t ldo, int64_t m,
                     int64_t n, int64_t k, int split, void* workspace, int64_t workspace_bytes, void* stream);
 int bg_geglu_backward(const void* gu, const void* dh, void* dgu, int64_t rows, int64_t inter, void* stream);
+/* h[rows, inter] = gelu_tanh(g) * u for gu = [g | u] [rows, 2 inter]: the activation as its own pass, for a
+ * training forward that keeps gu for bg_geglu_backward instead of recomputing it (HF T5Gemma2MLP.forward,
+ * modeling_t5gemma2.py:87-91, forms it from the bf16 projections the same way). */
+int bg_geglu_forward(const void* gu, void* h, int64_t rows, int64_t inter, void* stream);
 
 /* Backward of the norms the reference trains through with autograd (transformers T5Gemma2RMSNorm,
  * modeling_t5gemma2.py:55-69; QK-norm + RoPE: bongard/attention.py:172-180).  fp32 math, bf16 in and out,

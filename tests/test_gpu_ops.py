@@ -245,11 +245,17 @@ def test_linear_backward(m, n, k):
     assert torch.equal(t[:, :m].cpu(), x.t()) and float(t[:, m:].abs().max() if t.shape[1] > m else 0) == 0
 
 
+@pytest.mark.parametrize('keep', [True, False])
 @pytest.mark.parametrize('m,i,k', [(7, 256, 128), (300, 1024, 256)])
-def test_linear_geglu_backward(m, i, k):
+def test_linear_geglu_backward(m, i, k, keep, monkeypatch):
+    """Both training forms: pre-activations kept by the forward (plain GEMM + activation pass), or recomputed
+    by the backward after the fused GEMM + GeGLU forward."""
+    monkeypatch.setattr(ops, 'GEGLU_KEEP_PREACTIVATIONS', keep)
     x, gu, dh = rnd(m, k, seed=53), rnd(2 * i, k, seed=54, std=0.05), rnd(m, i, seed=55)
     xd, gd = x.to(DEV).requires_grad_(True), gu.to(DEV).requires_grad_(True)
-    ops.linear_geglu_autograd(xd, gd).backward(dh.to(DEV))
+    out = ops.linear_geglu_autograd(xd, gd)
+    assert_close(out, ops.linear_geglu(x.to(DEV), gu.to(DEV)).float(), atol=2e-2, rtol=2e-2)
+    out.backward(dh.to(DEV))
     xf, gf = x.float().requires_grad_(True), gu.float().requires_grad_(True)
     pre = xf @ gf.t()
     (torch.nn.functional.gelu(pre[:, :i], approximate='tanh') * pre[:, i:]).backward(dh.float())
