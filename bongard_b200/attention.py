@@ -102,19 +102,14 @@ def _fused_qkv_trainable(module, x, positions, position_embeddings):
     d = module.head_dim
     qkv = ops.linear_autograd(x, _trainable_weight(module, ('q_proj', 'k_proj', 'v_proj')))
     qd, kd = module.q_proj.weight.shape[0], module.k_proj.weight.shape[0]
-    t = x.shape[0]
-    q = qkv[:, :qd].view(t, qd // d, d)
-    k = qkv[:, qd:qd + kd].view(t, kd // d, d)
-    v = qkv[:, qd + kd:].view(t, kd // d, d)
     if positions is not None:
-        q, k = ops.qk_norm_rope_autograd(q, k, module.q_norm.weight, module.k_norm.weight, positions,
-                                         ops.inv_freq(d, _theta(module), x.device), module.q_norm.eps)
-    else:
-        cos, sin = position_embeddings
-        q, k = ops.qk_norm_rope_table_autograd(q, k, module.q_norm.weight, module.k_norm.weight,
-                                               cos.reshape(-1, d).to(torch.bfloat16), sin.reshape(-1, d).to(torch.bfloat16),
-                                               module.q_norm.eps)
-    return q, k, v.contiguous()     # q and k are fresh contiguous tensors now: v has to share k's strides
+        return ops.qkv_norm_rope_autograd(qkv, qd // d, kd // d, d, module.q_norm.weight, module.k_norm.weight,
+                                          positions=positions, freqs=ops.inv_freq(d, _theta(module), x.device),
+                                          eps=module.q_norm.eps)
+    cos, sin = position_embeddings
+    return ops.qkv_norm_rope_autograd(qkv, qd // d, kd // d, d, module.q_norm.weight, module.k_norm.weight,
+                                      cos=cos.reshape(-1, d).to(torch.bfloat16), sin=sin.reshape(-1, d).to(torch.bfloat16),
+                                      eps=module.q_norm.eps)
 
 
 def project_out(module, attended, hidden_shape):

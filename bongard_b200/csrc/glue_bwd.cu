@@ -120,15 +120,25 @@ __global__ void geglu_forward_kernel(const __nv_bfloat16* __restrict__ gu, __nv_
     *reinterpret_cast<uint4*>(h + i) = pack8(o);
 }
 
-// Sum of the partial rows in row order: columns below `split` go to out0, the others to out1.
+// Sum of the partial rows, columns below `split` to out0 and the others to out1.  A block owns 32 columns: its
+// eight warps each add every eighth row (128-byte coalesced reads), then the eight sums are added in warp order,
+// so the result does not depend on scheduling.
 __global__ void column_sum_kernel(const float* __restrict__ partial, int64_t parts, int64_t cols, int64_t split,
                                   float* __restrict__ out0, float* __restrict__ out1) {
-    const int64_t c = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (c >= cols) return;
+    __shared__ float sums[8][33];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t c = int64_t(blockIdx.x) * 32 + lane;
     float acc = 0.f;
-    for (int64_t p = 0; p < parts; ++p) acc += partial[p * cols + c];
-    if (c < split) out0[c] = acc;
-    else if (out1 != nullptr) out1[c - split] = acc;
+    if (c < cols)
+        for (int64_t p = warp; p < parts; p += 8) acc += partial[p * cols + c];
+    sums[warp][lane] = acc;
+    __syncthreads();
+    if (warp != 0 || c >= cols) return;
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) total += sums[w][lane];
+    if (c < split) out0[c] = total;
+    else if (out1 != nullptr) out1[c - split] = total;
 }
 
 // E consecutive bf16 values as 32-bit words (kept in registers: unpacked with shifts, packed with cvt).
@@ -328,7 +338,7 @@ int bg_rmsnorm_backward(const void* x, int64_t ldx, const void* w, const void* d
         static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(w),
         static_cast<const __nv_bfloat16*>(dy), lddy, static_cast<__nv_bfloat16*>(dx), lddx,
         static_cast<float*>(workspace), rows, int(h), eps);
-    column_sum_kernel<<<(unsigned)((h + 255) / 256), 256, 0, s>>>(static_cast<const float*>(workspace), blocks, h, h, dw,
+    column_sum_kernel<<<(unsigned)((h + 31) / 32), 256, 0, s>>>(static_cast<const float*>(workspace), blocks, h, h, dw,
                                                                   nullptr);
     return check_launch("bg_rmsnorm_backward");
 }
@@ -382,7 +392,7 @@ int bg_qk_norm_rope_backward(const void* xq, int64_t ldxq, const void* dyq, int6
     else if (head_dim == 128) launch(qk_norm_rope_backward_kernel<128>);
     else launch(qk_norm_rope_backward_kernel<256>);
     // the partial rows are [query gain | key gain]
-    column_sum_kernel<<<(unsigned)((2 * head_dim + 255) / 256), 256, 0, s>>>(
+    column_sum_kernel<<<(unsigned)((2 * head_dim + 31) / 32), 256, 0, s>>>(
         static_cast<const float*>(workspace), blocks * QK_WARPS, 2 * head_dim, head_dim, dq_weight, dk_weight);
     return check_launch("bg_qk_norm_rope_backward");
 }

@@ -408,10 +408,11 @@ def rmsnorm_autograd(x, weight, eps=1e-6):
 
 
 def qk_norm_rope_backward(xq, xk, q_weight, k_weight, dyq, dyk, *, positions=None, freqs=None, cos=None, sin=None,
-                          eps=1e-6, rotate=True):
+                          eps=1e-6, rotate=True, out_q=None, out_k=None):
     """Backward of qk_norm_rope_ / qk_norm_rope_table_: xq [T,Hq,D] and xk [T,Hkv,D] (or None) are the inputs
     the forward normalised, dyq / dyk the gradients of its outputs.  Returns (dxq, dxk, dq_weight, dk_weight)
-    with fp32 gain gradients; the k entries are None when xk is None."""
+    with fp32 gain gradients; the k entries are None when xk is None.  out_q / out_k ([T, heads, D] views with
+    contiguous heads, e.g. slices of one gradient buffer of the stacked projection) receive dxq / dxk in place."""
     lib = _lib.load()
     tokens, hq, d = xq.shape
 
@@ -422,14 +423,14 @@ def qk_norm_rope_backward(xq, xk, q_weight, k_weight, dyq, dyk, *, positions=Non
         return t
 
     xq, dyq = token_major(xq, 'xq'), token_major(dyq.to(BF16), 'dyq')
-    dxq = torch.empty((tokens, hq, d), device=xq.device, dtype=BF16)
+    dxq = out_q if out_q is not None else torch.empty((tokens, hq, d), device=xq.device, dtype=BF16)
     dqw = torch.empty((d,), device=xq.device, dtype=torch.float32)
     hk = 0
     dxk = dkw = None
     if xk is not None:
         hk = xk.shape[1]
         xk, dyk = token_major(xk, 'xk'), token_major(dyk.to(BF16), 'dyk')
-        dxk = torch.empty((tokens, hk, d), device=xq.device, dtype=BF16)
+        dxk = out_k if out_k is not None else torch.empty((tokens, hk, d), device=xq.device, dtype=BF16)
         dkw = torch.empty((d,), device=xq.device, dtype=torch.float32)
     if rotate and cos is None:
         _need(positions, 'positions', torch.int32), _need(freqs, 'inv_freq', torch.float32)
@@ -474,6 +475,50 @@ class _QkNormRope(torch.autograd.Function):
         dxq, dxk, dqw, dkw = qk_norm_rope_backward(q, k, qw, kw, dq, dk, positions=positions, freqs=freqs, cos=cos,
                                                    sin=sin, eps=ctx.eps)
         return dxq, dxk, dqw.to(ctx.dtypes[0]), dkw.to(ctx.dtypes[1]), None, None, None, None, None
+
+
+class _QkvNormRope(torch.autograd.Function):
+    """The stacked projection output qkv [T, (Hq + 2 Hkv) D] -> (q', k', v) with QK-norm + RoPE on q and k.  One
+    function instead of three slices plus _QkNormRope so that the backward writes the three gradients into ONE
+    buffer shaped like qkv (the kernel takes row strides), not into zero-filled copies that autograd then adds."""
+
+    @staticmethod
+    def forward(ctx, qkv, q_heads, kv_heads, d, q_weight, k_weight, cos, sin, positions, freqs, eps):
+        qw, kw = q_weight.detach().to(BF16), k_weight.detach().to(BF16)
+        t, qd, kd = qkv.shape[0], q_heads * d, kv_heads * d
+        ctx.save_for_backward(qkv, qw, kw)
+        ctx.angles = (cos, sin, positions, freqs)
+        ctx.meta = (q_heads, kv_heads, d, eps, q_weight.dtype, k_weight.dtype)
+        q = qkv[:, :qd].reshape(t, q_heads, d).contiguous()
+        k = qkv[:, qd:qd + kd].reshape(t, kv_heads, d).contiguous()
+        v = qkv[:, qd + kd:].reshape(t, kv_heads, d).contiguous()
+        if cos is not None:
+            qk_norm_rope_table_(q, k, qw, kw, cos, sin, eps)
+        else:
+            qk_norm_rope_(q, k, qw, kw, positions, freqs, eps)
+        return q, k, v
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        qkv, qw, kw = ctx.saved_tensors
+        cos, sin, positions, freqs = ctx.angles
+        q_heads, kv_heads, d, eps, q_dtype, k_dtype = ctx.meta
+        t, qd, kd = qkv.shape[0], q_heads * d, kv_heads * d
+        dqkv = torch.empty_like(qkv)
+        _, _, dqw, dkw = qk_norm_rope_backward(
+            qkv[:, :qd].view(t, q_heads, d), qkv[:, qd:qd + kd].view(t, kv_heads, d), qw, kw, dq, dk,
+            positions=positions, freqs=freqs, cos=cos, sin=sin, eps=eps,
+            out_q=dqkv[:, :qd].view(t, q_heads, d), out_k=dqkv[:, qd:qd + kd].view(t, kv_heads, d))
+        dqkv[:, qd + kd:].copy_(dv.reshape(t, kd))
+        return dqkv, None, None, None, dqw.to(q_dtype), dkw.to(k_dtype), None, None, None, None, None
+
+
+def qkv_norm_rope_autograd(qkv, q_heads, kv_heads, head_dim, q_weight, k_weight, *, cos=None, sin=None, positions=None,
+                           freqs=None, eps=1e-6):
+    """(q', k', v) [T, heads, D] from the stacked projection output, recording one backward for all three."""
+    if cos is not None:
+        cos, sin = cos.contiguous(), sin.contiguous()
+    return _QkvNormRope.apply(qkv, q_heads, kv_heads, head_dim, q_weight, k_weight, cos, sin, positions, freqs, eps)
 
 
 def qk_norm_rope_table_autograd(q, k, q_weight, k_weight, cos, sin, eps=1e-6):
