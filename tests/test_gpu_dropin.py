@@ -458,3 +458,58 @@ def test_state_projection_trains(tiny):
         got = got.float().cpu().reshape(ref.shape)
         err, scale = float((got - ref).abs().max()), float(ref.abs().max())
         assert err < 4e-2 * scale + 2e-3, (what, err, scale)
+
+
+def test_substituted_decoder_trains_like_the_native_one(tiny):
+    """Whole decoder, train mode: questions packed over two shared states, the state K/V projected per layer by
+    the substituted module, against the native decoder run one question at a time on its own state: gradients of
+    every decoder parameter and of the encoder states."""
+    weights, _ = tiny
+    shape = wl.TINY
+    state_lengths, lengths, owners = [90, 150], [40, 25, 33], [0, 0, 1]
+    gen = torch.Generator().manual_seed(41)
+    states = [torch.randn(n, shape.hidden, generator=gen).bfloat16() for n in state_lengths]
+    ids = [torch.randint(2, shape.vocab, (n,), generator=gen) for n in lengths]
+    dys = [torch.randn(n, shape.hidden, generator=gen).bfloat16().to(DEV) for n in lengths]
+
+    native = build_backbone(shape, weights).train()
+    native_states = [s.to(DEV).requires_grad_(True) for s in states]
+    for tokens, dy, owner in zip(ids, dys, owners):
+        out = native.decoder(input_ids=tokens.to(DEV)[None], encoder_hidden_states=native_states[owner][None],
+                             use_cache=False).last_hidden_state
+        (out[0].float() * dy.float()).sum().backward()
+    want = {n: p.grad.float().cpu() for n, p in native.decoder.named_parameters() if p.grad is not None}
+
+    ours = build_backbone(shape, weights).train()
+    install_b200_inference(ours)
+    decoder = ours.decoder
+    our_states = [s.to(DEV).requires_grad_(True) for s in states]
+    layout = packing.packed_layout(lengths, [], DEV, owners=owners, state_lengths=state_lengths)
+    hidden = decoder.embed_tokens(torch.cat(ids).to(DEV)[None])
+    embeddings = {t: decoder.rotary_emb(hidden, layout.positions, t) for t in set(decoder.config.layer_types)}
+    empty = torch.empty(0, device=DEV)
+    for index, layer in enumerate(decoder.layers):
+        parts = [layer.self_attn._cross(None, s[None], None) for s in our_states]
+        cross = (torch.cat([k[0].transpose(0, 1) for k, _ in parts]), torch.cat([v[0].transpose(0, 1) for _, v in parts]))
+        hidden = layer(hidden, embeddings[decoder.config.layer_types[index]], empty, layout.positions, None, False,
+                       None, question_layout=layout, packed_cross=cross)
+    out = decoder.norm(hidden)[0]
+    (out.float() * torch.cat(dys).float()).sum().backward()
+    got = {n: p.grad.float().cpu() for n, p in decoder.named_parameters() if p.grad is not None}
+    for name in [n for n in got if n.endswith('mlp.gate_up.weight')]:
+        layer = name[:-len('gate_up.weight')]
+        got[layer + 'gate_proj.weight'], got[layer + 'up_proj.weight'] = got[name].split(shape.intermediate)
+        got[layer + 'down_proj.weight'] = got[layer + 'down.weight']
+
+    checked = 0
+    for name, ref in want.items():
+        if float(ref.abs().max()) == 0:
+            continue
+        assert name in got, (name, sorted(got))
+        err, scale = float((got[name] - ref).abs().max()), float(ref.abs().max())
+        assert err < 6e-2 * scale + 1e-3, (name, err, scale)
+        checked += 1
+    assert checked >= 2 * 11
+    for mine, theirs in zip(our_states, native_states):
+        err, scale = float((mine.grad.float() - theirs.grad.float()).abs().max()), float(theirs.grad.float().abs().max())
+        assert err < 6e-2 * scale + 1e-3, ('state', err, scale)
