@@ -18,6 +18,7 @@ SIGNATURES = {
     'bg_last_error_string': ([], c_char_p),
     'bg_device_check': ([], INT),
     'bg_read_status': ([P], INT),
+    'bg_selftest_bounded_wait': ([I64, P, P], INT),
     'bg_rmsnorm': ([P, I64, P, P, I64, I64, I64, F32, P], INT),
     'bg_add_rmsnorm': ([P, P, P, P, P, I64, I64, F32, P], INT),
     'bg_qk_norm_rope': ([P, I64, INT, P, I64, INT, P, P, P, P, I64, INT, F32, INT, P], INT),

@@ -15,7 +15,7 @@ import torch
 from torch import nn
 
 from . import ops
-from .packing import PackedLayout, packed_layout
+from .packing import PackedLayout, is_packed_layout, packed_layout  # noqa: F401
 
 _COPIED = ('config', 'layer_idx', 'layer_type', 'head_dim', 'num_key_value_groups', 'scaling',
            'attention_dropout', 'is_causal', 'attn_logit_softcapping', 'sliding_window', 'is_sliding')
@@ -255,7 +255,7 @@ class B200DecoderAttention(nn.Module):
                 past_key_values=None, *, question_layout=None, packed_cross=None, **kwargs):
         from .packing import decoder_attention
 
-        if isinstance(question_layout, PackedLayout):
+        if is_packed_layout(question_layout):      # this module's layout or the reference's own
             return decoder_attention(self, hidden_states, position_embeddings, past_key_values, question_layout,
                                      packed_cross)
         cross = self._cross(past_key_values, encoder_hidden_states, packed_cross)

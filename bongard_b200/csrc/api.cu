@@ -67,28 +67,60 @@ int bg_make_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, int rank, co
     return BG_OK;
 }
 
+int bg_device_slot() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kBgMaxDevices) return 0;
+    return dev;
+}
+
+// Every cache below is a table indexed by the current device: a process that drives several GPUs
+// gets each device's own SM count, status word and kernel attributes.
 int bg_num_sms() {
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (sms <= 0) sms = 148;
+    static int sms[kBgMaxDevices] = {};
+    const int dev = bg_device_slot();
+    if (!sms[dev]) {
+        int n = 0;
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        sms[dev] = n > 0 ? n : 148;
     }
-    return sms;
+    return sms[dev];
 }
 
 int32_t* bg_status_word() {
-    static int32_t* ptr = nullptr;
-    if (!ptr) {
+    static int32_t* ptr[kBgMaxDevices] = {};
+    const int dev = bg_device_slot();
+    if (!ptr[dev]) {
         void* p = nullptr;
-        if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) {
+        if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) {     // the symbol's address on the CURRENT device
             bg_set_error("cudaGetSymbolAddress(status word) failed");
             return nullptr;
         }
-        ptr = static_cast<int32_t*>(p);
+        ptr[dev] = static_cast<int32_t*>(p);
     }
-    return ptr;
+    return ptr[dev];
+}
+
+// Self-test of the bounded wait: one CTA waits on a barrier phase that nothing completes, with the
+// caller's budget instead of the kernels' 4 s.  When the budget runs out the wait reports site 901
+// to the status word and returns false, as it does inside the GEMM and attention kernels; every
+// thread then takes the normal way out.  Nothing traps, faults or spins past the budget.
+__global__ void bounded_wait_selftest_kernel(int32_t* status, uint64_t budget_ns, int32_t* finished) {
+    using namespace bg;
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    Abort ab{&abort_flag, status};
+    bool ok = true;
+    if (threadIdx.x == 0) ok = mbar_wait(&bar, 0, ab, 901, budget_ns);     // nobody arrives: runs out
+    __syncthreads();
+    // the other threads see the CTA-wide abort flag, as the kernels' later waits do
+    if (threadIdx.x == 1 && finished) *finished = ab.raised() ? 1 : 0;
+    (void)ok;
 }
 
 static int g_programmatic_launch = 0;
@@ -145,6 +177,25 @@ int bg_read_status(void* stream) {
         bg_set_error("a bounded device wait ran out (site %d)", host);
     }
     return host;
+}
+
+// Launches the bounded-wait self-test (see bounded_wait_selftest_kernel) with a budget of
+// `budget_us` microseconds (1 .. 100000).  `finished` (device int32, may be NULL) is set to 1 by
+// the kernel after the wait gave up.  bg_read_status(stream) afterwards returns 901.
+int bg_selftest_bounded_wait(int64_t budget_us, int32_t* finished, void* stream) {
+    if (budget_us < 1 || budget_us > 100000) {
+        bg_set_error("bg_selftest_bounded_wait: budget must be 1..100000 microseconds");
+        return BG_ERR_SHAPE;
+    }
+    int32_t* word = bg_status_word();
+    if (!word) return BG_ERR_DRIVER;
+    bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(word, (uint64_t)budget_us * 1000ull, finished);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        bg_set_error("bg_selftest_bounded_wait: %s", cudaGetErrorString(e));
+        return BG_ERR_LAUNCH;
+    }
+    return BG_OK;
 }
 
 }  // extern "C"

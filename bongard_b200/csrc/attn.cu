@@ -337,7 +337,8 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 template <int D>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mck,
            const CUtensorMap& mcv, const AttnParams& p, int n_tiles, cudaStream_t stream) {
-    static bool configured = false;
+    static bool configured_on[kBgMaxDevices] = {};
+    bool& configured = configured_on[bg_device_slot()];
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(varlen_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              Smem<D>::TOTAL);

@@ -522,7 +522,8 @@ int row_map(CUtensorMap* map, const void* base, int64_t tokens, int heads, int d
 
 template <int D, int PASS>
 int launch_pass(const CUtensorMap* m, const BwdParams& p, int n_tiles, cudaStream_t stream) {
-    static bool configured = false;
+    static bool configured_on[kBgMaxDevices] = {};
+    bool& configured = configured_on[bg_device_slot()];
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_bwd_kernel<D, PASS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              Layout<D, PASS>::TOTAL);

@@ -28,6 +28,9 @@ int bg_make_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, int rank, co
                        const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
                        CUtensorMapSwizzle swizzle);
 int bg_num_sms();
+// Index of the current device in the per-device tables (0 when it cannot be read or exceeds the table).
+constexpr int kBgMaxDevices = 64;
+int bg_device_slot();
 int bg_programmatic_launch();  // 1 when kernels are launched with programmatic stream serialization
 int32_t* bg_status_word();  // device pointer, zero unless a bounded wait ran out
 
@@ -99,7 +102,8 @@ struct Abort {
 };
 
 // Bounded wait on an mbarrier phase.  Returns false when the CTA has aborted.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const Abort& ab, int where) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const Abort& ab, int where,
+                                          uint64_t budget_ns = kWaitBudgetNs) {
     if (mbar_try_wait(bar, parity)) return true;
     uint64_t start = 0;
     uint32_t spins = 0;
@@ -109,7 +113,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
         if ((++spins & 0x3ff) == 0) {
             uint64_t now = global_timer_ns();
             if (start == 0) start = now;
-            else if (now - start > kWaitBudgetNs) {
+            else if (now - start > budget_ns) {
                 ab.raise(where);
                 return false;
             }

@@ -285,7 +285,8 @@ extern "C" int bg_gemm_bf16(const void* a, int64_t lda, const void* w, int64_t l
     p.status = bg_status_word();
     if (!p.status) return BG_ERR_DRIVER;
 
-    static bool configured = false;
+    static bool configured_on[kBgMaxDevices] = {};
+    bool& configured = configured_on[bg_device_slot()];
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) {

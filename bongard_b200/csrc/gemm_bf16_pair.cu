@@ -493,7 +493,8 @@ static int pair_launch(PairParams p, const CUtensorMap& map_a, const CUtensorMap
     }
     p.status = bg_status_word();
     if (!p.status) return BG_ERR_DRIVER;
-    static bool configured = false;
+    static bool configured_on[kBgMaxDevices] = {};
+    bool& configured = configured_on[bg_device_slot()];
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_bf16_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e == cudaSuccess)

@@ -348,7 +348,8 @@ extern "C" int bg_gemm_bf16_skinny(const void* a, int64_t lda, const void* w, in
         tiles = (int)(n / 128);
     }
 
-    static bool configured = false;
+    static bool configured_on[kBgMaxDevices] = {};
+    bool& configured = configured_on[bg_device_slot()];
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_bf16_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              SMEM_BYTES);

@@ -395,7 +395,8 @@ int bg_gemm_fp8_block128(const void* aq, int64_t lda, const float* a_inv_t, cons
     p.tiles_n = epilogue == 1 ? (int)(n / 128) : (int)((n + BN - 1) / BN);
     p.status = bg_status_word();
     if (!p.status) return BG_ERR_DRIVER;
-    static bool configured = false;
+    static bool configured_on[kBgMaxDevices] = {};
+    bool& configured = configured_on[bg_device_slot()];
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) {
@@ -457,7 +458,7 @@ int bg_linear_fp8(const void* x, int64_t ldx, const void* wq, int64_t ldw, const
 // two calls whose kernels overlap on the GPU - different streams, no ordering between them -
 // would overwrite each other's quantised activations: order them on one stream or with events.
 constexpr int64_t kStaticScratchBytes = 9ll << 20;     // 8 Mi activation elements + their block scales
-constexpr int kMaxDevices = 64;
+constexpr int kMaxDevices = kBgMaxDevices;
 static __device__ __align__(256) uint8_t g_fp8_static_scratch[kStaticScratchBytes];
 
 int64_t bg_linear_fp8_static_max_bytes(void) { return kStaticScratchBytes; }

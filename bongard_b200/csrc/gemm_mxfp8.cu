@@ -447,7 +447,8 @@ static int gemm_mxfp8_launch(const void* aq, int64_t lda, const void* a_scales, 
     p.tiles_n = epilogue == 1 ? (int)(n / 128) : (int)((n + BN - 1) / BN);
     p.status = bg_status_word();
     if (!p.status) return BG_ERR_DRIVER;
-    static bool configured = false;
+    static bool configured_on[kBgMaxDevices] = {};
+    bool& configured = configured_on[bg_device_slot()];
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_mxfp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) {

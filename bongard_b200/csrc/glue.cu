@@ -603,7 +603,8 @@ int bg_judgment_head(const void* hidden, int64_t ldh, const int32_t* cand_rows, 
     }
     if (candidates == 0) return BG_OK;
     const size_t smem = 2 * h * sizeof(float);
-    static bool configured = false;
+    static bool configured_on[kBgMaxDevices] = {};
+    bool& configured = configured_on[bg_device_slot()];
     if (!configured && smem > 48 * 1024) {
         cudaFuncSetAttribute(judgment_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
         configured = true;

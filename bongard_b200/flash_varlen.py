@@ -22,15 +22,51 @@ import torch
 from . import ops
 
 
-def _plan_from_cu(cu_q, window, group, device, *, decoder=False, cu_k=None, head_dim=None, backward=False):
+def _prefix_bank(lengths, key_lengths, indices, cu_k, state_rows):
+    """Owners and state bank of a prefix call from the reference's arguments.
+
+    The reference hands its op the whole state bank (`ck`, `cv`: one state per owner) and a gather
+    `indices` over cat(bank, own keys) that lists, for every question, its owner's state rows and
+    then its own rows (bongard/packing.py:86-101, bongard/flash_varlen.py:61-63).  The kernel needs
+    no gather, only where each question's state starts: the first index of its key run.  Questions
+    whose states start at the same row share an owner (and therefore one key stream).  An empty
+    `indices` means one private state per question, back to back in question order."""
+    state_lengths = [k - n for k, n in zip(key_lengths, lengths)]
+    if any(s < 0 for s in state_lengths):
+        raise ValueError('cu_seqlens_k must give every question at least its own keys')
+    if indices is None or indices.numel() == 0:
+        return list(range(len(lengths))), state_lengths, None
+    if indices.numel() != sum(key_lengths):
+        raise ValueError(f'indices has {indices.numel()} entries, cu_seqlens_k describes {sum(key_lengths)} keys')
+    starts = indices.index_select(0, cu_k[:-1].to(torch.int64).clamp(max=indices.numel() - 1)).tolist()
+    bank, owners = {}, []
+    for start, state, own in zip(starts, state_lengths, lengths):
+        key = (start, state) if state else (0, 0)
+        if state and not 0 <= start <= state_rows - state:
+            raise ValueError(f'indices address state rows {start}..{start + state}, the state bank holds {state_rows}')
+        owners.append(bank.setdefault(key, len(bank)))
+    offsets, sizes = [k[0] for k in bank], [k[1] for k in bank]
+    # the gather must be exactly [owner's state run | own run] per question
+    own_offsets = torch.tensor([state_rows + sum(lengths[:i]) for i in range(len(lengths))], device=indices.device)
+    expect = []
+    for i, (start, state, own) in enumerate(zip(starts, state_lengths, lengths)):
+        expect.append(torch.arange(start, start + state, device=indices.device))
+        expect.append(torch.arange(own, device=indices.device) + own_offsets[i])
+    if not torch.equal(torch.cat(expect), indices.to(torch.int64)):
+        raise ValueError('indices must list, per question, a contiguous run of state rows followed by its own rows')
+    return owners, sizes, offsets
+
+
+def _plan_from_cu(cu_q, window, group, device, *, decoder=False, cu_k=None, head_dim=None, backward=False,
+                  indices=None, state_rows=0):
     """Attention plan from cu_seqlens tensors (synchronises: the custom-op surface carries no host lengths)."""
     lengths = (cu_q[1:] - cu_q[:-1]).tolist()
     if not decoder:
         return ops.make_plan(lengths, window, device, group=group, head_dim=head_dim, backward=backward)
     key_lengths = (cu_k[1:] - cu_k[:-1]).tolist()
-    state_lengths = [k - n for k, n in zip(key_lengths, lengths)]
-    return ops.make_plan(lengths, window, device, group=group, owners=list(range(len(lengths))),
-                         state_lengths=state_lengths, head_dim=head_dim, backward=backward)
+    owners, state_lengths, state_offsets = _prefix_bank(lengths, key_lengths, indices, cu_k, state_rows)
+    return ops.make_plan(lengths, window, device, group=group, owners=owners, state_lengths=state_lengths,
+                         state_offsets=state_offsets, head_dim=head_dim, backward=backward)
 
 
 def flash_packed_forward(q, k, v, cuq, cuk, scale, causal):
@@ -45,11 +81,12 @@ def flash_packed_forward(q, k, v, cuq, cuk, scale, causal):
 
 def flash_prefix_forward(q, k, v, ck, cv, indices, cuq, cuk, scale):
     """Decoder form, op `bongard::flash_prefix_forward` (bongard/flash_varlen.py:66-77): keys of
-    question i are [state_i | own_i] with bottom-right causal alignment.  `indices` (the gather
-    the reference needs) is accepted and ignored; state segments are taken in question order,
-    i.e. ck/cv hold one state per question back to back, or the caller uses `attention` below
-    with a layout that knows the owners."""
-    plan = _plan_from_cu(cuq, None, q.shape[1] // k.shape[1], q.device, decoder=True, cu_k=cuk, head_dim=q.shape[-1])
+    question i are [state of its owner | own_i] with bottom-right causal alignment.  `ck`, `cv` are
+    the state bank and `indices` the reference's gather over cat(bank, own keys); the owners and
+    state offsets are read from it and the kernel streams each state in place (nothing is
+    gathered).  An empty `indices` means one state per question, back to back."""
+    plan = _plan_from_cu(cuq, None, q.shape[1] // k.shape[1], q.device, decoder=True, cu_k=cuk, head_dim=q.shape[-1],
+                         indices=indices, state_rows=ck.shape[0])
     out, lse = ops.varlen_attention(q, k, v, plan, scale, (ck, cv), return_lse=True)
     return out.view(q.shape), lse
 
@@ -67,7 +104,7 @@ def flash_prefix_backward(q, k, v, ck, cv, indices, cuq, cuk, out, lse, dout, sc
     the state gradients are written by the key-tile passes directly, so there is no gathered
     gradient to scatter back with index_add_."""
     plan = _plan_from_cu(cuq, None, q.shape[1] // k.shape[1], q.device, decoder=True, cu_k=cuk, head_dim=q.shape[-1],
-                         backward=True)
+                         backward=True, indices=indices, state_rows=ck.shape[0])
     return ops.varlen_attention_backward(q, k, v, plan, scale, out, lse, dout, (ck, cv))
 
 

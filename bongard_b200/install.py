@@ -44,5 +44,10 @@ def install_b200_inference(model, *, linears='bf16'):
                     setattr(parent, name, B200RMSNorm(child))
                     counts['norms'] += 1
     if hasattr(model, 'packing_attention'):
+        # the reference's forward_packed asks packed_layout for this backend (bongard/packing.py:247-252,
+        # 284-289); the name it calls is bound to a dispatcher that serves it, no source is edited
+        from .packing import serve_reference_packing
+
         model.packing_attention = 'b200'
+        serve_reference_packing()
     return counts

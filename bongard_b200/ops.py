@@ -560,6 +560,8 @@ class AttentionPlan:
     tile_rows: int = 128     # query rows (tokens x GQA group) a tile may hold
     kv_tiles: torch.Tensor = None    # int32 [n_kv_tiles, 8], key tiles of the backward passes (optional)
     n_kv_tiles: int = 0
+    own_extent: int = 0      # one past the last own-key row any tile addresses (host copy, for bounds checks)
+    state_extent: int = 0    # one past the last state row any tile addresses
 
 
 def plan_rows(lengths, window, *, decoder):
@@ -596,6 +598,8 @@ class HostPlan:
     pairs: int
     tile_rows: int = 128
     n_kv_tiles: int = 0      # key tiles for the backward passes, appended after row_hi
+    own_extent: int = 0      # one past the last own-key row / state row the tiles address
+    state_extent: int = 0
 
     def to(self, device):
         dev = torch.from_numpy(self.packed).to(device, non_blocking=True)
@@ -612,12 +616,12 @@ class HostPlan:
         out[:n8] = self.packed[:n8]
         out[n_tiles * 8:n_tiles * 8 + t] = self.packed[n8:n8 + t]
         out[n_tiles * 8 + tokens:n_tiles * 8 + tokens + t] = self.packed[n8 + t:n8 + 2 * t]
-        return HostPlan(out, tokens, n_tiles, self.pairs, self.tile_rows)
+        return HostPlan(out, tokens, n_tiles, self.pairs, self.tile_rows, 0, self.own_extent, self.state_extent)
 
     def view(self, dev):
         n8, t = self.n_tiles * 8, self.tokens
         plan = AttentionPlan(dev[:n8].view(-1, 8), dev[n8:n8 + t], dev[n8 + t:n8 + 2 * t], t, self.n_tiles, self.pairs,
-                             self.tile_rows)
+                             self.tile_rows, own_extent=self.own_extent, state_extent=self.state_extent)
         if self.n_kv_tiles:
             plan.kv_tiles = dev[n8 + 2 * t:n8 + 2 * t + self.n_kv_tiles * 8].view(-1, 8)
             plan.n_kv_tiles = self.n_kv_tiles
@@ -629,7 +633,23 @@ def tile_rows(head_dim):
     return _lib.load().bg_attention_tile_rows(int(head_dim)) if head_dim else 128
 
 
-def make_host_kv_tiles(lengths, window, *, owners=None, state_lengths=None, keys_per_tile=128):
+def _state_bank(owners, state_lengths, state_offsets):
+    """Validated (offsets, lengths) of the state bank: `state_lengths[o]` rows starting at
+    `state_offsets[o]` (default: the states lie back to back) for every owner o."""
+    state_lengths = [int(n) for n in state_lengths]
+    if any(n < 0 for n in state_lengths):
+        raise ValueError('state lengths must not be negative')
+    if state_offsets is None:
+        state_offsets = np.concatenate(([0], np.cumsum(np.asarray(state_lengths, dtype=np.int64))))[:-1]
+    state_offsets = [int(o) for o in state_offsets]
+    if len(state_offsets) != len(state_lengths) or any(o < 0 for o in state_offsets):
+        raise ValueError('state offsets must be one non-negative row per state')
+    if any(not 0 <= int(o) < len(state_lengths) for o in owners):
+        raise ValueError('an owner names a state that is not in the bank')
+    return state_offsets, state_lengths
+
+
+def make_host_kv_tiles(lengths, window, *, owners=None, state_lengths=None, state_offsets=None, keys_per_tile=128):
     """Key tiles for the backward passes (host arithmetic on lengths only): int32 [n, 8] rows
     {k_start, k_count, q_lo, q_hi, is_state, 0, 0, 0}.
 
@@ -652,7 +672,7 @@ def make_host_kv_tiles(lengths, window, *, owners=None, state_lengths=None, keys
                 tiles.append((k0, count, q_lo, max(q_lo, q_hi), 0))
         offset += n
     if decoder:
-        state_offsets = np.concatenate(([0], np.cumsum(np.asarray(state_lengths, dtype=np.int64))))
+        state_offsets, state_lengths = _state_bank(owners, state_lengths, state_offsets)
         runs, offset = [], 0
         for n, owner in zip(lengths, owners):
             if n:
@@ -676,14 +696,21 @@ def make_host_kv_tiles(lengths, window, *, owners=None, state_lengths=None, keys
     return out[np.argsort(-(out[:, 3] - out[:, 2]), kind='stable')]
 
 
-def make_host_plan(lengths, window, *, group, owners=None, state_lengths=None, head_dim=None, backward=False):
+def make_host_plan(lengths, window, *, group, owners=None, state_lengths=None, head_dim=None, backward=False,
+                   state_offsets=None):
     """Tile a pack of segments for the attention kernel (host arithmetic on lengths only).
 
     Encoder (owners None): tiles never cross a segment.  Decoder: consecutive questions of the
     same owner form one run; a tile is up to 128/group consecutive tokens of a run, so
-    questions that share a state also share its key stream.  Tiles are ordered heaviest first."""
+    questions that share a state also share its key stream.  `state_offsets[o]` is the first row
+    of owner o's state in the bank (default: states back to back in owner order).  Tiles are
+    ordered heaviest first."""
     lengths = [int(n) for n in lengths]
+    if any(n < 0 for n in lengths):
+        raise ValueError('segment lengths must not be negative')
     decoder = owners is not None
+    if decoder and (state_lengths is None or len(owners) != len(lengths)):
+        raise ValueError('decoder plans need state_lengths and one owner per segment')
     lo, hi = plan_rows(lengths, window, decoder=decoder)
     total = len(lo)
     rows = tile_rows(head_dim)
@@ -691,7 +718,7 @@ def make_host_plan(lengths, window, *, group, owners=None, state_lengths=None, h
     runs = []      # [start, end, prefix_start, prefix_len, owner]
     offset = 0
     if decoder:
-        state_offsets = np.concatenate(([0], np.cumsum(np.asarray(state_lengths, dtype=np.int64))))
+        state_offsets, state_lengths = _state_bank(owners, state_lengths, state_offsets)
         for n, owner in zip(lengths, owners):
             if runs and runs[-1][4] == owner:
                 runs[-1][1] = offset + n
@@ -721,18 +748,31 @@ def make_host_plan(lengths, window, *, group, owners=None, state_lengths=None, h
     parts = [tiles.reshape(-1), lo.astype(np.int32), hi.astype(np.int32)]
     n_kv = 0
     if backward:
-        kv = make_host_kv_tiles(lengths, window, owners=owners, state_lengths=state_lengths)
+        kv = make_host_kv_tiles(lengths, window, owners=owners, state_lengths=state_lengths, state_offsets=state_offsets)
         parts.append(kv.reshape(-1))
         n_kv = kv.shape[0]
     pairs = int((hi - lo).sum())
     if decoder:
         pairs += int(sum(n * state_lengths[o] for n, o in zip(lengths, owners)))
-    return HostPlan(np.concatenate(parts), total, tiles.shape[0], pairs, rows, n_kv)
+    state_extent = int((run[:, 2] + run[:, 3])[run[:, 3] > 0].max(initial=0))
+    return HostPlan(np.concatenate(parts), total, tiles.shape[0], pairs, rows, n_kv, total, state_extent)
 
 
-def make_plan(lengths, window, device, *, group, owners=None, state_lengths=None, head_dim=None, backward=False):
+def make_plan(lengths, window, device, *, group, owners=None, state_lengths=None, head_dim=None, backward=False,
+              state_offsets=None):
     return make_host_plan(lengths, window, group=group, owners=owners, state_lengths=state_lengths,
-                          head_dim=head_dim, backward=backward).to(device)
+                          head_dim=head_dim, backward=backward, state_offsets=state_offsets).to(device)
+
+
+def check_plan_bounds(plan, key_rows, state_rows):
+    """Host check that every key row a plan addresses exists: raises ValueError before any launch
+    (the forward would read zero-filled rows, the backward would store state gradients past the
+    end of their buffers)."""
+    if plan.own_extent > key_rows:
+        raise ValueError(f'the attention plan addresses own-key rows up to {plan.own_extent}, k/v hold {key_rows}')
+    if plan.state_extent > state_rows:
+        raise ValueError(f'the attention plan addresses state rows up to {plan.state_extent}, '
+                         f'the state keys/values hold {state_rows}')
 
 
 def varlen_attention(q, k, v, plan, scale, cross=None, return_lse=False):
@@ -759,6 +799,7 @@ def varlen_attention(q, k, v, plan, scale, cross=None, return_lse=False):
         if ck.shape != cv.shape or ck.stride() != cv.stride() or ck.shape[1:] != k.shape[1:] or ck.stride(2) != 1:
             raise ValueError('cross keys/values must be [S, kv_heads, D] with equal strides')
         ts, ldc, hsc = ck.shape[0], ck.stride(0), ck.stride(1)
+    check_plan_bounds(plan, tk, ts)
     out = torch.empty((tq, hq * d), device=q.device, dtype=BF16)
     lse = torch.empty((hq, tq), device=q.device, dtype=torch.float32) if return_lse else None
     timer = ATTN_TIMER
@@ -801,6 +842,8 @@ def varlen_attention_backward(q, k, v, plan, scale, out, lse, dout, cross=None):
         if ck.shape != cv.shape or ck.stride() != cv.stride() or ck.shape[1:] != k.shape[1:] or ck.stride(2) != 1:
             raise ValueError('cross keys/values must be [S, kv_heads, D] with equal strides')
         ts, ldc, hsc = ck.shape[0], ck.stride(0), ck.stride(1)
+    check_plan_bounds(plan, tk, ts)
+    if cross is not None:
         dck = torch.zeros((ts, hkv, d), device=q.device, dtype=BF16)    # states without a question keep zero
         dcv = torch.zeros((ts, hkv, d), device=q.device, dtype=BF16)
     dq = torch.empty((tq, hq, d), device=q.device, dtype=BF16)

@@ -37,6 +37,7 @@ class PackedLayout:
     state_lengths: tuple | None = None
     positions32: torch.Tensor | None = None      # int32 [T]
     plans: dict = field(default_factory=dict)    # (window, group) -> ops.AttentionPlan
+    state_offsets: tuple | None = None           # first bank row of every state (None: back to back)
 
     @property
     def decoder(self):
@@ -56,7 +57,7 @@ class PackedLayout:
         if key not in self.plans:
             self.plans[key] = ops.make_plan(self.lengths, key[0], self.positions.device, group=group,
                                             owners=self.owners, state_lengths=self.state_lengths, head_dim=head_dim,
-                                            backward=backward)
+                                            backward=backward, state_offsets=self.state_offsets)
         return self.plans[key]
 
 
@@ -84,13 +85,99 @@ def packed_layout(lengths, windows, device, *, owners=None, state_lengths=None, 
                         positions.to(torch.int32))
 
 
+def is_packed_layout(layout):
+    """True for this module's PackedLayout and for one built by the reference's own
+    `packed_layout` (bongard/packing.py:42-51): both carry `positions` [1, T] and `cu_seqlens`,
+    which a padded-batch QuestionLayout (`valid`, bongard/attention.py:183-202) does not."""
+    return layout is not None and hasattr(layout, 'cu_seqlens') and hasattr(layout, 'positions') \
+        and not hasattr(layout, 'valid')
+
+
+def adopt_layout(layout):
+    """A PackedLayout of this module for `layout`, which may be one the reference's own
+    `packed_layout` built (bongard/packing.py:54-151).  The conversion reads the segment lengths
+    from `cu_seqlens` (backend 'flash' on CUDA, packing.py:80-81) or, failing that, from the
+    positions, which restart at zero at every segment (packing.py:59); a decoder layout names
+    its owners through `key_seqlens` / `key_indices` (packing.py:86-101: every question's key run
+    starts with its owner's state rows).  The result is cached on the foreign object, so the
+    device round trip happens once per pack, not once per layer."""
+    if isinstance(layout, PackedLayout):
+        return layout
+    cached = layout.__dict__.get('_b200_layout') if hasattr(layout, '__dict__') else None
+    if cached is not None:
+        return cached
+    positions = layout.positions.reshape(-1)
+    cu = getattr(layout, 'cu_seqlens', None)
+    if cu is not None:
+        bounds = cu.tolist()
+    else:
+        bounds = (positions == 0).nonzero().reshape(-1).tolist() + [positions.numel()]
+    lengths = [b - a for a, b in zip(bounds, bounds[1:])]
+    owners = state_lengths = state_offsets = None
+    key_cu = getattr(layout, 'key_seqlens', None)
+    if key_cu is not None:
+        from .flash_varlen import _prefix_bank
+
+        key_bounds = key_cu.tolist()
+        key_lengths = [b - a for a, b in zip(key_bounds, key_bounds[1:])]
+        indices = getattr(layout, 'key_indices', None)
+        state_rows = int(indices.numel() and indices.max()) + 1 - sum(lengths) if indices is not None else 0
+        owners, state_lengths, state_offsets = _prefix_bank(lengths, key_lengths, indices, key_cu, max(state_rows, 0))
+    elif getattr(layout, 'masks', None) and any(m is not None and getattr(m, 'ndim', 4) == 4 and
+                                               m.shape[-1] != m.shape[-2] for m in layout.masks.values()):
+        raise ValueError("a decoder layout without key_seqlens does not say which state a question reads; build it "
+                         "with backend='b200' (install_b200_inference sets model.packing_attention) or 'flash'")
+    ours = PackedLayout(layout.positions, {}, 'b200', cu if cu is None else cu.to(torch.int32), key_cu, None,
+                        frozenset(getattr(layout, 'flash_windows', ())), {}, tuple(lengths),
+                        None if owners is None else tuple(owners),
+                        None if state_lengths is None else tuple(state_lengths),
+                        positions.to(torch.int32), {},
+                        None if state_offsets is None else tuple(state_offsets))
+    if hasattr(layout, '__dict__'):
+        layout.__dict__['_b200_layout'] = ours
+    return ours
+
+
+def serve_reference_packing(module=None):
+    """Make the reference's own `forward_packed` (bongard/packing.py:228-318) build B200 layouts.
+
+    `forward_packed` calls `packed_layout(..., backend=model.packing_attention)` through its
+    module's global name, so binding that name to a dispatcher is all it takes: backend 'b200'
+    goes to this module's `packed_layout`, every other backend to the reference's own function.
+    No reference source is edited.  `module` defaults to `bongard.packing` when the reference is
+    importable; returns True when the name was (or already is) bound."""
+    if module is None:
+        import importlib
+        import sys
+
+        module = sys.modules.get('bongard.packing')
+        if module is None:
+            try:
+                module = importlib.import_module('bongard.packing')
+            except ImportError:
+                return False
+    native = module.packed_layout
+    if getattr(native, 'b200_dispatch', False):
+        return True
+
+    def dispatch(lengths, windows, device, *, owners=None, state_lengths=None, backend='triton'):
+        if backend == 'b200':
+            return packed_layout(lengths, windows, device, owners=owners, state_lengths=state_lengths, backend=backend)
+        return native(lengths, windows, device, owners=owners, state_lengths=state_lengths, backend=backend)
+
+    dispatch.b200_dispatch, dispatch.native = True, native
+    dispatch.__doc__ = native.__doc__
+    module.packed_layout = dispatch
+    return True
+
+
 def layout_attention(q, k, v, layout, scale, window, cross=None, dropout=0.0):
     """bongard/packing.py:178-198.  q [1,Hq,T,D]; k, v [1,Hkv,T,D]; cross = (ck, cv) [1,Hkv,S,D]."""
     from .flash_varlen import attention
 
     if dropout:
         raise ValueError('Packed CUDA attention requires zero attention dropout')
-    return attention(q, k, v, layout, scale, window, cross)
+    return attention(q, k, v, adopt_layout(layout), scale, window, cross)
 
 
 def _project(module, hidden_states, layout_positions, position_embeddings):
@@ -104,6 +191,7 @@ def encoder_attention(module, hidden_states, position_embeddings, layout):
     """bongard/packing.py:201-210: projections, QK-norm + RoPE, packed attention, o_proj."""
     from .attention import needs_grad, project_out
 
+    layout = adopt_layout(layout)
     q, k, v = _project(module, hidden_states, layout.positions32, position_embeddings)
     group = q.shape[1] // k.shape[1]
     if needs_grad(module, hidden_states):
@@ -118,6 +206,7 @@ def decoder_attention(module, hidden_states, position_embeddings, cache, layout,
     """bongard/packing.py:213-225: as above with the owner's state K/V as key prefix."""
     from .attention import as_token_major, needs_grad, project_out
 
+    layout = adopt_layout(layout)
     q, k, v = _project(module, hidden_states, layout.positions32, position_embeddings)
     if packed_cross is None:
         cross = cache.cross_attention_cache.layers[module.layer_idx]

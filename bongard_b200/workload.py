@@ -193,6 +193,33 @@ def make_weights_device(shape: ModelShape, seed: int, device, *, std=0.02, dtype
     return out
 
 
+def make_weights_host(shape: ModelShape, seed: int, *, std=0.02, dtype=torch.bfloat16, threads=None):
+    """Random-init weights on the host, generated by a pool of threads (timing runs of a CPU arm
+    at the full model size, where one sequential generator would take minutes).  Every chunk of
+    rows draws from its own seeded generator, so the result depends on the seed only."""
+    import os
+    from concurrent.futures import ThreadPoolExecutor
+
+    out, jobs = {}, []
+    for index, (name, dims) in enumerate(weight_names(shape)):
+        if len(dims) < 2:
+            out[name] = torch.zeros(dims, dtype=dtype)
+            continue
+        out[name] = torch.empty(dims, dtype=dtype)
+        rows = max(1, (1 << 24) // dims[1])
+        jobs += [(name, index, r0, min(r0 + rows, dims[0])) for r0 in range(0, dims[0], rows)]
+
+    def fill(job):
+        name, index, r0, r1 = job
+        gen = torch.Generator().manual_seed((seed * 1_000_003 + index) * 4096 + r0 // max(1, r1 - r0))
+        block = torch.randn((r1 - r0, out[name].shape[1]), generator=gen)
+        out[name][r0:r1].copy_(block.mul_(std))
+
+    with ThreadPoolExecutor(threads or os.cpu_count() or 1) as pool:
+        list(pool.map(fill, jobs))
+    return out
+
+
 # --------------------------------------------------------------------------------------
 # requests
 # --------------------------------------------------------------------------------------

@@ -44,6 +44,14 @@ int bg_device_check(void);
  * bounded wait that ran out (1xx BF16 GEMM, 2xx attention, 3xx FP8 GEMM). */
 int bg_read_status(void* stream);
 
+/* Self-test of the bounded device waits (no counterpart in the reference, which has no device
+ * waits of its own).  Launches one CTA that waits, with a budget of `budget_us` microseconds
+ * (1..100000), on a barrier that nothing completes; when the budget runs out the wait reports
+ * site 901 exactly as the waits inside the GEMM and attention kernels report theirs, the kernel
+ * sets *finished = 1 (device int32, may be NULL) and returns normally.  bg_read_status() then
+ * returns 901 and the library keeps working.  Nothing traps or faults. */
+int bg_selftest_bounded_wait(int64_t budget_us, int32_t* finished, void* stream);
+
 /* Programmatic dependent launch for the latency path: with enable = 1 the kernels of the serving chain
  * (bg_gemm_bf16, bg_gemm_bf16_skinny, bg_varlen_attention, the norm / RoPE / embedding / head kernels) are
  * launched with programmatic stream serialization: a kernel may start while its predecessor in the stream is
@@ -243,7 +251,7 @@ int bg_gemm_mxfp8_geglu_q(const void* aq, int64_t lda, const void* a_scales, con
 /* bg_linear_fp8 for callers that cannot supply scratch memory.  (No counterpart in the reference.)
  * The quantised activations go to a fixed buffer inside the library instead of a caller-owned
  * workspace, so the call allocates nothing; in exchange the activation is limited to
- * bg_linear_fp8_static_max_bytes() of scratch (9 MiB: about 8 Mi elements, e.g. 3 276 rows of 2 560),
+ * bg_linear_fp8_static_max_bytes() of scratch (9 MiB: e.g. 3 574 rows of 2 560, at 2 560 bytes of E4M3 plus 80 bytes of block scales a row),
  * larger ones are refused with BG_ERR_WORKSPACE.  Every GPU that loads the library holds the buffer
  * until exit.  The first call on each device looks up the buffer's device address: make it before
  * any stream capture.  All calls on a device share the buffer, so calls that may overlap on the GPU

@@ -161,7 +161,7 @@ def test_attention_surface_is_differentiable():
         out.backward(dout.to(DEV))
         for leaf, want in zip(leaves, oracle(win=None)):
             close(leaf.grad, want)
-        # one state per question, back to back, as the reference's op takes them
+        # an empty gather: one private state per question, back to back
         states = [50, 64, 20]
         ck, cv = (torch.randn(sum(states), hkv, d, generator=g).bfloat16() for _ in range(2))
         cuk = torch.tensor([0, 140, 241, 461], dtype=torch.int32, device=DEV)
@@ -170,6 +170,62 @@ def test_attention_surface_is_differentiable():
         out.backward(dout.to(DEV))
         for leaf, want in zip(leaves, oracle((ck, cv), [0, 1, 2], states, win=None)):
             close(leaf.grad, want)
+
+
+def reference_gather(lengths, owners, state_lengths):
+    """key_seqlens and key_indices as the reference's packed_layout builds them
+    (bongard/packing.py:86-101): per question its owner's state rows, then its own rows, as
+    indices into cat(state bank, own keys)."""
+    from itertools import accumulate
+
+    state_offsets = list(accumulate(state_lengths, initial=0))
+    query_offsets = list(accumulate(lengths, initial=0))
+    total = sum(state_lengths)
+    indices = []
+    for i, owner in enumerate(owners):
+        indices.extend(range(state_offsets[owner], state_offsets[owner + 1]))
+        indices.extend(range(total + query_offsets[i], total + query_offsets[i + 1]))
+    key_cu = list(accumulate((state_lengths[o] + n for o, n in zip(owners, lengths)), initial=0))
+    return (torch.tensor(key_cu, dtype=torch.int32, device=DEV), torch.tensor(indices, device=DEV),
+            torch.tensor(query_offsets, dtype=torch.int32, device=DEV))
+
+
+def test_prefix_ops_take_the_state_bank_and_the_gather():
+    """The prefix ops with the reference's own arguments (bongard/flash_varlen.py:129-139): ck/cv
+    are the state BANK - one state per owner, shared by its questions - and `indices` is the
+    gather over cat(bank, own keys).  Eight questions on one state plus two on another, forward
+    and backward against the oracle; state rows nobody reads keep a zero gradient."""
+    hq, hkv, d = 4, 2, 64
+    lengths = [17, 40, 9, 33, 25, 64, 12, 30, 21, 50]
+    owners = [0] * 8 + [2] * 2
+    state_lengths = [150, 70, 90]             # state 1 belongs to nobody in this group
+    t, ts = sum(lengths), sum(state_lengths)
+    g = torch.Generator().manual_seed(8)
+    q, k, v, dout = (torch.randn(t, h, d, generator=g).bfloat16() for h in (hq, hkv, hkv, hq))
+    ck, cv = (torch.randn(ts, hkv, d, generator=g).bfloat16() for _ in range(2))
+    cuk, indices, cuq = reference_gather(lengths, owners, state_lengths)
+    leaves = [x.float().requires_grad_(True) for x in (q, k, v, ck, cv)]
+    want, want_lse = om.varlen_attention(*leaves[:3], lengths, 0.125, None, cross=(leaves[3], leaves[4]), owners=owners,
+                                         state_lengths=state_lengths)
+    want.backward(dout.float())
+    dev = [x.to(DEV) for x in (q, k, v, ck, cv)]
+    out, lse = flash_varlen.flash_prefix_forward(*dev, indices, cuq, cuk, 0.125)
+    assert out.shape == q.shape and lse.shape == (hq, t)
+    assert float((out.float().cpu() - want.detach()).abs().max()) < 2e-2
+    assert float((lse.cpu() - want_lse.detach()).abs().max()) < 2e-2
+    grads = flash_varlen.flash_prefix_backward(*dev, indices, cuq, cuk, out, lse, dout.to(DEV), 0.125)
+    for got, leaf in zip(grads, leaves):
+        assert got.shape == leaf.shape
+        assert float((got.float().cpu() - leaf.grad).abs().max()) < 2e-2 * (float(leaf.grad.abs().max()) + 1e-6)
+    assert not grads[3][150:220].any() and not grads[4][150:220].any()
+    if flash_varlen.REGISTERED:
+        out2, _ = torch.ops.bongard.flash_prefix_forward(*dev, indices, cuq, cuk, 0.125)
+        assert torch.equal(out2, out)
+    # a gather that is not [state run | own run], or that runs past the bank, is refused on the host
+    with pytest.raises(ValueError):
+        flash_varlen.flash_prefix_forward(*dev, indices.flip(0), cuq, cuk, 0.125)
+    with pytest.raises(ValueError):
+        flash_varlen.flash_prefix_forward(dev[0], dev[1], dev[2], dev[3][:100], dev[4][:100], indices, cuq, cuk, 0.125)
 
 
 def test_converted_mlp_trains_like_the_native_one(tiny):

@@ -6,7 +6,6 @@ quantisation error itself (emulation vs the unquantised product) is reported, no
 """
 
 import json
-from pathlib import Path
 
 import pytest
 import torch
@@ -66,10 +65,8 @@ def test_linear_fp8(m, n, k):
     assert_close(got, want)
     exact = x.float() @ w.float().t()
     rel = float((want - exact).norm() / exact.norm())
-    Path('gpurun_out').mkdir(exist_ok=True)
-    with open('gpurun_out/fp8_quantisation_error.jsonl', 'a') as f:
-        f.write(json.dumps(dict(m=m, n=n, k=k, relative_l2_quantisation_error=rel,
-                                kernel_vs_emulation_max_abs=float((got.float().cpu() - want).abs().max()))) + '\n')
+    print(json.dumps(dict(m=m, n=n, k=k, relative_l2_quantisation_error=rel,
+                          kernel_vs_emulation_max_abs=float((got.float().cpu() - want).abs().max()))))
     assert rel < 0.06
 
 
