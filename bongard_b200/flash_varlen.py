@@ -182,8 +182,11 @@ def attention(q, k, v, layout, scale, window, cross=None):
     """bongard/flash_varlen.py:129-139.  q [1,Hq,T,D], k/v [1,Hkv,T,D], cross (ck, cv) [1,Hkv,S,D];
     returns [1,Hq,T,D].  The [heads, tokens, D] storage is read in place (the kernel takes
     head and token strides), so nothing is transposed on the way in."""
+    from .packing import adopt_layout
+
     if q.ndim != 4 or q.shape[0] != 1:
         raise ValueError('packed attention expects [1, heads, tokens, head_dim] tensors')
+    layout = adopt_layout(layout)       # the reference's own PackedLayout is accepted as it is
     q3, k3, v3 = (t[0].transpose(0, 1) for t in (q, k, v))
     if k3.stride() != v3.stride():
         k3, v3 = k[0].contiguous().transpose(0, 1), v[0].contiguous().transpose(0, 1)

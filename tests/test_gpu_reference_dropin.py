@@ -150,7 +150,7 @@ def test_prefix_op_with_the_layout_the_reference_builds():
     q4, k4, v4, ck4, cv4 = (to4(x) for x in (q, k, v, ck, cv))
     # the module-level surface with the reference's layout object, window inactive
     out = flash_varlen.attention(q4, k4, v4, layout, 0.125, None, (ck4, cv4))
-    assert float((out[0].transpose(0, 1).float().cpu() - want.detach()).abs().max()) < 2e-2
+    assert float((out[0].detach().transpose(0, 1).float().cpu() - want.detach()).abs().max()) < 2e-2
     out.backward(dout.to(DEV).transpose(0, 1)[None])
     for got, leaf in zip((q4.grad, k4.grad, v4.grad, ck4.grad, cv4.grad), leaves):
         got = got[0].transpose(0, 1).float().cpu()
