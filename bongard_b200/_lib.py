@@ -21,6 +21,9 @@ SIGNATURES = {
     'bg_selftest_bounded_wait': ([I64, P, P], INT),
     'bg_rmsnorm': ([P, I64, P, P, I64, I64, I64, F32, P], INT),
     'bg_add_rmsnorm': ([P, P, P, P, P, I64, I64, F32, P], INT),
+    'bg_rmsnorm_f32': ([P, I64, P, P, I64, I64, I64, F32, P], INT),
+    'bg_add_rmsnorm_f32': ([P, P, P, P, P, I64, I64, F32, P], INT),
+    'bg_embed_f32': ([P, P, P, P, I64, I64, F32, I64, I64, P], INT),
     'bg_qk_norm_rope': ([P, I64, INT, P, I64, INT, P, P, P, P, I64, INT, F32, INT, P], INT),
     'bg_qk_norm_rope_table': ([P, I64, INT, P, I64, INT, P, P, P, P, I64, INT, F32, P], INT),
     'bg_embed': ([P, P, P, P, I64, I64, F32, I64, I64, P], INT),
@@ -56,7 +59,10 @@ SIGNATURES = {
     'bg_linear_fp8_static_max_bytes': ([], I64),
     'bg_linear_fp8_static': ([P, I64, P, I64, P, P, I64, I64, I64, I64, INT, P], INT),
     'bg_attention_tile_rows': ([INT], INT),
+    'bg_attention_pair_tile_rows': ([INT], INT),
     'bg_varlen_attention': ([P, I64, I64, P, P, I64, I64, P, P, I64, I64, P, P, P, I32, P, P, I64, I64, I64, INT, INT, INT,
+                             F32, P], INT),
+    'bg_varlen_attention_pair': ([P, I64, I64, P, P, I64, I64, P, P, I64, I64, P, P, P, I32, P, P, I64, I64, I64, INT, INT, INT,
                              F32, P], INT),
     'bg_varlen_attention_backward': ([P, I64, I64, P, P, I64, I64, P, P, I64, I64, P, P, I64, I64, P, P, P, P, P, P, P,
                                       P, I32, P, I32, P, P, I64, I64, I64, INT, INT, INT, F32, P], INT),

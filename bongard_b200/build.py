@@ -8,7 +8,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / 'csrc'
 LIB = HERE / 'libbongard_b200.so'
-SOURCES = ['api.cu', 'glue.cu', 'glue_bwd.cu', 'gemm_bf16.cu', 'gemm_bf16_pair.cu', 'gemm_bf16_skinny.cu', 'gemm_fp8.cu', 'gemm_mxfp8.cu', 'attn.cu', 'attn_bwd.cu']
+SOURCES = ['api.cu', 'glue.cu', 'glue_bwd.cu', 'gemm_bf16.cu', 'gemm_bf16_pair.cu', 'gemm_bf16_skinny.cu', 'gemm_fp8.cu', 'gemm_mxfp8.cu', 'attn.cu', 'attn_pair.cu', 'attn_bwd.cu']
 FLAGS = ['-gencode', 'arch=compute_100a,code=sm_100a', '-lineinfo', '-O3', '-std=c++17',
          '-Xcompiler', '-fPIC', '-cudart', 'static']
 

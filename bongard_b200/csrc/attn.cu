@@ -132,7 +132,7 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 for (int s = 0; s < SLABS; ++s)
                     tma_load_3d(smem + L::Q + s * SLAB, &map_q, q_full, s * 64, kvh * G, q_start);
                 auto load_k = [&](int j) {
-                    if (!mbar_wait(k_empty, (j & 1) ^ 1, ab, 201)) return;
+                    if (!mbar_wait_parked(k_empty, (j & 1) ^ 1, ab, 201)) return;
                     const bool pre = j < n_pre;
                     const int key0 = pre ? pre_start + j * KEYS : own_lo + (j - n_pre) * KEYS;
                     mbar_expect_tx(k_full, SLABS * SLAB);
@@ -140,7 +140,7 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         tma_load_3d(smem + L::K + s * SLAB, pre ? &map_ck : &map_k, k_full, s * 64, kvh, key0);
                 };
                 auto load_v = [&](int j) {
-                    if (!mbar_wait(v_empty, (j & 1) ^ 1, ab, 202)) return;
+                    if (!mbar_wait_parked(v_empty, (j & 1) ^ 1, ab, 202)) return;
                     const bool pre = j < n_pre;
                     const int key0 = pre ? pre_start + j * KEYS : own_lo + (j - n_pre) * KEYS;
                     mbar_expect_tx(v_full, SLABS * SLAB);
@@ -256,6 +256,13 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 }
                 l += sum;
 
+                // P(j) as packed bf16, formed BEFORE the wait below (the empty asm pins the conversions there): after the
+                // wait only the two tensor-memory stores remain on the critical path P.V(j-1) -> P(j) -> P.V(j).
+                uint32_t w[KEYS / 2];
+#pragma unroll
+                for (int i = 0; i < KEYS / 2; ++i) w[i] = pack_bf16(s[2 * i], s[2 * i + 1]);
+#pragma unroll
+                for (int i = 0; i < KEYS / 2; ++i) asm volatile("" : "+r"(w[i]));
                 // P(j) may only be stored once P.V(j-1) has completed: a tcgen05.st into tensor memory while a
                 // TS-form MMA is still reading its A operand from tensor memory corrupted results on B200, even
                 // though the two touch different columns.  The same wait makes O stable for a rescale.
@@ -275,14 +282,9 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         tmem_wait_st();
                     }
                 }
-                // P(j) as packed bf16 over the first 64 columns of the S buffer this thread has just read.
-#pragma unroll
-                for (int cc = 0; cc < KEYS / 2; cc += 32) {
-                    uint32_t w[32];
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) w[i] = pack_bf16(s[2 * (cc + i)], s[2 * (cc + i) + 1]);
-                    tmem_st32(tmem_base + lane_addr + b * KEYS + cc, w);
-                }
+                // over the first 64 columns of the S buffer this thread has just read
+                tmem_st32(tmem_base + lane_addr + b * KEYS, w);
+                tmem_st32(tmem_base + lane_addr + b * KEYS + 32, w + 32);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
@@ -294,20 +296,23 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 tc_fence_after();
                 const float inv = l > 0.f ? 1.f / l : 0.f;
                 __nv_bfloat16* dst = p.out + (token * p.q_heads + head) * D;
+                // a tensor-memory load takes some hundred cycles to return: up to four are in flight per wait
+                constexpr int EP = D < 128 ? D : 128;
 #pragma unroll 1
-                for (int cc = 0; cc < D; cc += 32) {
-                    uint32_t o[32];
-                    tmem_ld32(tmem_o + lane_addr + cc, o);
+                for (int half = 0; half < D; half += EP) {
+                    uint32_t o[EP];
+#pragma unroll
+                    for (int cc = 0; cc < EP; cc += 32) tmem_ld32(tmem_o + lane_addr + half + cc, o + cc);
                     tmem_wait_ld();
                     if (row_valid) {
 #pragma unroll
-                        for (int v4 = 0; v4 < 4; ++v4) {
+                        for (int v4 = 0; v4 < EP / 8; ++v4) {
                             uint4 v;
                             v.x = pack_bf16(__uint_as_float(o[v4 * 8 + 0]) * inv, __uint_as_float(o[v4 * 8 + 1]) * inv);
                             v.y = pack_bf16(__uint_as_float(o[v4 * 8 + 2]) * inv, __uint_as_float(o[v4 * 8 + 3]) * inv);
                             v.z = pack_bf16(__uint_as_float(o[v4 * 8 + 4]) * inv, __uint_as_float(o[v4 * 8 + 5]) * inv);
                             v.w = pack_bf16(__uint_as_float(o[v4 * 8 + 6]) * inv, __uint_as_float(o[v4 * 8 + 7]) * inv);
-                            *reinterpret_cast<uint4*>(dst + cc + v4 * 8) = v;
+                            *reinterpret_cast<uint4*>(dst + half + v4 * 8) = v;
                         }
                     }
                 }

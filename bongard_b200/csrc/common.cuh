@@ -89,6 +89,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// The same test with a suspend-time hint: the hardware may park the thread for up to `hint_ns` and wakes it
+// when the phase completes, so a waiting warp does not take issue slots from the warps that share its
+// scheduler (a spinning producer or MMA warp slowed the softmax warp beside it by a third).
+__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred P;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n"
+        "selp.b32 %0, 1, 0, P;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
 
 // Abort state shared by a CTA: word 0 of a small smem block.
 struct Abort {
@@ -102,6 +118,9 @@ struct Abort {
 };
 
 // Bounded wait on an mbarrier phase.  Returns false when the CTA has aborted.
+// Spinning form, for waits on a kernel's critical path (an MMA thread waiting for operands, epilogue and
+// softmax warps waiting for an accumulator): wakes within a few cycles of the phase completing.  The abort
+// flag and the budget are looked at every 32 failed tests.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const Abort& ab, int where,
                                           uint64_t budget_ns = kWaitBudgetNs) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -109,14 +128,31 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
     uint32_t spins = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (ab.raised()) return false;
-        if ((++spins & 0x3ff) == 0) {
-            uint64_t now = global_timer_ns();
+        if ((++spins & 31) == 0) {
+            if (ab.raised()) return false;
+            const uint64_t now = global_timer_ns();
             if (start == 0) start = now;
             else if (now - start > budget_ns) {
                 ab.raise(where);
                 return false;
             }
+        }
+    }
+}
+// Parked form, for waits that have slack (a producer waiting for a free slot of its ring): the thread is
+// parked in slices of kParkNs (see mbar_try_wait_parked) and takes no issue slots from the warp that shares
+// its scheduler; it wakes some hundred nanoseconds after the phase completes.
+constexpr uint32_t kParkNs = 50000;
+__device__ __forceinline__ bool mbar_wait_parked(uint64_t* bar, uint32_t parity, const Abort& ab, int where,
+                                                 uint64_t budget_ns = kWaitBudgetNs) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t start = global_timer_ns();
+    while (true) {
+        if (mbar_try_wait_parked(bar, parity, kParkNs)) return true;
+        if (ab.raised()) return false;
+        if (global_timer_ns() - start > budget_ns) {
+            ab.raise(where);
+            return false;
         }
     }
 }
@@ -147,6 +183,20 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, u
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
         : "memory");
 }
+
+// Tiled store from shared memory to global memory (the shared-memory tile has the layout a load with the same
+// map would produce).  Completion is tracked per thread in bulk groups: commit, then wait before the shared
+// memory is reused or the kernel ends.  Coordinates must not be negative; x * element size is a multiple of 16.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* src, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map),
+                 "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Until the stores committed so far have READ their shared-memory source (it may then be reused or released;
+// the global writes themselves complete on their own before the grid does).
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 
 // ---------------------------------------------------------------- TMEM / tcgen05
 __device__ __forceinline__ void tmem_alloc(uint32_t* slot_in_smem, uint32_t columns) {  // one full warp
@@ -273,8 +323,12 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
     return r;
 }
+// Arrive on a barrier given by its cluster address (own or peer CTA).  Default semantics (release at CTA
+// scope): what the waiting side consumes was produced by tcgen05 / TMA operations, which are ordered by their own
+// fences; a release at cluster scope stalled the arriving thread for 700-2000 cycles on the attention kernel's
+// critical path.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* slot_in_smem, uint32_t columns) {  // one warp in EACH CTA
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot_in_smem)),

@@ -146,7 +146,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                 // GeGLU -> rank 0 loads 128 gate rows, rank 1 the matching 128 up rows.
                 const int w0 = p.epilogue == 1 ? (rank == 0 ? tn * 128 : p.n + tn * 128) : tn * BN + rank * 128;
                 for (int kb = kb0; kb < kb1; ++kb) {
-                    if (!mbar_wait(&empty[stage], phase ^ 1, ab, 111)) break;
+                    if (!mbar_wait_parked(&empty[stage], phase ^ 1, ab, 111)) break;
                     uint8_t* sa = smem + stage * STAGE_BYTES;
                     const uint32_t leader_full = map_to_cta(smem_u32(&full[stage]), 0);
                     if (leader) mbar_expect_tx(&full[stage], 2 * STAGE_BYTES);

@@ -104,7 +104,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const int w0 = p.epilogue == 1 ? tn * 128 : tn * BN;
                 const int w1 = p.epilogue == 1 ? p.n + tn * 128 : tn * BN + 128;
                 for (int kb = 0; kb < kblocks; ++kb) {
-                    if (!mbar_wait(&empty[stage], phase ^ 1, ab, 301)) break;
+                    if (!mbar_wait_parked(&empty[stage], phase ^ 1, ab, 301)) break;
                     uint8_t* sa = smem + stage * STAGE_BYTES;
                     uint8_t* sb = sa + A_BYTES;
                     mbar_expect_tx(&full[stage], STAGE_BYTES);

@@ -146,7 +146,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 const int w1 = p.epilogue == 1 ? p.n + tn * 128 : tn * BN + 128;
                 const int w_rows = p.epilogue == 1 ? 2 * p.n : p.n;
                 for (int kb = 0; kb < kblocks; ++kb) {
-                    if (!mbar_wait(&empty[stage], phase ^ 1, ab, 501)) break;
+                    if (!mbar_wait_parked(&empty[stage], phase ^ 1, ab, 501)) break;
                     uint8_t* sa = smem + stage * TILE_BYTES;
                     uint8_t* sb = sa + A_BYTES;
                     uint8_t* sf = smem + SF_OFFSET + stage * SF_BYTES;

@@ -152,6 +152,143 @@ __global__ void add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ y, const __
     }
 }
 
+
+// ---------------------------------------------------------------- row-per-warp norm kernels
+// For hidden sizes that are a multiple of 256 (CH chunks of 32 lanes x 8 elements) one WARP owns a
+// row: it issues every 16-byte load of the row (and of the residual row) before the first use, so
+// a lane keeps CH (2 CH, 3 CH) independent requests in flight, reduces with shuffles only - no
+// shared memory, no block barrier - and walks on to row + (warps in the grid).  The residual stream
+// may be bf16 (the module chain's own rounding points are kept) or fp32 (no rounding between layers).
+template <typename T>
+struct Chunk8;
+template <>
+struct Chunk8<__nv_bfloat16> {
+    uint4 v;
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) { v = *reinterpret_cast<const uint4*>(p); }
+    __device__ __forceinline__ void load_streaming(const __nv_bfloat16* p) { v = __ldcs(reinterpret_cast<const uint4*>(p)); }
+    __device__ __forceinline__ void get(float* f) const { unpack8(v, f); }
+    __device__ __forceinline__ void set(const float* f) { v = pack8(f); }
+    __device__ __forceinline__ void store(__nv_bfloat16* p) const { *reinterpret_cast<uint4*>(p) = v; }
+};
+template <>
+struct Chunk8<float> {
+    float4 a, b;
+    __device__ __forceinline__ void load(const float* p) {
+        a = reinterpret_cast<const float4*>(p)[0];
+        b = reinterpret_cast<const float4*>(p)[1];
+    }
+    __device__ __forceinline__ void load_streaming(const float* p) { load(p); }
+    __device__ __forceinline__ void get(float* f) const {
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    }
+    __device__ __forceinline__ void set(const float* f) {
+        a = make_float4(f[0], f[1], f[2], f[3]);
+        b = make_float4(f[4], f[5], f[6], f[7]);
+    }
+    __device__ __forceinline__ void store(float* p) const {
+        reinterpret_cast<float4*>(p)[0] = a;
+        reinterpret_cast<float4*>(p)[1] = b;
+    }
+};
+template <typename T> __device__ __forceinline__ float round_as(float x);
+template <> __device__ __forceinline__ float round_as<__nv_bfloat16>(float x) { return round_bf16(x); }
+template <> __device__ __forceinline__ float round_as<float>(float x) { return x; }
+
+constexpr int ROW_WARPS = 4;    // warps per block of the row-per-warp kernels
+
+template <int CH, typename XT>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+rmsnorm_rows_kernel(const XT* __restrict__ x, int64_t ldx, const __nv_bfloat16* __restrict__ w,
+                    __nv_bfloat16* __restrict__ out, int64_t ldo, int64_t rows, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int64_t stride = int64_t(gridDim.x) * ROW_WARPS;
+    constexpr float inv_h = 1.f / float(CH * 256);
+    for (int64_t row = int64_t(blockIdx.x) * ROW_WARPS + (threadIdx.x >> 5); row < rows; row += stride) {
+        Chunk8<XT> xv[CH];
+#pragma unroll
+        for (int c = 0; c < CH; ++c) xv[c].load_streaming(x + row * ldx + c * 256 + lane * 8);
+        float ss = 0.f;
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+            float f[8];
+            xv[c].get(f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+        }
+        const float r = rsqrtf(warp_sum(ss) * inv_h + eps);
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+            float f[8], g[8];
+            xv[c].get(f);
+            unpack8(__ldg(reinterpret_cast<const uint4*>(w + c * 256 + lane * 8)), g);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = f[i] * r * (1.f + g[i]);
+            *reinterpret_cast<uint4*>(out + row * ldo + c * 256 + lane * 8) = pack8(f);
+        }
+    }
+}
+
+// resid <- resid + post_norm(y);  normed <- pre_norm(resid)   (see add_rmsnorm_kernel for the contract).
+// RT = __nv_bfloat16: post-norm result and updated residual are each rounded to bf16, as the module chain does;
+// RT = float: the residual stream stays in fp32 and nothing is rounded on the way into it.
+template <int CH, typename RT>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+add_rmsnorm_rows_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ w_post,
+                        RT* __restrict__ resid, const __nv_bfloat16* __restrict__ w_next,
+                        __nv_bfloat16* __restrict__ normed, int64_t rows, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int64_t stride = int64_t(gridDim.x) * ROW_WARPS;
+    constexpr int H = CH * 256;
+    constexpr float inv_h = 1.f / float(H);
+    for (int64_t row = int64_t(blockIdx.x) * ROW_WARPS + (threadIdx.x >> 5); row < rows; row += stride) {
+        Chunk8<__nv_bfloat16> yv[CH];
+        Chunk8<RT> xv[CH];
+#pragma unroll
+        for (int c = 0; c < CH; ++c) yv[c].load_streaming(y + row * H + c * 256 + lane * 8);
+#pragma unroll
+        for (int c = 0; c < CH; ++c) xv[c].load(resid + row * H + c * 256 + lane * 8);
+        float ss = 0.f;
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+            float f[8];
+            yv[c].get(f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+        }
+        float r = rsqrtf(warp_sum(ss) * inv_h + eps);
+        ss = 0.f;
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+            float f[8], g[8], x[8];
+            yv[c].get(f);
+            xv[c].get(x);
+            unpack8(__ldg(reinterpret_cast<const uint4*>(w_post + c * 256 + lane * 8)), g);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                x[i] = round_as<RT>(x[i] + round_as<RT>(f[i] * r * (1.f + g[i])));
+                ss += x[i] * x[i];
+            }
+            xv[c].set(x);
+            xv[c].store(resid + row * H + c * 256 + lane * 8);
+        }
+        if (w_next == nullptr) continue;
+        r = rsqrtf(warp_sum(ss) * inv_h + eps);
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+            float x[8], g[8];
+            xv[c].get(x);
+            unpack8(__ldg(reinterpret_cast<const uint4*>(w_next + c * 256 + lane * 8)), g);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] = x[i] * r * (1.f + g[i]);
+            *reinterpret_cast<uint4*>(normed + row * H + c * 256 + lane * 8) = pack8(x);
+        }
+    }
+}
+
 // QK-norm + RoPE in place.  One warp per token walks that token's query heads and key heads:
 // per head an fp32 RMSNorm over head_dim with (1 + w) gain, then rotate-half RoPE with the
 // angle position * inv_freq[i mod D/2] (bongard/attention.py:172-180; the fused form follows
@@ -242,8 +379,10 @@ __global__ void rope_table_kernel(float2* __restrict__ table, int64_t rows, int 
 }
 
 // Scaled word embedding with the end-of-image override (transformers modeling_t5gemma2.py:644-647).
+// OT = float writes the fp32 residual stream: the product table * scale is then not rounded.
+template <typename OT>
 __global__ void embed_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
-                             const __nv_bfloat16* __restrict__ eoi, __nv_bfloat16* __restrict__ out, int h,
+                             const __nv_bfloat16* __restrict__ eoi, OT* __restrict__ out, int h,
                              float scale, int64_t eoi_token, int64_t vocab) {
     pdl_wait();
     pdl_launch_dependents();
@@ -251,18 +390,18 @@ __global__ void embed_kernel(const int64_t* __restrict__ ids, const __nv_bfloat1
     const int c = threadIdx.x * 8;
     if (c >= h) return;
     int64_t id = ids[row];
-    uint4 v;
+    float f[8];
     if (id == eoi_token) {
-        v = *reinterpret_cast<const uint4*>(eoi + c);
+        unpack8(*reinterpret_cast<const uint4*>(eoi + c), f);
     } else {
         if (id < 0 || id >= vocab) id = 0;
-        float f[8];
         unpack8(*reinterpret_cast<const uint4*>(table + id * h + c), f);
 #pragma unroll
         for (int i = 0; i < 8; ++i) f[i] *= scale;
-        v = pack8(f);
     }
-    *reinterpret_cast<uint4*>(out + row * h + c) = v;
+    Chunk8<OT> v;
+    v.set(f);
+    v.store(out + row * h + c);
 }
 
 // Judgment head (bongard/model.py:92-95): logit = w.h + (C h).(G g) / sqrt(rank).
@@ -432,6 +571,43 @@ int check_launch(const char* what) {
 
 int row_threads(int64_t h) { return int(((h / 8 + 31) / 32) * 32); }
 
+// Grid of the row-per-warp kernels: enough blocks for every row, at most 16 per SM (rows beyond that are
+// reached by the stride loop).
+unsigned row_grid(int64_t rows) {
+    const int64_t blocks = (rows + ROW_WARPS - 1) / ROW_WARPS;
+    const int64_t cap = int64_t(bg_num_sms()) * 16;
+    return (unsigned)(blocks < cap ? blocks : cap);
+}
+
+// Row-per-warp RMSNorm for hidden sizes 256 * {1..16}; false when the size is not covered.
+template <typename XT>
+bool launch_rmsnorm_rows(const XT* x, int64_t ldx, const __nv_bfloat16* w, __nv_bfloat16* out, int64_t ldo, int64_t rows,
+                         int64_t h, float eps, cudaStream_t s) {
+    if (h % 256 || h > 4096) return false;
+    const dim3 grid(row_grid(rows)), block(ROW_WARPS * 32);
+#define BG_ROWS_CASE(CH) case CH: launch_kernel(rmsnorm_rows_kernel<CH, XT>, grid, block, 0, s, 0, x, ldx, w, out, ldo, rows, eps); return true;
+    switch (int(h / 256)) {
+        BG_ROWS_CASE(1) BG_ROWS_CASE(2) BG_ROWS_CASE(3) BG_ROWS_CASE(4) BG_ROWS_CASE(5) BG_ROWS_CASE(6) BG_ROWS_CASE(7) BG_ROWS_CASE(8)
+        BG_ROWS_CASE(9) BG_ROWS_CASE(10) BG_ROWS_CASE(11) BG_ROWS_CASE(12) BG_ROWS_CASE(13) BG_ROWS_CASE(14) BG_ROWS_CASE(15) BG_ROWS_CASE(16)
+    }
+#undef BG_ROWS_CASE
+    return false;
+}
+
+template <typename RT>
+bool launch_add_rmsnorm_rows(const __nv_bfloat16* y, const __nv_bfloat16* w_post, RT* resid, const __nv_bfloat16* w_next,
+                             __nv_bfloat16* normed, int64_t rows, int64_t h, float eps, cudaStream_t s) {
+    if (h % 256 || h > 4096) return false;
+    const dim3 grid(row_grid(rows)), block(ROW_WARPS * 32);
+#define BG_ROWS_CASE(CH) case CH: launch_kernel(add_rmsnorm_rows_kernel<CH, RT>, grid, block, 0, s, 0, y, w_post, resid, w_next, normed, rows, eps); return true;
+    switch (int(h / 256)) {
+        BG_ROWS_CASE(1) BG_ROWS_CASE(2) BG_ROWS_CASE(3) BG_ROWS_CASE(4) BG_ROWS_CASE(5) BG_ROWS_CASE(6) BG_ROWS_CASE(7) BG_ROWS_CASE(8)
+        BG_ROWS_CASE(9) BG_ROWS_CASE(10) BG_ROWS_CASE(11) BG_ROWS_CASE(12) BG_ROWS_CASE(13) BG_ROWS_CASE(14) BG_ROWS_CASE(15) BG_ROWS_CASE(16)
+    }
+#undef BG_ROWS_CASE
+    return false;
+}
+
 }  // namespace
 
 extern "C" {
@@ -443,10 +619,26 @@ int bg_rmsnorm(const void* x, int64_t ldx, const void* w, void* out, int64_t ldo
         return BG_ERR_SHAPE;
     }
     if (rows == 0) return BG_OK;
+    if (launch_rmsnorm_rows(static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(w),
+                            static_cast<__nv_bfloat16*>(out), ldo, rows, h, eps, static_cast<cudaStream_t>(stream)))
+        return check_launch("bg_rmsnorm");
     launch_kernel(rmsnorm_kernel, dim3((unsigned)rows), dim3(row_threads(h)), 0, static_cast<cudaStream_t>(stream), 0,
                   static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(w),
                   static_cast<__nv_bfloat16*>(out), ldo, (int)h, eps, (uint8_t*)nullptr, (uint8_t*)nullptr);
     return check_launch("bg_rmsnorm");
+}
+
+// The same norm over an fp32 input (the fp32 residual stream): x fp32 [rows, h] with row stride ldx, out bf16.
+int bg_rmsnorm_f32(const float* x, int64_t ldx, const void* w, void* out, int64_t ldo, int64_t rows, int64_t h,
+                   float eps, void* stream) {
+    if (rows < 0 || h <= 0 || h % 256 || h > 4096 || ldx % 8 || ldo % 8) {
+        bg_set_error("bg_rmsnorm_f32: hidden size must be a multiple of 256 up to 4096 (got %lld)", (long long)h);
+        return BG_ERR_SHAPE;
+    }
+    if (rows == 0) return BG_OK;
+    launch_rmsnorm_rows(x, ldx, static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(out), ldo, rows, h, eps,
+                        static_cast<cudaStream_t>(stream));
+    return check_launch("bg_rmsnorm_f32");
 }
 
 int bg_rmsnorm_mxfp8(const void* x, int64_t ldx, const void* w, void* out_q, void* out_scales, int64_t rows, int64_t h,
@@ -470,11 +662,30 @@ int bg_add_rmsnorm(const void* y, const void* w_post, void* resid, const void* w
         return BG_ERR_SHAPE;
     }
     if (rows == 0) return BG_OK;
+    if (launch_add_rmsnorm_rows(static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(w_post),
+                                static_cast<__nv_bfloat16*>(resid), static_cast<const __nv_bfloat16*>(w_next),
+                                static_cast<__nv_bfloat16*>(normed), rows, h, eps, static_cast<cudaStream_t>(stream)))
+        return check_launch("bg_add_rmsnorm");
     launch_kernel(add_rmsnorm_kernel, dim3((unsigned)rows), dim3(row_threads(h)), 0, static_cast<cudaStream_t>(stream), 0,
                   static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(w_post),
                   static_cast<__nv_bfloat16*>(resid), static_cast<const __nv_bfloat16*>(w_next),
                   static_cast<__nv_bfloat16*>(normed), (int)h, eps, (uint8_t*)nullptr, (uint8_t*)nullptr);
     return check_launch("bg_add_rmsnorm");
+}
+
+// bg_add_rmsnorm over an fp32 residual stream: resid fp32 [rows, h] is updated without rounding
+// (resid += rmsnorm(y) * (1 + w_post), all in fp32); normed (bf16) feeds the next GEMM.
+int bg_add_rmsnorm_f32(const void* y, const void* w_post, float* resid, const void* w_next, void* normed, int64_t rows,
+                       int64_t h, float eps, void* stream) {
+    if (rows < 0 || h <= 0 || h % 256 || h > 4096) {
+        bg_set_error("bg_add_rmsnorm_f32: hidden size must be a multiple of 256 up to 4096 (got %lld)", (long long)h);
+        return BG_ERR_SHAPE;
+    }
+    if (rows == 0) return BG_OK;
+    launch_add_rmsnorm_rows(static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(w_post), resid,
+                            static_cast<const __nv_bfloat16*>(w_next), static_cast<__nv_bfloat16*>(normed), rows, h, eps,
+                            static_cast<cudaStream_t>(stream));
+    return check_launch("bg_add_rmsnorm_f32");
 }
 
 int bg_add_rmsnorm_mxfp8(const void* y, const void* w_post, void* resid, const void* w_next, void* normed_q,
@@ -588,10 +799,24 @@ int bg_embed(const int64_t* ids, const void* table, const void* eoi_embedding, v
         return BG_ERR_SHAPE;
     }
     if (rows == 0) return BG_OK;
-    launch_kernel(embed_kernel, dim3((unsigned)rows), dim3(row_threads(h)), 0, static_cast<cudaStream_t>(stream), 0, 
+    launch_kernel(embed_kernel<__nv_bfloat16>, dim3((unsigned)rows), dim3(row_threads(h)), 0, static_cast<cudaStream_t>(stream), 0,
         ids, static_cast<const __nv_bfloat16*>(table), static_cast<const __nv_bfloat16*>(eoi_embedding),
         static_cast<__nv_bfloat16*>(out), (int)h, scale, eoi_token, vocab);
     return check_launch("bg_embed");
+}
+
+// bg_embed into an fp32 residual stream: out fp32 [rows, h] = table[id] * scale, not rounded.
+int bg_embed_f32(const int64_t* ids, const void* table, const void* eoi_embedding, float* out, int64_t rows, int64_t h,
+                 float scale, int64_t eoi_token, int64_t vocab, void* stream) {
+    if (rows < 0 || h <= 0 || h % 8 || h > 8192) {
+        bg_set_error("bg_embed_f32: hidden size must be a multiple of 8 up to 8192");
+        return BG_ERR_SHAPE;
+    }
+    if (rows == 0) return BG_OK;
+    launch_kernel(embed_kernel<float>, dim3((unsigned)rows), dim3(row_threads(h)), 0, static_cast<cudaStream_t>(stream), 0,
+        ids, static_cast<const __nv_bfloat16*>(table), static_cast<const __nv_bfloat16*>(eoi_embedding), out, (int)h, scale,
+        eoi_token, vocab);
+    return check_launch("bg_embed_f32");
 }
 
 int bg_judgment_head(const void* hidden, int64_t ldh, const int32_t* cand_rows, const int32_t* dec_rows,

@@ -66,10 +66,19 @@ class JudgmentEngine:
     """A full replica of the judgment model on one GPU."""
 
     def __init__(self, weights, shape: ModelShape, device='cuda', *, encoder_pack_tokens=65536,
-                 decoder_pack_tokens=16384, linears='bf16'):
+                 decoder_pack_tokens=16384, linears='bf16', residual='bf16'):
         ops.device_check()
         if linears not in ('bf16', 'fp8', 'mxfp8'):
             raise ValueError("linears must be 'bf16', 'fp8' or 'mxfp8'")
+        if residual not in ('bf16', 'fp32'):
+            raise ValueError("residual must be 'bf16' or 'fp32'")
+        if residual == 'fp32' and (linears == 'mxfp8' or shape.hidden % 256):
+            raise ValueError('the fp32 residual stream needs a hidden size that is a multiple of 256 and bf16 or fp8 linears')
+        # 'bf16': the residual stream and the post-norm results are rounded to bf16 exactly where the bf16 module
+        # chain rounds them.  'fp32': the stream between layers stays fp32 (embedding, residual adds, the input of
+        # every pre-norm), GEMM and attention operands are bf16 as before - the arithmetic of the reference run
+        # in float32 apart from the tensor-core operand rounding.
+        self.residual = residual
         self.linears, fp8 = linears, linears
         self.shape, self.device = shape, torch.device(device)
         self.encoder_pack_tokens, self.decoder_pack_tokens = encoder_pack_tokens, decoder_pack_tokens
@@ -81,7 +90,7 @@ class JudgmentEngine:
         self.dec = [_stack_layer(weights, f'decoder.layers.{i}.', self.device, fp8, True) for i in range(shape.layers)]
         self.head_w, self.head_c, self.head_g = g('head.w.weight'), g('head.candidate.weight'), g('head.global_readout.weight')
         # per stack, as a checkpoint may override either (bongard/model.py:632-637)
-        self.embed_scale_enc = self.embed_scale_dec = embed_scale(shape, BF16)
+        self.embed_scale_enc = self.embed_scale_dec = embed_scale(shape, BF16 if residual == 'bf16' else torch.float32)
         self.launches = 0          # kernels launched by this library (for reporting)
         # The serving path lets stacks of up to 256 tokens use the split-K weight-streaming GEMM.  The
         # packed engine keeps it off, so that where a pack boundary falls never changes a result bit.
@@ -196,7 +205,8 @@ class JudgmentEngine:
     def _stack(self, layers, final_norm, pack, cross=None):
         s = self.shape
         scale = self.embed_scale_enc if layers is self.enc else self.embed_scale_dec
-        x = ops.embed(pack.ids, self.table, self.eoi, scale, s.eoi_token)
+        x = ops.embed(pack.ids, self.table, self.eoi, scale, s.eoi_token,
+                      dtype=BF16 if self.residual == 'bf16' else torch.float32)
         mx = self.linears == 'mxfp8'          # norms hand the GEMMs MXFP8 directly: no bf16 copy of a normed row
         n = ops.rmsnorm_mxfp8(x, layers[0].pre_attn, s.eps) if mx else ops.rmsnorm(x, layers[0].pre_attn, s.eps)
         t = x.shape[0]

@@ -3,7 +3,9 @@
 Mirrors bongard/fused_mlp.py: `enable_fused_mlp(model, recipe)` replaces every text layer's
 `mlp` by a module that also owns the pre-feed-forward RMSNorm (zero-centred gain) and sets
 `layer.pre_feedforward_layernorm` to Identity (fused_mlp.py:84-98), returning the count.
-The module keeps the native parameter objects, so `hf_state_dict` only has to rename keys.
+The norm gain and the down projection stay the native parameter objects; gate and up are stacked
+into one parameter (as the reference's fc1_weight is, fused_mlp.py:37-38).  `hf_state_dict(backbone)`
+gives the state under Hugging Face keys again, for `JudgmentModel.save` (bongard/model.py:531-539).
 """
 
 from __future__ import annotations
@@ -50,10 +52,19 @@ def enable_fused_mlp(model, recipe='bf16'):
     return count
 
 
-def hf_state_dict(module_name, fused: B200FusedMLP):
-    """Hugging Face keys for one fused MLP (the inverse of the stacking, bongard/fused_mlp.py:101-124)."""
-    layer = module_name.rsplit('.', 1)[0]
-    gate, up = fused.mlp.gate_up.weight.split(fused.intermediate_size)
-    return {f'{layer}.pre_feedforward_layernorm.weight': fused.layer_norm_weight,
-            f'{module_name}.gate_proj.weight': gate, f'{module_name}.up_proj.weight': up,
-            f'{module_name}.down_proj.weight': fused.mlp.down.weight}
+def hf_state_dict(backbone):
+    """The backbone's state under Hugging Face keys, or None when nothing was converted
+    (bongard/fused_mlp.py:101-124: the inverse of the fused gate/up layout and of the converted
+    projections, what `Transformers.save_pretrained(state_dict=...)` is handed by JudgmentModel.save)."""
+    from . import te_linear
+
+    fused = [(name, module) for name, module in backbone.named_modules() if isinstance(module, B200FusedMLP)]
+    if not fused and not te_linear.present(backbone):
+        return None
+    state = te_linear.restore_hf_layout(backbone, backbone.state_dict())
+    for name, module in fused:
+        prefix = name + '.'
+        for key in ('gate_proj', 'up_proj', 'down_proj'):       # the inner B200MLP was un-stacked one level down
+            state[prefix + key + '.weight'] = state.pop(prefix + 'mlp.' + key + '.weight')
+        state[name.rsplit('.', 1)[0] + '.pre_feedforward_layernorm.weight'] = state.pop(prefix + 'layer_norm_weight')
+    return state

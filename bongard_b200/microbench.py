@@ -39,6 +39,9 @@ from . import ops, workload as wl
 DEV = 'cuda'
 
 
+MIN_SECONDS = 0.4      # every timing loops at least this long, so that the 200 ms clock sampler sees it
+
+
 def timed(fn, iters, warmup, flush=None):
     for _ in range(warmup):
         fn()
@@ -46,12 +49,17 @@ def timed(fn, iters, warmup, flush=None):
     total = 0.0
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if flush is None:
-        begin.record()
-        for _ in range(iters):
-            fn()
-        end.record()
-        torch.cuda.synchronize()
-        return begin.elapsed_time(end) / iters
+        rounds = 0
+        while True:
+            begin.record()
+            for _ in range(iters):
+                fn()
+            end.record()
+            torch.cuda.synchronize()
+            total += begin.elapsed_time(end)
+            rounds += 1
+            if total >= MIN_SECONDS * 1e3 or iters <= 1:
+                return total / (rounds * iters)
     for _ in range(iters):
         flush.zero_()
         begin.record()
@@ -78,10 +86,12 @@ def attention(args, flush):
     gain = torch.zeros(d, device=DEV, dtype=torch.bfloat16)
     positions = torch.cat([torch.arange(n, dtype=torch.int32) for n in lengths]).to(DEV)
     ops.qk_norm_rope_(q, k, gain, gain, positions, ops.inv_freq(d, theta, DEV))
-    plan = ops.make_plan(lengths, window, DEV, group=hq // hkv, head_dim=d, backward=args.backward)
+    plan = ops.make_plan(lengths, window, DEV, group=hq // hkv, head_dim=d, backward=args.backward,
+                         pair=False if args.no_pair else None)
     ms = timed(lambda: ops.varlen_attention(q, k, v, plan, d ** -0.5), args.iters, args.warmup, flush)
     flops = 4 * d * hq * plan.pairs
     out = [dict(op=f'varlen_attention_{args.variant}', tokens=t, sequences=len(lengths), tiles=plan.n_tiles,
+                pair_tiles=plan.n_pair_tiles,
                 ms=ms, tflops=flops / ms / 1e9, algorithmic_tflop=flops / 1e12,
                 min_bytes=2 * t * (2 * hq + 2 * hkv) * d)]
     if args.backward:
@@ -369,13 +379,18 @@ def main():
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--fp8', action='store_true', help='mlp: also time the E4M3 block-scaled path')
     ap.add_argument('--flush', action='store_true', help='write a 256 MB buffer between launches')
+    ap.add_argument('--no-pair', action='store_true', help='attention: 128-row tiles on single CTAs instead of CTA pairs')
     args = ap.parse_args()
     ops.device_check()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV) if args.flush else None
+    from .clocks import ClockSampler
+
+    sampler = ClockSampler(torch.cuda.current_device()).start()
     result = {'attention': attention, 'mlp': mlp, 'linear': linear, 'glue': glue, 'serve': serve, 'dropin': dropin, 'train': train}[args.op](args, flush)
     ops.read_status()
+    clocks = sampler.stop()       # SM clock and throttle reasons while the ops above ran: a timing without it proves nothing
     for row in result if isinstance(result, list) else [result]:
-        print(json.dumps(row))
+        print(json.dumps({**row, 'clocks': clocks}))
 
 
 if __name__ == '__main__':

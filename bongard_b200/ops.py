@@ -59,9 +59,9 @@ def _need(t, name, dtype=BF16):
     return t
 
 
-def _rows(t, name):
+def _rows(t, name, dtype=BF16):
     """View [..., h] as rows with one stride; returns (tensor, rows, h, row_stride)."""
-    _need(t, name)
+    _need(t, name, dtype)
     if t.stride(-1) != 1:
         raise ValueError(f'{name} must be contiguous in its last dimension')
     flat = t.reshape(-1, t.shape[-1])
@@ -82,25 +82,35 @@ def read_status():
 
 
 def rmsnorm(x, weight, eps=1e-6):
+    """rmsnorm(x) * (1 + weight) as bf16; x bf16, or fp32 (the fp32 residual stream; hidden size a multiple of 256)."""
     lib = _lib.load()
-    flat, rows, h, ldx = _rows(x, 'x')
+    fp32 = x.dtype == torch.float32
+    flat, rows, h, ldx = _rows(x, 'x', x.dtype if fp32 else BF16)
+    if fp32 and h % 256:
+        raise ValueError('an fp32 input needs a hidden size that is a multiple of 256')
     out = torch.empty((rows, h), device=x.device, dtype=BF16)
-    _lib.check(lib.bg_rmsnorm(_ptr(flat), ldx, _ptr(_need(weight, 'weight')), _ptr(out), h, rows, h, eps, _stream()),
-               'bg_rmsnorm')
+    entry, name = (lib.bg_rmsnorm_f32, 'bg_rmsnorm_f32') if fp32 else (lib.bg_rmsnorm, 'bg_rmsnorm')
+    _lib.check(entry(_ptr(flat), ldx, _ptr(_need(weight, 'weight')), _ptr(out), h, rows, h, eps, _stream()), name)
     return out.view(x.shape)
 
 
 def add_rmsnorm_(y, w_post, resid, w_next=None, eps=1e-6):
-    """resid += rmsnorm(y)*(1+w_post) in place; returns rmsnorm(resid)*(1+w_next) or None."""
+    """resid += rmsnorm(y)*(1+w_post) in place; returns rmsnorm(resid)*(1+w_next) (bf16) or None.
+    resid is bf16 (post-norm result and sum each rounded to bf16, as the module chain does) or fp32
+    (nothing rounded on the way into the residual stream)."""
     lib = _lib.load()
-    _need(y, 'y'), _need(resid, 'resid')
+    fp32 = resid.dtype == torch.float32
+    _need(y, 'y'), _need(resid, 'resid', resid.dtype if fp32 else BF16)
     if not (y.is_contiguous() and resid.is_contiguous()) or y.shape != resid.shape:
         raise ValueError('y and resid must be contiguous and of equal shape')
     h = y.shape[-1]
+    if fp32 and h % 256:
+        raise ValueError('an fp32 residual stream needs a hidden size that is a multiple of 256')
     rows = y.numel() // h
-    normed = torch.empty_like(resid) if w_next is not None else None
-    _lib.check(lib.bg_add_rmsnorm(_ptr(y), _ptr(_need(w_post, 'w_post')), _ptr(resid), _ptr(w_next), _ptr(normed),
-                                  rows, h, eps, _stream()), 'bg_add_rmsnorm')
+    normed = torch.empty_like(y) if w_next is not None else None
+    entry, name = (lib.bg_add_rmsnorm_f32, 'bg_add_rmsnorm_f32') if fp32 else (lib.bg_add_rmsnorm, 'bg_add_rmsnorm')
+    _lib.check(entry(_ptr(y), _ptr(_need(w_post, 'w_post')), _ptr(resid), _ptr(w_next), _ptr(normed),
+                     rows, h, eps, _stream()), name)
     return normed
 
 
@@ -148,13 +158,17 @@ def qk_norm_rope_table_(q, k, q_weight, k_weight, cos, sin, eps=1e-6):
                'bg_qk_norm_rope_table')
 
 
-def embed(ids, table, eoi_embedding, scale, eoi_token=256_000):
+def embed(ids, table, eoi_embedding, scale, eoi_token=256_000, dtype=BF16):
+    """table[ids] * scale (the end-of-image row unscaled); dtype torch.float32 writes an fp32 residual stream."""
     lib = _lib.load()
     _need(ids, 'ids', torch.int64), _need(table, 'table')
+    if dtype not in (BF16, torch.float32):
+        raise ValueError('the embedding is written as bf16 or fp32')
     ids = ids.reshape(-1).contiguous()
-    out = torch.empty((ids.numel(), table.shape[1]), device=table.device, dtype=BF16)
-    _lib.check(lib.bg_embed(_ptr(ids), _ptr(table), _ptr(_need(eoi_embedding, 'eoi_embedding')), _ptr(out),
-                            ids.numel(), table.shape[1], scale, eoi_token, table.shape[0], _stream()), 'bg_embed')
+    out = torch.empty((ids.numel(), table.shape[1]), device=table.device, dtype=dtype)
+    entry, name = (lib.bg_embed, 'bg_embed') if dtype == BF16 else (lib.bg_embed_f32, 'bg_embed_f32')
+    _lib.check(entry(_ptr(ids), _ptr(table), _ptr(_need(eoi_embedding, 'eoi_embedding')), _ptr(out),
+                     ids.numel(), table.shape[1], scale, eoi_token, table.shape[0], _stream()), name)
     return out
 
 
@@ -562,6 +576,8 @@ class AttentionPlan:
     n_kv_tiles: int = 0
     own_extent: int = 0      # one past the last own-key row any tile addresses (host copy, for bounds checks)
     state_extent: int = 0    # one past the last state row any tile addresses
+    pair_tiles: torch.Tensor = None  # int32 [n_pair_tiles, 8]: 256-row tiles served by CTA pairs (head_dim 256)
+    n_pair_tiles: int = 0
 
 
 def plan_rows(lengths, window, *, decoder):
@@ -590,7 +606,7 @@ def plan_rows(lengths, window, *, decoder):
 
 @dataclass
 class HostPlan:
-    """Host half of an attention plan: one int32 array [tiles*8 | row_lo | row_hi]."""
+    """Host half of an attention plan: one int32 array [tiles*8 | pair tiles*8 | row_lo | row_hi | key tiles*8]."""
 
     packed: np.ndarray
     tokens: int
@@ -600,6 +616,7 @@ class HostPlan:
     n_kv_tiles: int = 0      # key tiles for the backward passes, appended after row_hi
     own_extent: int = 0      # one past the last own-key row / state row the tiles address
     state_extent: int = 0
+    n_pair_tiles: int = 0    # 256-row tiles for the CTA-pair kernel, stored after the 128-row tiles
 
     def to(self, device):
         dev = torch.from_numpy(self.packed).to(device, non_blocking=True)
@@ -611,6 +628,8 @@ class HostPlan:
         beyond its own see no key."""
         if tokens < self.tokens or n_tiles < self.n_tiles:
             raise ValueError(f'plan of {self.tokens} tokens / {self.n_tiles} tiles does not fit {tokens} / {n_tiles}')
+        if self.n_pair_tiles:
+            raise ValueError('fixed-size plans hold 128-row tiles only (build the plan with pair=False)')
         n8, t = self.n_tiles * 8, self.tokens
         out = np.zeros(n_tiles * 8 + 2 * tokens, dtype=np.int32)
         out[:n8] = self.packed[:n8]
@@ -619,18 +638,29 @@ class HostPlan:
         return HostPlan(out, tokens, n_tiles, self.pairs, self.tile_rows, 0, self.own_extent, self.state_extent)
 
     def view(self, dev):
-        n8, t = self.n_tiles * 8, self.tokens
-        plan = AttentionPlan(dev[:n8].view(-1, 8), dev[n8:n8 + t], dev[n8 + t:n8 + 2 * t], t, self.n_tiles, self.pairs,
+        s8, t = self.n_tiles * 8, self.tokens
+        n8 = s8 + self.n_pair_tiles * 8
+        plan = AttentionPlan(dev[:s8].view(-1, 8), dev[n8:n8 + t], dev[n8 + t:n8 + 2 * t], t, self.n_tiles, self.pairs,
                              self.tile_rows, own_extent=self.own_extent, state_extent=self.state_extent)
+        if self.n_pair_tiles:
+            plan.pair_tiles, plan.n_pair_tiles = dev[s8:n8].view(-1, 8), self.n_pair_tiles
         if self.n_kv_tiles:
             plan.kv_tiles = dev[n8 + 2 * t:n8 + 2 * t + self.n_kv_tiles * 8].view(-1, 8)
             plan.n_kv_tiles = self.n_kv_tiles
         return plan
 
 
-def tile_rows(head_dim):
-    """Query rows (tokens x GQA group) one attention tile holds for a head size, as the library reports it."""
-    return _lib.load().bg_attention_tile_rows(int(head_dim)) if head_dim else 128
+PAIR_ATTENTION = True    # head_dim 256, forward-only plans: 256-row tiles served by CTA pairs (off: 128-row tiles)
+
+
+def tile_rows(head_dim, pair=False):
+    """Query rows (tokens x GQA group) one attention tile holds for a head size, as the library reports it:
+    128 for the single-CTA kernel and the backward passes, 256 for the CTA-pair forward kernel (head_dim 256)."""
+    if not head_dim:
+        return 128
+    lib = _lib.load()
+    rows = lib.bg_attention_pair_tile_rows(int(head_dim)) if pair else 0
+    return rows or lib.bg_attention_tile_rows(int(head_dim))
 
 
 def _state_bank(owners, state_lengths, state_offsets):
@@ -697,14 +727,15 @@ def make_host_kv_tiles(lengths, window, *, owners=None, state_lengths=None, stat
 
 
 def make_host_plan(lengths, window, *, group, owners=None, state_lengths=None, head_dim=None, backward=False,
-                   state_offsets=None):
+                   state_offsets=None, pair=None):
     """Tile a pack of segments for the attention kernel (host arithmetic on lengths only).
 
     Encoder (owners None): tiles never cross a segment.  Decoder: consecutive questions of the
     same owner form one run; a tile is up to 128/group consecutive tokens of a run, so
     questions that share a state also share its key stream.  `state_offsets[o]` is the first row
     of owner o's state in the bank (default: states back to back in owner order).  Tiles are
-    ordered heaviest first."""
+    ordered heaviest first.  `pair` (default: PAIR_ATTENTION for forward-only plans) asks for the
+    256-row tiles of the CTA-pair kernel where the head size has one."""
     lengths = [int(n) for n in lengths]
     if any(n < 0 for n in lengths):
         raise ValueError('segment lengths must not be negative')
@@ -713,8 +744,10 @@ def make_host_plan(lengths, window, *, group, owners=None, state_lengths=None, h
         raise ValueError('decoder plans need state_lengths and one owner per segment')
     lo, hi = plan_rows(lengths, window, decoder=decoder)
     total = len(lo)
-    rows = tile_rows(head_dim)
-    tq = rows // group
+    single_rows = tile_rows(head_dim)
+    pair_rows = tile_rows(head_dim, pair=True) if (PAIR_ATTENTION if pair is None else pair) and not backward else 0
+    if pair_rows == single_rows:
+        pair_rows = 0                       # this head size has no pair kernel
     runs = []      # [start, end, prefix_start, prefix_len, owner]
     offset = 0
     if decoder:
@@ -731,21 +764,46 @@ def make_host_plan(lengths, window, *, group, owners=None, state_lengths=None, h
             offset += n
     runs = [r for r in runs if r[1] > r[0]]
     if not runs:
-        return HostPlan(np.zeros(0, dtype=np.int32), 0, 0, 0, rows)
+        return HostPlan(np.zeros(0, dtype=np.int32), 0, 0, 0, single_rows)
     run = np.asarray([r[:4] for r in runs], dtype=np.int64)
-    counts = (run[:, 1] - run[:, 0] + tq - 1) // tq
-    which = np.repeat(np.arange(len(runs)), counts)
-    first = np.cumsum(counts) - counts
-    q_start = run[which, 0] + (np.arange(int(counts.sum())) - first[which]) * tq
-    q_count = np.minimum(run[which, 1] - q_start, tq)
-    own_lo = np.minimum.reduceat(lo, q_start)
-    own_hi = np.maximum.reduceat(hi, q_start)
-    lo_max = np.maximum.reduceat(lo, q_start)
-    hi_min = np.minimum.reduceat(hi, q_start)
-    tiles = np.stack([q_start, q_count, own_lo, own_hi, lo_max, hi_min, run[which, 2], run[which, 3]], axis=1)
-    work = run[which, 3] + own_hi - own_lo
-    tiles = tiles[np.argsort(-work, kind='stable')].astype(np.int32)
-    parts = [tiles.reshape(-1), lo.astype(np.int32), hi.astype(np.int32)]
+
+    def tile(rows, part):
+        """Tile records of `rows`-row tiles over the runs `part` ([start, end, prefix_start, prefix_len] each)."""
+        part = part[part[:, 1] > part[:, 0]]
+        if not len(part):
+            return np.zeros((0, 8), dtype=np.int32)
+        tq = rows // group
+        big = np.int64(1) << 40
+        counts = (part[:, 1] - part[:, 0] + tq - 1) // tq
+        which = np.repeat(np.arange(len(part)), counts)
+        first = np.cumsum(counts) - counts
+        q_start = part[which, 0] + (np.arange(int(counts.sum())) - first[which]) * tq
+        q_count = np.minimum(part[which, 1] - q_start, tq)
+        # per-tile extremes of the rows' key ranges (reduceat over [q_start, q_start + q_count))
+        edges = np.stack([q_start, q_start + q_count], axis=1).reshape(-1)      # index `total` is the pad element
+        own_lo = np.minimum.reduceat(np.append(lo, big), edges)[::2]
+        own_hi = np.maximum.reduceat(np.append(hi, -big), edges)[::2]
+        lo_max = np.maximum.reduceat(np.append(lo, -big), edges)[::2]
+        hi_min = np.minimum.reduceat(np.append(hi, big), edges)[::2]
+        records = np.stack([q_start, q_count, own_lo, own_hi, lo_max, hi_min, part[which, 2], part[which, 3]], axis=1)
+        work = part[which, 3] + own_hi - own_lo
+        return records[np.argsort(-work, kind='stable')].astype(np.int32)
+
+    if pair_rows:
+        # A pair occupies two SMs for the whole key stream of its tile however few rows its second CTA holds.  So a run
+        # is cut into full 256-row tiles, and what is left goes to a pair only if it fills more than one CTA; a
+        # shorter rest becomes one 128-row tile for the single-CTA kernel.  The cut depends on the run alone.
+        tqp, tqs = pair_rows // group, single_rows // group
+        n = run[:, 1] - run[:, 0]
+        rest = n % tqp
+        pair_tokens = n - np.where(rest > tqs if pair is None else False, 0, rest) if pair is None else n
+        pair_part = np.stack([run[:, 0], run[:, 0] + pair_tokens, run[:, 2], run[:, 3]], axis=1)
+        single_part = np.stack([run[:, 0] + pair_tokens, run[:, 1], run[:, 2], run[:, 3]], axis=1)
+        pair_tiles, tiles = tile(pair_rows, pair_part), tile(single_rows, single_part)
+    else:
+        pair_tiles, tiles = np.zeros((0, 8), dtype=np.int32), tile(single_rows, run)
+    rows = single_rows
+    parts = [tiles.reshape(-1), pair_tiles.reshape(-1), lo.astype(np.int32), hi.astype(np.int32)]
     n_kv = 0
     if backward:
         kv = make_host_kv_tiles(lengths, window, owners=owners, state_lengths=state_lengths, state_offsets=state_offsets)
@@ -755,13 +813,14 @@ def make_host_plan(lengths, window, *, group, owners=None, state_lengths=None, h
     if decoder:
         pairs += int(sum(n * state_lengths[o] for n, o in zip(lengths, owners)))
     state_extent = int((run[:, 2] + run[:, 3])[run[:, 3] > 0].max(initial=0))
-    return HostPlan(np.concatenate(parts), total, tiles.shape[0], pairs, rows, n_kv, total, state_extent)
+    return HostPlan(np.concatenate(parts), total, tiles.shape[0], pairs, rows, n_kv, total, state_extent,
+                    pair_tiles.shape[0])
 
 
 def make_plan(lengths, window, device, *, group, owners=None, state_lengths=None, head_dim=None, backward=False,
-              state_offsets=None):
+              state_offsets=None, pair=None):
     return make_host_plan(lengths, window, group=group, owners=owners, state_lengths=state_lengths,
-                          head_dim=head_dim, backward=backward, state_offsets=state_offsets).to(device)
+                          head_dim=head_dim, backward=backward, state_offsets=state_offsets, pair=pair).to(device)
 
 
 def check_plan_bounds(plan, key_rows, state_rows):
@@ -791,6 +850,8 @@ def varlen_attention(q, k, v, plan, scale, cross=None, return_lse=False):
         raise ValueError(f'plan was built for {plan.tokens} tokens, q has {tq}')
     if plan.tile_rows > lib.bg_attention_tile_rows(d):
         raise ValueError(f'plan has {plan.tile_rows}-row tiles; head_dim {d} takes {lib.bg_attention_tile_rows(d)}')
+    if plan.n_pair_tiles and lib.bg_attention_pair_tile_rows(d) == 0:
+        raise ValueError(f'plan has tiles for CTA pairs; head_dim {d} has no pair kernel')
     ck = cv = None
     ts = ldc = hsc = 0
     if cross is not None:
@@ -804,11 +865,13 @@ def varlen_attention(q, k, v, plan, scale, cross=None, return_lse=False):
     lse = torch.empty((hq, tq), device=q.device, dtype=torch.float32) if return_lse else None
     timer = ATTN_TIMER
     begin = timer.start() if timer is not None else None
-    _lib.check(lib.bg_varlen_attention(
-        _ptr(q), q.stride(0), q.stride(1), _ptr(k), _ptr(v), k.stride(0), k.stride(1), _ptr(ck), _ptr(cv), ldc, hsc,
-        _ptr(out), _ptr(lse),
-        _ptr(plan.tiles), plan.n_tiles, _ptr(plan.row_lo), _ptr(plan.row_hi), tq, tk, ts, hq, hkv, d,
-        float(scale), _stream()), 'bg_varlen_attention')
+    for entry, name, tiles, n_tiles in ((lib.bg_varlen_attention_pair, 'bg_varlen_attention_pair', plan.pair_tiles, plan.n_pair_tiles),
+                                        (lib.bg_varlen_attention, 'bg_varlen_attention', plan.tiles, plan.n_tiles)):
+        if n_tiles:       # the two kernels write disjoint rows of out / lse
+            _lib.check(entry(
+                _ptr(q), q.stride(0), q.stride(1), _ptr(k), _ptr(v), k.stride(0), k.stride(1), _ptr(ck), _ptr(cv), ldc, hsc,
+                _ptr(out), _ptr(lse), _ptr(tiles), n_tiles, _ptr(plan.row_lo), _ptr(plan.row_hi), tq, tk, ts, hq, hkv, d,
+                float(scale), _stream()), name)
     if timer is not None:
         timer.stop(begin, 4 * d * hq * plan.pairs)
     return (out, lse) if return_lse else out
@@ -956,10 +1019,23 @@ def quantize_weight(weight):
 _WORKSPACE = {}
 
 
+_RETIRED_WORKSPACES = []
+
+
 def _workspace(device, nbytes):
-    """A grow-only scratch buffer per device for the quantised activations of bg_linear_fp8."""
+    """Scratch for the quantised activations of bg_linear_fp8: one grow-only buffer per device.
+
+    While a CUDA graph is being captured the scratch is allocated per call instead, so that it comes
+    from the graph's private pool and lives as long as the graph: a captured kernel keeps the address
+    it was given, and a shared buffer that later grew (and was replaced) would leave earlier graphs
+    writing into memory the allocator has handed to someone else.  For the same reason a buffer that
+    is outgrown in eager mode is retired, not freed: a graph captured by other means may still name it."""
+    if torch.cuda.is_current_stream_capturing():
+        return torch.empty(max(nbytes, 1), device=device, dtype=torch.uint8)
     buf = _WORKSPACE.get(device)
     if buf is None or buf.numel() < nbytes:
+        if buf is not None:
+            _RETIRED_WORKSPACES.append(buf)
         buf = torch.empty(max(nbytes, 1 << 20), device=device, dtype=torch.uint8)
         _WORKSPACE[device] = buf
     return buf

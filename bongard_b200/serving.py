@@ -203,7 +203,7 @@ class Predictor:
             state_lengths = [state_length, 0]
         for w, offset in inp.offsets.items():
             hp = ops.make_host_plan(lengths, w, group=self.group, owners=owners, state_lengths=state_lengths,
-                                    head_dim=s.head_dim).padded(inp.tokens, inp.plan_tiles)
+                                    head_dim=s.head_dim, pair=False).padded(inp.tokens, inp.plan_tiles)
             ints[offset:offset + hp.packed.size] = hp.packed
         if tail is not None:
             ints[inp.tail:inp.tail + len(tail)] = tail

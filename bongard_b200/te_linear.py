@@ -128,3 +128,18 @@ def enable_te_linear(model, *, mlp=None, attention=None):
 
 def present(backbone):
     return any(isinstance(m, (B200Linear, B200MLP)) for m in backbone.modules())
+
+
+def restore_hf_layout(backbone, state):
+    """Rename the converted projections' weights in `state` (a state_dict of `backbone`) to the Hugging
+    Face module keys (bongard/te_linear.py:144-161): `mlp.gate_up.weight` is split into `mlp.gate_proj.weight`
+    and `mlp.up_proj.weight`, `mlp.down.weight` becomes `mlp.down_proj.weight`; converted attention
+    projections already carry their native keys.  Returns `state`."""
+    for name, module in backbone.named_modules():
+        if isinstance(module, B200MLP):
+            prefix = name + '.'
+            gate, up = state.pop(prefix + 'gate_up.weight').split(module.intermediate_size)
+            state[prefix + 'gate_proj.weight'] = gate
+            state[prefix + 'up_proj.weight'] = up
+            state[prefix + 'down_proj.weight'] = state.pop(prefix + 'down.weight')
+    return state

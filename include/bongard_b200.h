@@ -70,6 +70,15 @@ int bg_rmsnorm(const void* x, int64_t ldx, const void* w, void* out, int64_t ldo
 int bg_add_rmsnorm(const void* y, const void* w_post, void* resid, const void* w_next, void* normed,
                    int64_t rows, int64_t h, float eps, void* stream);
 
+/* The same two calls over an fp32 residual stream (x / resid fp32, h a multiple of 256 up to 4096): the
+ * residual is updated in fp32 and nothing is rounded on the way into it; the normed rows that feed the
+ * GEMMs stay bf16.  This is the arithmetic of the reference run in float32 (HF:61-69 computes the norm in
+ * fp32 for every dtype; HF:496-502 adds the residual in the model's dtype). */
+int bg_rmsnorm_f32(const float* x, int64_t ldx, const void* w, void* out, int64_t ldo, int64_t rows, int64_t h,
+                   float eps, void* stream);
+int bg_add_rmsnorm_f32(const void* y, const void* w_post, float* resid, const void* w_next, void* normed,
+                       int64_t rows, int64_t h, float eps, void* stream);
+
 /* In-place per-head RMSNorm (1 + w gain) and rotate-half RoPE of q [tokens, q_heads, D] and
  * k [tokens, k_heads, D] (token strides ldq / ldk).  positions int32 [tokens]; inv_freq fp32 [D/2].
  * rotate = 0 normalises only; q or k may be NULL.
@@ -92,6 +101,9 @@ int bg_qk_norm_rope_table(void* q, int64_t ldq, int q_heads, void* k, int64_t ld
  * Replaces HF:644-647 T5Gemma2TextScaledWordEmbedding.forward. */
 int bg_embed(const int64_t* ids, const void* table, const void* eoi_embedding, void* out, int64_t rows, int64_t h,
              float scale, int64_t eoi_token, int64_t vocab, void* stream);
+/* bg_embed writing the fp32 residual stream (out fp32, the product is not rounded).  Replaces HF:644-647. */
+int bg_embed_f32(const int64_t* ids, const void* table, const void* eoi_embedding, float* out, int64_t rows, int64_t h,
+                 float scale, int64_t eoi_token, int64_t vocab, void* stream);
 
 /* out[m, n] = a[m, k] . w[n, k]^T on tcgen05 tensor cores, fp32 accumulate, bf16 out.
  * epilogue 0: plain.  epilogue 1 (GeGLU): w is the stacked [gate; up] weight of 2n rows and
@@ -277,6 +289,17 @@ int bg_linear_fp8_static(const void* x, int64_t ldx, const void* wq, int64_t ldw
  * serving path bongard/attention.py:122-169. */
 int bg_attention_tile_rows(int head_dim);
 int bg_varlen_attention(const void* q, int64_t ldq, int64_t hsq, const void* k, const void* v, int64_t ldkv,
+                        int64_t hskv, const void* ck, const void* cv, int64_t ldc, int64_t hsc, void* out,
+                        float* lse, const int32_t* tiles,
+                        int32_t n_tiles, const int32_t* row_lo, const int32_t* row_hi, int64_t tq, int64_t tk,
+                        int64_t ts, int q_heads, int kv_heads, int head_dim, float scale, void* stream);
+
+/* The same attention for head_dim 256 on CTA pairs: a tile record covers bg_attention_pair_tile_rows() = 256
+ * query rows (0 for head sizes without a pair kernel), two CTAs of a cluster take 128 rows each and share the
+ * key stream - each loads half of every K tile and half of every V tile's columns.  Arguments, results and
+ * errors as bg_varlen_attention.  Replaces the same reference code. */
+int bg_attention_pair_tile_rows(int head_dim);
+int bg_varlen_attention_pair(const void* q, int64_t ldq, int64_t hsq, const void* k, const void* v, int64_t ldkv,
                         int64_t hskv, const void* ck, const void* cv, int64_t ldc, int64_t hsc, void* out,
                         float* lse, const int32_t* tiles,
                         int32_t n_tiles, const int32_t* row_lo, const int32_t* row_hi, int64_t tq, int64_t tk,

@@ -35,10 +35,10 @@ def device():
     ops.read_status()
 
 
-def run(q, k, v, lengths, scale, window, cross=None, owners=None, state_lengths=None, lse=False):
+def run(q, k, v, lengths, scale, window, cross=None, owners=None, state_lengths=None, lse=False, pair=None):
     hq, hkv = q.shape[1], k.shape[1]
     plan = ops.make_plan(lengths, window, DEV, group=hq // hkv, owners=owners, state_lengths=state_lengths,
-                         head_dim=q.shape[-1])
+                         head_dim=q.shape[-1], pair=pair)
     cr = None if cross is None else (cross[0].to(DEV), cross[1].to(DEV))
     out = ops.varlen_attention(q.to(DEV), k.to(DEV), v.to(DEV), plan, scale, cr, return_lse=lse)
     if lse:
@@ -95,6 +95,36 @@ def test_decoder_random(d, hq, hkv, window):
     want, _ = om.varlen_attention(q.float(), k.float(), v.float(), lengths, scale, window,
                                   cross=(ck.float(), cv.float()), owners=owners, state_lengths=state_lengths)
     assert_close(out, want)
+
+
+@pytest.mark.parametrize('hq,hkv', [(4, 4), (8, 4), (8, 2), (8, 1)])
+@pytest.mark.parametrize('window', [None, 300])
+def test_cta_pair_and_single_cta_kernels_agree(hq, hkv, window):
+    """head_dim 256 has two forward kernels: 256-row tiles on CTA pairs and 128-row tiles on single CTAs.  A
+    forward-only plan cuts each run into full pair tiles plus, where the rest fits one CTA, a single-CTA tile
+    (pair=None); pair=True / False put everything on one kernel.  All three against the oracle, encoder and
+    decoder, for every GQA group; segment lengths around the 64- and 128-token tile edges and an empty segment."""
+    d = 256
+    lengths = [1, 0, 64, 65, 127, 128, 129, 191, 193, 700, 1300]
+    t = sum(lengths)
+    q, k, v = rnd(t, hq, d, seed=21), rnd(t, hkv, d, seed=22), rnd(t, hkv, d, seed=23)
+    scale = d ** -0.5
+    want, want_lse = om.varlen_attention(q.float(), k.float(), v.float(), lengths, scale, window)
+    for pair in (None, True, False):
+        plan = ops.make_plan(lengths, window, DEV, group=hq // hkv, head_dim=d, pair=pair)
+        assert (plan.n_pair_tiles > 0, plan.n_tiles > 0) == {True: (True, False), False: (False, True), None: (True, True)}[pair]
+        out, lse = run(q, k, v, lengths, scale, window, lse=True, pair=pair)
+        assert_close(out, want)
+        assert_close(lse, want_lse, atol=2e-2, rtol=1e-3)
+    state_lengths, owners = [300, 1, 1000, 0], [0, 0, 0, 1, 2, 2, 2, 2, 0, 3, 3]
+    s = sum(state_lengths)
+    ck, cv = rnd(s, hkv, d, seed=24), rnd(s, hkv, d, seed=25)
+    want, _ = om.varlen_attention(q.float(), k.float(), v.float(), lengths, scale, window,
+                                  cross=(ck.float(), cv.float()), owners=owners, state_lengths=state_lengths)
+    for pair in (None, True, False):
+        assert_close(run(q, k, v, lengths, scale, window, (ck, cv), owners, state_lengths, pair=pair), want)
+    # a backward-capable plan keeps the 128-row tiles its passes are written for
+    assert ops.make_plan(lengths, window, DEV, group=hq // hkv, head_dim=d, backward=True).n_pair_tiles == 0
 
 
 def test_strided_qkv_views():

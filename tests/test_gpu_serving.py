@@ -78,3 +78,34 @@ def test_single_question_subsets(engine):
         alone = wl.Request(request.state, {qid: question})
         got = served.predict(alone)[qid]
         assert float((got - whole[qid]).abs().max()) < 1e-6
+
+
+def test_serving_matches_the_reference_fixture(engine, golden_dir):
+    """Directly against the probabilities the reference's own serving path produced in fp32."""
+    import numpy as np
+
+    gold = np.load(golden_dir / 'tiny_config1.npz')
+    served = Predictor(engine, state_bucket=64, question_bucket=32)
+    got = torch.cat([cat(served.predict(r)) for r in wl.tiny_requests(1)])
+    spread = float(np.abs(gold['probs_serving_fp32'] - gold['probs_serving_bf16']).max())
+    assert float((got - torch.from_numpy(gold['probs_serving_fp32'])).abs().max()) <= 1.25 * max(spread, 1e-3)
+
+
+def test_fp8_graphs_survive_a_larger_bucket():
+    """FP8 linears quantise activations into scratch memory.  A graph captured for a small bucket must still
+    be correct after a larger bucket made the eager scratch buffer grow: replay A, build B, replay A again."""
+    engine = JudgmentEngine(wl.make_weights(wl.TINY, 1), wl.TINY, linears='fp8')
+    requests = wl.tiny_requests(1)
+    small = min(requests, key=lambda r: len(r.state))
+    large = max(requests, key=lambda r: len(r.state))
+    graphed = Predictor(engine, state_bucket=64, question_bucket=32)
+    eager = Predictor(engine, state_bucket=64, question_bucket=32, graphs=False)
+    want = cat(eager.predict(small))
+    first = cat(graphed.predict(small))
+    graphed.predict(large)                                  # larger buckets: more scratch
+    torch.cuda.synchronize()
+    filler = [torch.full((1 << 20,), 7, dtype=torch.uint8, device='cuda') for _ in range(8)]   # reuse any freed block
+    graphed.clear_state_cache()
+    again = cat(graphed.predict(small))
+    assert torch.equal(first, again) and torch.equal(again, want)
+    del filler
