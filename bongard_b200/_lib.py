@@ -23,6 +23,8 @@ SIGNATURES = {
     'bg_add_rmsnorm': ([P, P, P, P, P, I64, I64, F32, P], INT),
     'bg_rmsnorm_f32': ([P, I64, P, P, I64, I64, I64, F32, P], INT),
     'bg_add_rmsnorm_f32': ([P, P, P, P, P, I64, I64, F32, P], INT),
+    'bg_add_rmsnorm_f32y': ([P, P, P, P, P, I64, I64, F32, P], INT),
+    'bg_gemm_bf16_f32out': ([P, I64, P, I64, P, I64, I64, I64, P], INT),
     'bg_embed_f32': ([P, P, P, P, I64, I64, F32, I64, I64, P], INT),
     'bg_qk_norm_rope': ([P, I64, INT, P, I64, INT, P, P, P, P, I64, INT, F32, INT, P], INT),
     'bg_qk_norm_rope_table': ([P, I64, INT, P, I64, INT, P, P, P, P, I64, INT, F32, P], INT),

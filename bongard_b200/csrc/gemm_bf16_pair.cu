@@ -596,6 +596,35 @@ extern "C" int bg_gemm_bf16_splitk(const void* a, int64_t lda, const void* w, in
     return BG_OK;
 }
 
+// out[m, n] = a . w^T as UNROUNDED fp32 (contiguous [m, n]): the plain GEMM with the accumulators written as they
+// are.  Feeds the post-norm of a layer whose residual stream is kept in fp32.
+extern "C" int bg_gemm_bf16_f32out(const void* a, int64_t lda, const void* w, int64_t ldw, float* out, int64_t m,
+                                   int64_t n, int64_t k, void* stream) {
+    if (m < 0 || n <= 0 || k <= 0 || n % 8) {
+        bg_set_error("bg_gemm_bf16_f32out: bad shape (n must be a multiple of 8)");
+        return BG_ERR_SHAPE;
+    }
+    if (m == 0) return BG_OK;
+    if ((k % 8) || (lda % 8) || (ldw % 8) ||
+        ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) & 15)) {
+        bg_set_error("bg_gemm_bf16_f32out: pointers must be 16-byte aligned, k and leading dimensions multiples of 8");
+        return BG_ERR_ALIGN;
+    }
+    CUtensorMap map_a, map_w;
+    uint64_t dims_a[2] = {(uint64_t)k, (uint64_t)m}, str_a[1] = {(uint64_t)lda * 2};
+    uint64_t dims_w[2] = {(uint64_t)k, (uint64_t)n}, str_w[1] = {(uint64_t)ldw * 2};
+    uint32_t box_a[2] = {BK, BM}, box_w[2] = {BK, 128};
+    int rc = bg_make_tensor_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a, dims_a, str_a, box_a,
+                                CU_TENSOR_MAP_SWIZZLE_128B);
+    if (!rc) rc = bg_make_tensor_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, dims_w, str_w, box_w,
+                                     CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    PairParams p = {};
+    p.split_k = 1;
+    p.partial = out;             // one K slice: its "partial" tile is the result
+    return pair_launch(p, map_a, map_w, nullptr, n, m, n, k, 3, static_cast<cudaStream_t>(stream));
+}
+
 // out[m, n] = sum_k at[k, m] * wt[k, n]: both operands with the contraction as the row index.  This is the
 // weight gradient dW = dy^T x taken straight from dy [tokens, out features] and x [tokens, in features].
 extern "C" int bg_gemm_bf16_tn(const void* at, int64_t ldat, const void* wt, int64_t ldwt, void* out, int64_t ldo,

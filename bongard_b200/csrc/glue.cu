@@ -199,7 +199,8 @@ constexpr int ROW_WARPS = 4;    // warps per block of the row-per-warp kernels
 template <int CH, typename XT>
 __global__ void __launch_bounds__(ROW_WARPS * 32)
 rmsnorm_rows_kernel(const XT* __restrict__ x, int64_t ldx, const __nv_bfloat16* __restrict__ w,
-                    __nv_bfloat16* __restrict__ out, int64_t ldo, int64_t rows, float eps) {
+                    __nv_bfloat16* __restrict__ out, int64_t ldo, int64_t rows, float eps,
+                    uint8_t* __restrict__ out_q, uint8_t* __restrict__ out_sf) {
     pdl_wait();
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
@@ -225,7 +226,13 @@ rmsnorm_rows_kernel(const XT* __restrict__ x, int64_t ldx, const __nv_bfloat16* 
             unpack8(__ldg(reinterpret_cast<const uint4*>(w + c * 256 + lane * 8)), g);
 #pragma unroll
             for (int i = 0; i < 8; ++i) f[i] = f[i] * r * (1.f + g[i]);
-            *reinterpret_cast<uint4*>(out + row * ldo + c * 256 + lane * 8) = pack8(f);
+            if (out_q == nullptr) {
+                *reinterpret_cast<uint4*>(out + row * ldo + c * 256 + lane * 8) = pack8(f);
+            } else {        // MXFP8 of the bf16-rounded row: four neighbouring lanes share a 32-element block
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[i] = round_bf16(f[i]);
+                store_mxfp8(f, true, out_q, out_sf, row, c * 256 + lane * 8, CH * 256);
+            }
         }
     }
 }
@@ -233,11 +240,12 @@ rmsnorm_rows_kernel(const XT* __restrict__ x, int64_t ldx, const __nv_bfloat16* 
 // resid <- resid + post_norm(y);  normed <- pre_norm(resid)   (see add_rmsnorm_kernel for the contract).
 // RT = __nv_bfloat16: post-norm result and updated residual are each rounded to bf16, as the module chain does;
 // RT = float: the residual stream stays in fp32 and nothing is rounded on the way into it.
-template <int CH, typename RT>
+template <int CH, typename RT, typename YT>
 __global__ void __launch_bounds__(ROW_WARPS * 32)
-add_rmsnorm_rows_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ w_post,
+add_rmsnorm_rows_kernel(const YT* __restrict__ y, const __nv_bfloat16* __restrict__ w_post,
                         RT* __restrict__ resid, const __nv_bfloat16* __restrict__ w_next,
-                        __nv_bfloat16* __restrict__ normed, int64_t rows, float eps) {
+                        __nv_bfloat16* __restrict__ normed, int64_t rows, float eps,
+                        uint8_t* __restrict__ normed_q, uint8_t* __restrict__ normed_sf) {
     pdl_wait();
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
@@ -245,7 +253,7 @@ add_rmsnorm_rows_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16
     constexpr int H = CH * 256;
     constexpr float inv_h = 1.f / float(H);
     for (int64_t row = int64_t(blockIdx.x) * ROW_WARPS + (threadIdx.x >> 5); row < rows; row += stride) {
-        Chunk8<__nv_bfloat16> yv[CH];
+        Chunk8<YT> yv[CH];
         Chunk8<RT> xv[CH];
 #pragma unroll
         for (int c = 0; c < CH; ++c) yv[c].load_streaming(y + row * H + c * 256 + lane * 8);
@@ -284,7 +292,13 @@ add_rmsnorm_rows_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16
             unpack8(__ldg(reinterpret_cast<const uint4*>(w_next + c * 256 + lane * 8)), g);
 #pragma unroll
             for (int i = 0; i < 8; ++i) x[i] = x[i] * r * (1.f + g[i]);
-            *reinterpret_cast<uint4*>(normed + row * H + c * 256 + lane * 8) = pack8(x);
+            if (normed_q == nullptr) {
+                *reinterpret_cast<uint4*>(normed + row * H + c * 256 + lane * 8) = pack8(x);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) x[i] = round_bf16(x[i]);
+                store_mxfp8(x, true, normed_q, normed_sf, row, c * 256 + lane * 8, H);
+            }
         }
     }
 }
@@ -582,10 +596,10 @@ unsigned row_grid(int64_t rows) {
 // Row-per-warp RMSNorm for hidden sizes 256 * {1..16}; false when the size is not covered.
 template <typename XT>
 bool launch_rmsnorm_rows(const XT* x, int64_t ldx, const __nv_bfloat16* w, __nv_bfloat16* out, int64_t ldo, int64_t rows,
-                         int64_t h, float eps, cudaStream_t s) {
+                         int64_t h, float eps, cudaStream_t s, uint8_t* out_q = nullptr, uint8_t* out_sf = nullptr) {
     if (h % 256 || h > 4096) return false;
     const dim3 grid(row_grid(rows)), block(ROW_WARPS * 32);
-#define BG_ROWS_CASE(CH) case CH: launch_kernel(rmsnorm_rows_kernel<CH, XT>, grid, block, 0, s, 0, x, ldx, w, out, ldo, rows, eps); return true;
+#define BG_ROWS_CASE(CH) case CH: launch_kernel(rmsnorm_rows_kernel<CH, XT>, grid, block, 0, s, 0, x, ldx, w, out, ldo, rows, eps, out_q, out_sf); return true;
     switch (int(h / 256)) {
         BG_ROWS_CASE(1) BG_ROWS_CASE(2) BG_ROWS_CASE(3) BG_ROWS_CASE(4) BG_ROWS_CASE(5) BG_ROWS_CASE(6) BG_ROWS_CASE(7) BG_ROWS_CASE(8)
         BG_ROWS_CASE(9) BG_ROWS_CASE(10) BG_ROWS_CASE(11) BG_ROWS_CASE(12) BG_ROWS_CASE(13) BG_ROWS_CASE(14) BG_ROWS_CASE(15) BG_ROWS_CASE(16)
@@ -594,12 +608,13 @@ bool launch_rmsnorm_rows(const XT* x, int64_t ldx, const __nv_bfloat16* w, __nv_
     return false;
 }
 
-template <typename RT>
-bool launch_add_rmsnorm_rows(const __nv_bfloat16* y, const __nv_bfloat16* w_post, RT* resid, const __nv_bfloat16* w_next,
-                             __nv_bfloat16* normed, int64_t rows, int64_t h, float eps, cudaStream_t s) {
-    if (h % 256 || h > 4096) return false;
+template <typename RT, typename YT>
+bool launch_add_rmsnorm_rows(const YT* y, const __nv_bfloat16* w_post, RT* resid, const __nv_bfloat16* w_next,
+                             __nv_bfloat16* normed, int64_t rows, int64_t h, float eps, cudaStream_t s,
+                             uint8_t* normed_q = nullptr, uint8_t* normed_sf = nullptr) {
+    if (h % 256 || h > 4096 || (sizeof(YT) == 4 && h > 3072)) return false;
     const dim3 grid(row_grid(rows)), block(ROW_WARPS * 32);
-#define BG_ROWS_CASE(CH) case CH: launch_kernel(add_rmsnorm_rows_kernel<CH, RT>, grid, block, 0, s, 0, y, w_post, resid, w_next, normed, rows, eps); return true;
+#define BG_ROWS_CASE(CH) case CH: launch_kernel(add_rmsnorm_rows_kernel<CH, RT, YT>, grid, block, 0, s, 0, y, w_post, resid, w_next, normed, rows, eps, normed_q, normed_sf); return true;
     switch (int(h / 256)) {
         BG_ROWS_CASE(1) BG_ROWS_CASE(2) BG_ROWS_CASE(3) BG_ROWS_CASE(4) BG_ROWS_CASE(5) BG_ROWS_CASE(6) BG_ROWS_CASE(7) BG_ROWS_CASE(8)
         BG_ROWS_CASE(9) BG_ROWS_CASE(10) BG_ROWS_CASE(11) BG_ROWS_CASE(12) BG_ROWS_CASE(13) BG_ROWS_CASE(14) BG_ROWS_CASE(15) BG_ROWS_CASE(16)
@@ -648,6 +663,10 @@ int bg_rmsnorm_mxfp8(const void* x, int64_t ldx, const void* w, void* out_q, voi
         return BG_ERR_SHAPE;
     }
     if (rows == 0) return BG_OK;
+    if (launch_rmsnorm_rows(static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(w),
+                            (__nv_bfloat16*)nullptr, (int64_t)0, rows, h, eps, static_cast<cudaStream_t>(stream),
+                            static_cast<uint8_t*>(out_q), static_cast<uint8_t*>(out_scales)))
+        return check_launch("bg_rmsnorm_mxfp8");
     launch_kernel(rmsnorm_kernel, dim3((unsigned)rows), dim3(row_threads(h)), 0, static_cast<cudaStream_t>(stream), 0,
                   static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(w),
                   (__nv_bfloat16*)nullptr, (int64_t)0, (int)h, eps, static_cast<uint8_t*>(out_q),
@@ -688,6 +707,19 @@ int bg_add_rmsnorm_f32(const void* y, const void* w_post, float* resid, const vo
     return check_launch("bg_add_rmsnorm_f32");
 }
 
+// The same with y in fp32 as well (the unrounded output of bg_gemm_bf16_f32out); h a multiple of 256 up to 3072.
+int bg_add_rmsnorm_f32y(const float* y, const void* w_post, float* resid, const void* w_next, void* normed, int64_t rows,
+                        int64_t h, float eps, void* stream) {
+    if (rows < 0 || h <= 0 || h % 256 || h > 3072) {
+        bg_set_error("bg_add_rmsnorm_f32y: hidden size must be a multiple of 256 up to 3072 (got %lld)", (long long)h);
+        return BG_ERR_SHAPE;
+    }
+    if (rows == 0) return BG_OK;
+    launch_add_rmsnorm_rows(y, static_cast<const __nv_bfloat16*>(w_post), resid, static_cast<const __nv_bfloat16*>(w_next),
+                            static_cast<__nv_bfloat16*>(normed), rows, h, eps, static_cast<cudaStream_t>(stream));
+    return check_launch("bg_add_rmsnorm_f32y");
+}
+
 int bg_add_rmsnorm_mxfp8(const void* y, const void* w_post, void* resid, const void* w_next, void* normed_q,
                          void* normed_scales, int64_t rows, int64_t h, float eps, void* stream) {
     if (rows < 0 || h <= 0 || h % 128 || h > 8192 || w_next == nullptr) {
@@ -695,6 +727,11 @@ int bg_add_rmsnorm_mxfp8(const void* y, const void* w_post, void* resid, const v
         return BG_ERR_SHAPE;
     }
     if (rows == 0) return BG_OK;
+    if (launch_add_rmsnorm_rows(static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(w_post),
+                                static_cast<__nv_bfloat16*>(resid), static_cast<const __nv_bfloat16*>(w_next),
+                                (__nv_bfloat16*)nullptr, rows, h, eps, static_cast<cudaStream_t>(stream),
+                                static_cast<uint8_t*>(normed_q), static_cast<uint8_t*>(normed_scales)))
+        return check_launch("bg_add_rmsnorm_mxfp8");
     launch_kernel(add_rmsnorm_kernel, dim3((unsigned)rows), dim3(row_threads(h)), 0, static_cast<cudaStream_t>(stream), 0,
                   static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(w_post),
                   static_cast<__nv_bfloat16*>(resid), static_cast<const __nv_bfloat16*>(w_next),

@@ -87,7 +87,7 @@ def attention(args, flush):
     positions = torch.cat([torch.arange(n, dtype=torch.int32) for n in lengths]).to(DEV)
     ops.qk_norm_rope_(q, k, gain, gain, positions, ops.inv_freq(d, theta, DEV))
     plan = ops.make_plan(lengths, window, DEV, group=hq // hkv, head_dim=d, backward=args.backward,
-                         pair=False if args.no_pair else None)
+                         pair=False if args.no_pair else (True if args.all_pair else None))
     ms = timed(lambda: ops.varlen_attention(q, k, v, plan, d ** -0.5), args.iters, args.warmup, flush)
     flops = 4 * d * hq * plan.pairs
     out = [dict(op=f'varlen_attention_{args.variant}', tokens=t, sequences=len(lengths), tiles=plan.n_tiles,
@@ -380,6 +380,7 @@ def main():
     ap.add_argument('--fp8', action='store_true', help='mlp: also time the E4M3 block-scaled path')
     ap.add_argument('--flush', action='store_true', help='write a 256 MB buffer between launches')
     ap.add_argument('--no-pair', action='store_true', help='attention: 128-row tiles on single CTAs instead of CTA pairs')
+    ap.add_argument('--all-pair', action='store_true', help='attention: every run on CTA pairs, also the short rests')
     args = ap.parse_args()
     ops.device_check()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV) if args.flush else None

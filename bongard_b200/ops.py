@@ -100,15 +100,19 @@ def add_rmsnorm_(y, w_post, resid, w_next=None, eps=1e-6):
     (nothing rounded on the way into the residual stream)."""
     lib = _lib.load()
     fp32 = resid.dtype == torch.float32
-    _need(y, 'y'), _need(resid, 'resid', resid.dtype if fp32 else BF16)
+    fp32_y = y.dtype == torch.float32
+    if fp32_y and not fp32:
+        raise ValueError('an fp32 y needs an fp32 residual stream')
+    _need(y, 'y', y.dtype if fp32_y else BF16), _need(resid, 'resid', resid.dtype if fp32 else BF16)
     if not (y.is_contiguous() and resid.is_contiguous()) or y.shape != resid.shape:
         raise ValueError('y and resid must be contiguous and of equal shape')
     h = y.shape[-1]
     if fp32 and h % 256:
         raise ValueError('an fp32 residual stream needs a hidden size that is a multiple of 256')
     rows = y.numel() // h
-    normed = torch.empty_like(y) if w_next is not None else None
-    entry, name = (lib.bg_add_rmsnorm_f32, 'bg_add_rmsnorm_f32') if fp32 else (lib.bg_add_rmsnorm, 'bg_add_rmsnorm')
+    normed = torch.empty(y.shape, device=y.device, dtype=BF16) if w_next is not None else None
+    entry, name = ((lib.bg_add_rmsnorm_f32y, 'bg_add_rmsnorm_f32y') if fp32_y else
+                   (lib.bg_add_rmsnorm_f32, 'bg_add_rmsnorm_f32') if fp32 else (lib.bg_add_rmsnorm, 'bg_add_rmsnorm'))
     _lib.check(entry(_ptr(y), _ptr(_need(w_post, 'w_post')), _ptr(resid), _ptr(w_next), _ptr(normed),
                      rows, h, eps, _stream()), name)
     return normed
@@ -214,6 +218,24 @@ def linear(x, weight, out=None, *, few_rows=False):
 
 
 _ROPE_TABLES = {}
+
+
+def linear_f32out(x, weight):
+    """F.linear(x, weight) with the fp32 accumulators returned unrounded (fp32 [..., N])."""
+    lib = _lib.load()
+    flat, m, k, ldx = _rows(x, 'x')
+    _need(weight, 'weight')
+    n = weight.shape[0]
+    if weight.shape[1] != k or weight.stride(1) != 1:
+        raise ValueError('weight must be [N, K] with a contiguous last dimension')
+    out = torch.empty((m, n), device=x.device, dtype=torch.float32)
+    timer = GEMM_TIMER
+    begin = timer.start() if timer is not None else None
+    _lib.check(lib.bg_gemm_bf16_f32out(_ptr(flat), ldx, _ptr(weight), weight.stride(0), _ptr(out), m, n, k, _stream()),
+               'bg_gemm_bf16_f32out')
+    if timer is not None:
+        timer.stop(begin, 2 * m * n * k)
+    return out.view(*x.shape[:-1], n)
 
 
 def rope_table(head_dim, theta, rows, device):
@@ -650,7 +672,7 @@ class HostPlan:
         return plan
 
 
-PAIR_ATTENTION = True    # head_dim 256, forward-only plans: 256-row tiles served by CTA pairs (off: 128-row tiles)
+PAIR_ATTENTION = False   # head_dim 256, forward-only plans: also cut runs into 256-row tiles for the CTA-pair kernel
 
 
 def tile_rows(head_dim, pair=False):
@@ -796,7 +818,7 @@ def make_host_plan(lengths, window, *, group, owners=None, state_lengths=None, h
         tqp, tqs = pair_rows // group, single_rows // group
         n = run[:, 1] - run[:, 0]
         rest = n % tqp
-        pair_tokens = n - np.where(rest > tqs if pair is None else False, 0, rest) if pair is None else n
+        pair_tokens = np.where(rest > tqs, n, n - rest) if pair is None else n      # pair=True: everything on pairs
         pair_part = np.stack([run[:, 0], run[:, 0] + pair_tokens, run[:, 2], run[:, 3]], axis=1)
         single_part = np.stack([run[:, 0] + pair_tokens, run[:, 1], run[:, 2], run[:, 3]], axis=1)
         pair_tiles, tiles = tile(pair_rows, pair_part), tile(single_rows, single_part)

@@ -78,6 +78,9 @@ int bg_rmsnorm_f32(const float* x, int64_t ldx, const void* w, void* out, int64_
                    float eps, void* stream);
 int bg_add_rmsnorm_f32(const void* y, const void* w_post, float* resid, const void* w_next, void* normed,
                        int64_t rows, int64_t h, float eps, void* stream);
+/* ... and with y in fp32 too: the unrounded projection from bg_gemm_bf16_f32out (h up to 3072). */
+int bg_add_rmsnorm_f32y(const float* y, const void* w_post, float* resid, const void* w_next, void* normed,
+                        int64_t rows, int64_t h, float eps, void* stream);
 
 /* In-place per-head RMSNorm (1 + w gain) and rotate-half RoPE of q [tokens, q_heads, D] and
  * k [tokens, k_heads, D] (token strides ldq / ldk).  positions int32 [tokens]; inv_freq fp32 [D/2].
@@ -113,6 +116,12 @@ int bg_embed_f32(const int64_t* ids, const void* table, const void* eoi_embeddin
  * bongard/te_linear.py:98-103 TEMLP.forward / HF:87-91 T5Gemma2MLP.forward. */
 int bg_gemm_bf16(const void* a, int64_t lda, const void* w, int64_t ldw, void* out, int64_t ldo, int64_t m,
                  int64_t n, int64_t k, int epilogue, void* stream);
+
+/* The plain GEMM with its fp32 accumulators written unrounded: out fp32, contiguous [m, n].  For the output and
+ * down projections of a layer whose residual stream is fp32 (the post-norm then reads what the contraction
+ * produced, not its bf16 rounding).  Replaces F.linear as bg_gemm_bf16 does. */
+int bg_gemm_bf16_f32out(const void* a, int64_t lda, const void* w, int64_t ldw, float* out, int64_t m, int64_t n,
+                        int64_t k, void* stream);
 
 /* The q|k|v projection with QK-norm + RoPE fused into its epilogue: out[m, q_dim + 2 kv_dim] =
  * a[m, k] . w^T where w stacks the q, k and v projection weights; every query and key head gets the

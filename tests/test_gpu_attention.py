@@ -99,12 +99,15 @@ def test_decoder_random(d, hq, hkv, window):
 
 @pytest.mark.parametrize('hq,hkv', [(4, 4), (8, 4), (8, 2), (8, 1)])
 @pytest.mark.parametrize('window', [None, 300])
-def test_cta_pair_and_single_cta_kernels_agree(hq, hkv, window):
-    """head_dim 256 has two forward kernels: 256-row tiles on CTA pairs and 128-row tiles on single CTAs.  A
-    forward-only plan cuts each run into full pair tiles plus, where the rest fits one CTA, a single-CTA tile
-    (pair=None); pair=True / False put everything on one kernel.  All three against the oracle, encoder and
-    decoder, for every GQA group; segment lengths around the 64- and 128-token tile edges and an empty segment."""
+def test_cta_pair_and_single_cta_kernels_agree(hq, hkv, window, monkeypatch):
+    """head_dim 256 has two forward kernels: 128-row tiles on single CTAs (the default) and 256-row tiles on
+    CTA pairs (opt-in: pair=True, or ops.PAIR_ATTENTION, under which a forward-only plan cuts each run into full
+    pair tiles plus, where the rest fits one CTA, a single-CTA tile).  All three tilings against the oracle,
+    encoder and decoder, for every GQA group; segment lengths around the 64- and 128-token tile edges and an
+    empty segment."""
     d = 256
+    assert ops.make_plan([300], window, DEV, group=hq // hkv, head_dim=d).n_pair_tiles == 0    # single CTAs by default
+    monkeypatch.setattr(ops, 'PAIR_ATTENTION', True)       # pair=None then cuts runs between the two kernels
     lengths = [1, 0, 64, 65, 127, 128, 129, 191, 193, 700, 1300]
     t = sum(lengths)
     q, k, v = rnd(t, hq, d, seed=21), rnd(t, hkv, d, seed=22), rnd(t, hkv, d, seed=23)

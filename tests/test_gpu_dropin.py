@@ -43,7 +43,7 @@ def test_module_substitution_matches_reference_fixture(golden_dir, tiny):
     spread = float(np.abs(gold['probs_packed_fp32'] - gold['probs_packed_bf16']).max())
     err = float((probs - torch.from_numpy(gold['probs_packed_fp32'])).abs().max())
     assert err <= max(spread, 1e-3) * 1.25, (err, spread)
-    engine = probs_of(JudgmentEngine(weights, wl.TINY).forward_packed(requests, 8))
+    engine = probs_of(JudgmentEngine(weights, wl.TINY, residual='bf16').forward_packed(requests, 8))
     assert float((probs - engine).abs().max()) < 2e-3
 
 
@@ -297,8 +297,9 @@ def test_enable_surfaces_and_fp8_end_to_end(tiny):
     assert enable_float8(backbone, 'block128') == 2 * 2 * 7
     install_b200_inference(backbone, linears='fp8')
     p_mod = probs_of(PackedJudge(backbone, weights).forward_packed(requests, 8))
-    p_eng = probs_of(JudgmentEngine(weights, wl.TINY, linears='fp8').forward_packed(requests, 8))
-    p_bf16 = probs_of(JudgmentEngine(weights, wl.TINY).forward_packed(requests, 8))
+    # the substituted modules run the reference's bf16 chain: compare with the engine in the same mode
+    p_eng = probs_of(JudgmentEngine(weights, wl.TINY, linears='fp8', residual='bf16').forward_packed(requests, 8))
+    p_bf16 = probs_of(JudgmentEngine(weights, wl.TINY, residual='bf16').forward_packed(requests, 8))
     assert float((p_mod - p_eng).abs().max()) < 5e-3
     assert float((p_eng - p_bf16).abs().max()) < 3e-2
     with pytest.raises(ValueError):
