@@ -555,16 +555,7 @@ def strong_scaling(args, engine, shape, device, world, rank, full_answers, barri
     if rank != 0:
         return None
     # put the gathered answers back into request order and compare with the whole-batch run
-    sizes = [[len(q.candidate_positions) for q in r.questions.values()] for r in requests]
-    flat = gathered.cpu()
-    restored = [None] * len(requests)
-    for r, shard in enumerate(shards):
-        cursor = r * per_rank
-        for index in shard:
-            n = sum(sizes[index])
-            restored[index] = flat[cursor:cursor + n]
-            cursor += n
-    restored = torch.cat(restored)
+    restored = wl.reassemble_answers(gathered.cpu(), shards, requests, per_rank)
     diff = float((restored - full_answers).abs().max()) if restored.numel() == full_answers.numel() else None
     each = each.tolist()
     questions = sum(len(r.questions) for r in requests)

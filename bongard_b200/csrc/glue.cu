@@ -307,8 +307,32 @@ add_rmsnorm_rows_kernel(const YT* __restrict__ y, const __nv_bfloat16* __restric
 // per head an fp32 RMSNorm over head_dim with (1 + w) gain, then rotate-half RoPE with the
 // angle position * inv_freq[i mod D/2] (bongard/attention.py:172-180; the fused form follows
 // bongard/qk_norm_rope.metal:4-33: partner j = (i + D/2) mod D, sign - for i < D/2).
-// Lane l owns elements [l*D/32, (l+1)*D/32): its rotation partner lives in lane l ^ 16.
+// Lane l owns HE = D/64 elements of the FIRST half, [l*HE, (l+1)*HE), and their rotation partners in the
+// second half, [D/2 + l*HE, ...): both members of a pair sit in one lane, so the rotation needs no shuffle
+// and every angle is computed once (not once per half).  Heads are taken four at a time: the eight loads
+// of a batch are issued before the first is used, which is what keeps enough bytes in flight.
 // rotate == 0 leaves out the rotation (decoder state keys: bongard/model.py:135-139).
+template <int HE>
+struct HalfVec;          // HE bf16 values as one load
+template <> struct HalfVec<4> { using T = uint2; };
+template <> struct HalfVec<2> { using T = uint32_t; };
+template <> struct HalfVec<1> { using T = uint16_t; };
+
+template <int HE>
+__device__ __forceinline__ void unpack_half(const typename HalfVec<HE>::T& raw, float* f) {
+    const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+    for (int e = 0; e < HE; ++e) f[e] = __bfloat162float(h[e]);
+}
+template <int HE>
+__device__ __forceinline__ typename HalfVec<HE>::T pack_half(const float* f) {
+    typename HalfVec<HE>::T raw;
+    __nv_bfloat16* h = reinterpret_cast<__nv_bfloat16*>(&raw);
+#pragma unroll
+    for (int e = 0; e < HE; ++e) h[e] = __float2bfloat16_rn(f[e]);
+    return raw;
+}
+
 template <int D>
 __global__ void qk_norm_rope_kernel(__nv_bfloat16* __restrict__ q, int64_t ldq, int q_heads,
                                     __nv_bfloat16* __restrict__ k, int64_t ldk, int k_heads,
@@ -319,64 +343,82 @@ __global__ void qk_norm_rope_kernel(__nv_bfloat16* __restrict__ q, int64_t ldq, 
                                     int rotate) {
     pdl_wait();
     pdl_launch_dependents();
-    constexpr int E = D / 32;  // elements per lane
+    constexpr int HE = D / 64;     // elements per lane and half
+    constexpr int NB = 4;          // heads per batch
+    using Vec = typename HalfVec<HE>::T;
     const int lane = threadIdx.x & 31;
     const int64_t token = int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (token >= tokens) return;
-    float cs[E], sn[E];
+    if (k == nullptr) k_heads = 0;
+    const int first = lane * HE;           // this lane's columns: [first, first + HE) and D/2 + the same
+    float cs[HE], sn[HE], cs2[HE], sn2[HE];     // angles of the first-half columns and of their partners
     if (rotate && cos_table != nullptr) {
         // caller-supplied tables [tokens, D] (the rotary module's cos/sin, cat(freqs, freqs))
 #pragma unroll
-        for (int e = 0; e < E; ++e) {
-            cs[e] = __bfloat162float(cos_table[token * D + lane * E + e]);
-            sn[e] = __bfloat162float(sin_table[token * D + lane * E + e]);
+        for (int e = 0; e < HE; ++e) {
+            cs[e] = __bfloat162float(cos_table[token * D + first + e]);
+            sn[e] = __bfloat162float(sin_table[token * D + first + e]);
+            cs2[e] = __bfloat162float(cos_table[token * D + D / 2 + first + e]);
+            sn2[e] = __bfloat162float(sin_table[token * D + D / 2 + first + e]);
         }
     } else if (rotate) {
         const float pos = float(positions[token]);
 #pragma unroll
-        for (int e = 0; e < E; ++e) {
-            const int i = (lane * E + e) & (D / 2 - 1);
-            sincosf(pos * inv_freq[i], &sn[e], &cs[e]);
+        for (int e = 0; e < HE; ++e) {
+            sincosf(pos * inv_freq[first + e], &sn[e], &cs[e]);
+            cs2[e] = cs[e];
+            sn2[e] = sn[e];
         }
     }
-    const float sign = lane < 16 ? -1.f : 1.f;
-    for (int head = 0; head < q_heads + k_heads; ++head) {
-        const bool is_q = head < q_heads;
-        if (!is_q && k == nullptr) break;
-        __nv_bfloat16* p = is_q ? q + token * ldq + head * D : k + token * ldk + (head - q_heads) * D;
-        const __nv_bfloat16* w = is_q ? qw : kw;
-        p += lane * E;
-        float f[E], g[E];
-        if constexpr (E == 8) {
-            unpack8(*reinterpret_cast<const uint4*>(p), f);
-            unpack8(*reinterpret_cast<const uint4*>(w + lane * E), g);
-        } else {
+    // gains of this lane's columns (q and k), as 1 + w
+    float gq[2][HE], gk[2][HE];
 #pragma unroll
-            for (int e = 0; e < E; ++e) {
-                f[e] = __bfloat162float(p[e]);
-                g[e] = __bfloat162float(w[lane * E + e]);
+    for (int half = 0; half < 2; ++half)
+#pragma unroll
+        for (int e = 0; e < HE; ++e) {
+            gq[half][e] = q_heads ? 1.f + __bfloat162float(qw[half * (D / 2) + first + e]) : 1.f;
+            gk[half][e] = k_heads ? 1.f + __bfloat162float(kw[half * (D / 2) + first + e]) : 1.f;
+        }
+    const int heads = q_heads + k_heads;
+    for (int base = 0; base < heads; base += NB) {
+        Vec raw[NB][2];
+        __nv_bfloat16* ptr[NB];
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+            const int head = base + b;
+            if (head < heads) {
+                ptr[b] = (head < q_heads ? q + token * ldq + head * D : k + token * ldk + (head - q_heads) * D) + first;
+                raw[b][0] = *reinterpret_cast<const Vec*>(ptr[b]);
+                raw[b][1] = *reinterpret_cast<const Vec*>(ptr[b] + D / 2);
             }
         }
-        float ss = 0.f;
 #pragma unroll
-        for (int e = 0; e < E; ++e) ss += f[e] * f[e];
-        const float r = rsqrtf(warp_sum(ss) / float(D) + eps);
+        for (int b = 0; b < NB; ++b) {
+            const int head = base + b;
+            if (head >= heads) break;
+            const bool is_q = head < q_heads;
+            float x1[HE], x2[HE];
+            unpack_half<HE>(raw[b][0], x1);
+            unpack_half<HE>(raw[b][1], x2);
+            float ss = 0.f;
 #pragma unroll
-        for (int e = 0; e < E; ++e) f[e] = f[e] * r * (1.f + g[e]);
-        if (rotate) {
+            for (int e = 0; e < HE; ++e) ss += x1[e] * x1[e] + x2[e] * x2[e];
+            const float r = rsqrtf(warp_sum(ss) / float(D) + eps);
 #pragma unroll
-            for (int e = 0; e < E; ++e) {
-                const float other = __shfl_xor_sync(0xffffffffu, f[e], 16);
-                g[e] = f[e] * cs[e] + sign * other * sn[e];
+            for (int e = 0; e < HE; ++e) {
+                x1[e] = x1[e] * r * (is_q ? gq[0][e] : gk[0][e]);
+                x2[e] = x2[e] * r * (is_q ? gq[1][e] : gk[1][e]);
             }
+            if (rotate) {
 #pragma unroll
-            for (int e = 0; e < E; ++e) f[e] = g[e];
-        }
-        if constexpr (E == 8) {
-            *reinterpret_cast<uint4*>(p) = pack8(f);
-        } else {
-#pragma unroll
-            for (int e = 0; e < E; ++e) p[e] = __float2bfloat16_rn(f[e]);
+                for (int e = 0; e < HE; ++e) {
+                    const float a = x1[e], c = x2[e];
+                    x1[e] = a * cs[e] - c * sn[e];
+                    x2[e] = c * cs2[e] + a * sn2[e];
+                }
+            }
+            *reinterpret_cast<Vec*>(ptr[b]) = pack_half<HE>(x1);
+            *reinterpret_cast<Vec*>(ptr[b] + D / 2) = pack_half<HE>(x2);
         }
     }
 }

@@ -16,9 +16,22 @@ from . import ops
 from .te_linear import B200Linear
 
 RECIPES = ('block128',)
+# the reference's recipe names (bongard/float8_training.py:9): dynamic amax scaling per tensor / per row
+REFERENCE_RECIPES = ('tensorwise', 'rowwise', 'rowwise_with_gw_hp')
 
 
 def enable_float8(model, recipe='block128', *, emulate=False):
+    """Convert every eligible text linear to the FP8 recipe and return the count (bongard/float8_training.py:27-65).
+
+    Eligible: bias-free `nn.Linear` modules of the two text stacks whose dimensions are multiples of 128 (the
+    reference asks for multiples of 16 and pads; 128 is the block this recipe scales by - every projection of the
+    4B and tiny shapes qualifies).  The reference's own recipe names are refused with a message naming the
+    replacement: its scaling granularities (one scale per tensor or per row) are coarser than 'block128' and
+    there is no kernel for them here."""
+    if recipe in REFERENCE_RECIPES:
+        raise ValueError(f"recipe {recipe!r} (torchao dynamic scaling per tensor / per row) is served here by 'block128': the "
+                         "same dynamic 448 / amax rule over 1 x 128 activation blocks and 128 x 128 weight tiles; pass "
+                         "recipe='block128'")
     if recipe not in RECIPES:
         raise ValueError(f'fp8 must be one of {RECIPES}')
     if emulate:

@@ -185,6 +185,14 @@ def glue(args, flush):
     out.append(dict(op='rmsnorm', tokens=t, ms=ms, gbs=2 * t * h * 2 / ms / 1e6))
     ms = timed(lambda: ops.add_rmsnorm_(y, w, x, w), args.iters, args.warmup, flush)
     out.append(dict(op='add_rmsnorm', tokens=t, ms=ms, gbs=4 * t * h * 2 / ms / 1e6))
+    # the fp32 residual stream: fp32 x read by the norm; y and resid fp32 in the update (the engine's default)
+    x32, y32 = x.float(), y.float()
+    ms = timed(lambda: ops.rmsnorm(x32, w), args.iters, args.warmup, flush)
+    out.append(dict(op='rmsnorm_fp32_input', tokens=t, ms=ms, gbs=t * h * (4 + 2) / ms / 1e6))
+    ms = timed(lambda: ops.add_rmsnorm_(y, w, x32, w), args.iters, args.warmup, flush)
+    out.append(dict(op='add_rmsnorm_fp32_residual', tokens=t, ms=ms, gbs=t * h * (2 + 4 + 4 + 2) / ms / 1e6))
+    ms = timed(lambda: ops.add_rmsnorm_(y32, w, x32, w), args.iters, args.warmup, flush)
+    out.append(dict(op='add_rmsnorm_fp32_residual_fp32_y', tokens=t, ms=ms, gbs=t * h * (4 + 4 + 4 + 2) / ms / 1e6))
     qkv = randn(t, 4096, seed=11)
     q, k = qkv[:, :2048].view(t, 8, 256), qkv[:, 2048:3072].view(t, 4, 256)
     gain = randn(256, std=0.1, seed=12)

@@ -361,6 +361,26 @@ def partition_requests(costs, world):
     return [sorted(s) for s in shards]
 
 
+def reassemble_answers(gathered, shards, requests, per_rank):
+    """Answers of a partitioned batch back in request order.
+
+    `gathered` is the concatenation over ranks of `per_rank` values each: rank r's buffer starts with the flat
+    per-candidate answers of its requests `shards[r]` (in that order, questions in request order), the rest is
+    padding.  Returns one flat tensor in the order a single rank would produce for the whole batch."""
+    sizes = [sum(len(q.candidate_positions) for q in r.questions.values()) for r in requests]
+    parts = [None] * len(requests)
+    for rank, shard in enumerate(shards):
+        cursor = rank * per_rank
+        for index in shard:
+            parts[index] = gathered[cursor:cursor + sizes[index]]
+            cursor += sizes[index]
+        if cursor > (rank + 1) * per_rank:
+            raise ValueError(f'rank {rank} holds more answers than its {per_rank}-value buffer')
+    if any(p is None for p in parts):
+        raise ValueError('the shards do not cover every request')
+    return torch.cat(parts) if parts else gathered[:0]
+
+
 def embed_scale(shape: ModelShape, dtype):
     """sqrt(hidden) rounded to the weight dtype, as the embedding multiplies it
     (transformers modeling_t5gemma2.py:645)."""

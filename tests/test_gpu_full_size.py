@@ -126,3 +126,37 @@ def test_mlp_and_linears_full_size_sampled_rows():
         got = ops.linear(a, w)
         want = a[rows].float().cpu() @ w.float().cpu().t()
         assert float((got[rows].float().cpu() - want).abs().max()) < 1e-2 * float(want.abs().max()) + 1e-3, name
+
+
+@pytest.mark.parametrize('pair', [False, True])
+def test_long_context_attention_sampled_rows(pair):
+    """The long-context shape: one 32 768-token segment through the encoder kernel (global and window 1024) and a
+    32 768-row state prefix in front of eight questions through the decoder form, on both forward kernels;
+    sampled query rows against fp32 attention over exactly the keys each row may see."""
+    n = 32768
+    q, k, v = randn(n, HQ, D, seed=21), randn(n, HKV, D, seed=22), randn(n, HKV, D, seed=23)
+    rows = torch.randint(0, n, (24,), generator=torch.Generator().manual_seed(7)).tolist() + [0, n - 1, 511, 512, n - 512]
+    for window in (None, 1024):
+        plan = ops.make_plan([n], window, DEV, group=HQ // HKV, head_dim=D, pair=pair)
+        out = ops.varlen_attention(q, k, v, plan, SCALE)
+        ops.read_status()
+        lo, hi = ops.plan_rows([n], window, decoder=False)
+        want = oracle_rows(q, k, v, rows, lo[rows], hi[rows])
+        assert float((out[rows].float().cpu() - want).abs().max()) < 2e-2, window
+    # decoder: every row of eight questions sees the whole state and its own causal prefix
+    lengths = [141, 77, 200, 64, 129, 33, 180, 95]
+    t = sum(lengths)
+    qd, kd, vd = randn(t, HQ, D, seed=24), randn(t, HKV, D, seed=25), randn(t, HKV, D, seed=26)
+    plan = ops.make_plan(lengths, None, DEV, group=HQ // HKV, owners=[0] * len(lengths), state_lengths=[n], head_dim=D, pair=pair)
+    out = ops.varlen_attention(qd, kd, vd, plan, SCALE, (k, v))          # the segment's k, v serve as the state
+    ops.read_status()
+    starts = [sum(lengths[:i]) for i in range(len(lengths))]
+    picks = [(0, 0), (0, 140), (3, 63), (7, 94), (4, 64), (6, 100)]
+    for seg, pos in picks:
+        r = starts[seg] + pos
+        qs = qd[r].float().cpu().view(HKV, HQ // HKV, D)
+        ks = torch.cat([k.float().cpu(), kd[starts[seg]:r + 1].float().cpu()])
+        vs = torch.cat([v.float().cpu(), vd[starts[seg]:r + 1].float().cpu()])
+        s = torch.einsum('hgd,khd->hgk', qs, ks) * SCALE
+        want = torch.einsum('hgk,khd->hgd', s.softmax(-1), vs).reshape(HQ * D)
+        assert float((out[r].float().cpu() - want).abs().max()) < 2e-2, (seg, pos)

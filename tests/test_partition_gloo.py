@@ -42,6 +42,11 @@ def _rank(rank, world, port, out):
     gathered = [torch.zeros(width, dtype=torch.float64) for _ in range(world)]
     dist.all_gather(gathered, padded)
     if rank == 0:
+        # the flat reassembly the benchmark uses for its strong-scaling check
+        whole = wl.reassemble_answers(torch.cat(gathered), shards, requests, width)
+        expect = [i * 100 + j * 10 + c for i in range(len(requests)) for j, q in enumerate(requests[i].questions.values())
+                  for c in range(len(q.candidate_positions))]
+        assert whole.tolist() == [float(v) for v in expect]
         answers = {}
         for r, buf in enumerate(gathered):
             cursor = 0
