@@ -74,7 +74,7 @@ def parse():
     ap.add_argument('--decoder-pack-tokens', type=int, default=16384)
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-extras', action='store_true', help='skip the strong / long_context / ops keys')
-    ap.add_argument('--extra-steps', type=int, default=3, help='timed steps of the strong and long_context runs')
+    ap.add_argument('--extra-steps', type=int, default=2, help='timed steps of the strong and long_context runs')
     args = ap.parse_args()
     if args.seed is None:
         args.seed = 5 if args.workload == 'long' else 4
