@@ -7,8 +7,13 @@
 // limits the single-CTA kernel.  In a pair each CTA loads its own 128 rows of A and only HALF
 // of the weight panel (128 of the 256 rows); one tcgen05.mma.cta_group::2 instruction issued
 // by the leader CTA drives both tensor cores with M = 256 and reads the two weight halves
-// from both CTAs' shared memory.  Per CTA that is 32 KB per 512 clocks - a third less - and
-// the smaller stages allow a 6-deep ring.
+// from both CTAs' shared memory.  Per CTA that is 32 KB per 512 clocks - a third less.
+//
+// A stage covers 128 of the contraction (two 64-element swizzle slabs per operand, 64 KB per CTA, three
+// stages).  Issuing one MMA costs the issuing thread ~65 cycles, a barrier test ~70 and the two commits
+// that free a stage ~120, so with 64-deep stages (4 MMAs of 128 tensor-core cycles each) the thread
+// needed ~630 cycles per 512 cycles of tensor work and the pipe idled for a sixth of the time; with
+// 8 MMAs per stage the same overheads fit under the 1024 cycles the pipe needs.
 //
 // Synchronisation between the two CTAs (all barriers sit at the same shared-memory offset in
 // both CTAs; nothing uses a multi-destination form):
@@ -25,10 +30,10 @@ using namespace bg;
 
 constexpr int BM = 128;           // rows per CTA (256 per pair)
 constexpr int BN = 256;
-constexpr int BK = 64;
-constexpr int STAGES = 6;
-constexpr int A_BYTES = BM * BK * 2;        // 16 KB
-constexpr int B_BYTES = (BN / 2) * BK * 2;  // 16 KB: this CTA's half of the weight panel
+constexpr int BK = 128;           // contraction per stage: two 64-element (128-byte) swizzle slabs
+constexpr int STAGES = 3;
+constexpr int A_BYTES = BM * BK * 2;        // 32 KB
+constexpr int B_BYTES = (BN / 2) * BK * 2;  // 32 KB: this CTA's half of the weight panel
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + 2 * 256 * 4;
 constexpr int THREADS = 192;
@@ -69,8 +74,8 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 
 // MN = true is the weight-gradient form: out[M, N] = sum_k At[k, M] * Wt[k, N] with both operands stored
 // with the contraction as the ROW index (dW = dy^T x straight from dy [tokens, out] and x [tokens, in]).
-// A stage then holds, per operand, two slabs of 64 contraction rows x 64 elements (128 B, swizzled) instead of
-// 128 rows x 64 contraction elements, and the MMA descriptors say "MN-major".
+// A stage then holds, per operand, two slabs of 128 contraction rows x 64 elements (128 B, swizzled) instead of
+// two slabs of 128 rows x 64 contraction elements, and the MMA descriptors say "MN-major".
 template <bool MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
@@ -158,6 +163,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     } else {
                         tma_load_2d_pair(sa, &map_a, leader_full, kb * BK, row0);
                         tma_load_2d_pair(sa + A_BYTES, &map_w, leader_full, kb * BK, w0);
+                        tma_load_2d_pair(sa + A_BYTES / 2, &map_a, leader_full, kb * BK + 64, row0);
+                        tma_load_2d_pair(sa + A_BYTES + B_BYTES / 2, &map_w, leader_full, kb * BK + 64, w0);
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -183,10 +190,13 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     const uint32_t sb = sa + A_BYTES;
 #pragma unroll
                     for (int kk = 0; kk < BK / 16; ++kk) {
-                        // K-major: 32 B along the swizzled row per 16-deep step; MN-major: 16 contraction rows of
-                        // 128 B per step, slabs of 64 elements 8 KB apart
-                        uint64_t da = MN ? smem_desc_sw128(sa + kk * 2048, A_BYTES / 2, 1024) : smem_desc_sw128(sa + kk * 32, 16, 1024);
-                        uint64_t db = MN ? smem_desc_sw128(sb + kk * 2048, B_BYTES / 2, 1024) : smem_desc_sw128(sb + kk * 32, 16, 1024);
+                        // K-major: 32 B along the swizzled row per 16-deep step, the second 64 of the contraction in
+                        // the second slab; MN-major: 16 contraction rows of 128 B per step, slabs of 64 elements
+                        // half an operand apart
+                        uint64_t da = MN ? smem_desc_sw128(sa + kk * 2048, A_BYTES / 2, 1024)
+                                         : smem_desc_sw128(sa + (kk >> 2) * (A_BYTES / 2) + (kk & 3) * 32, 16, 1024);
+                        uint64_t db = MN ? smem_desc_sw128(sb + kk * 2048, B_BYTES / 2, 1024)
+                                         : smem_desc_sw128(sb + (kk >> 2) * (B_BYTES / 2) + (kk & 3) * 32, 16, 1024);
                         mma_bf16_ss_pair(d_tmem, da, db, idesc, kb != kb0 || kk != 0);
                     }
                     const uint32_t e = smem_u32(&empty[stage]);
@@ -437,7 +447,7 @@ extern "C" int bg_gemm_bf16_qkv_rope(const void* a, int64_t lda, const void* w, 
     CUtensorMap map_a, map_w;
     uint64_t dims_a[2] = {(uint64_t)k, (uint64_t)m}, str_a[1] = {(uint64_t)lda * 2};
     uint64_t dims_w[2] = {(uint64_t)k, (uint64_t)n}, str_w[1] = {(uint64_t)ldw * 2};
-    uint32_t box_a[2] = {BK, BM}, box_w[2] = {BK, 128};
+    uint32_t box_a[2] = {64, BM}, box_w[2] = {64, 128};
     int rc = bg_make_tensor_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a, dims_a, str_a, box_a,
                                 CU_TENSOR_MAP_SWIZZLE_128B);
     if (!rc) rc = bg_make_tensor_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, dims_w, str_w, box_w,
@@ -532,7 +542,7 @@ static int splitk_choice(int64_t m, int64_t n, int64_t k) {
     if (tiles > 3 * pairs) return 1;
     // time ~ waves of the persistent grid x the length of one item: ceil(tiles * s / pairs) / s against
     // ceil(tiles / pairs) unsplit, plus the partial-sum traffic; a split has to save at least 15 % to be taken
-    const int64_t kblocks = (k + BK - 1) / BK;
+    const int64_t kblocks = (k + 63) / 64;          // the split rules count 64-deep blocks
     const double unsplit = double((tiles + pairs - 1) / pairs);
     int best = 1;
     double best_cost = 1.0;
@@ -555,7 +565,7 @@ extern "C" int64_t bg_gemm_bf16_splitk_workspace_bytes(int64_t m, int64_t n, int
 extern "C" int bg_gemm_bf16_splitk(const void* a, int64_t lda, const void* w, int64_t ldw, void* out, int64_t ldo,
                                    int64_t m, int64_t n, int64_t k, int split, void* workspace,
                                    int64_t workspace_bytes, void* stream) {
-    const int64_t kblocks = (k + BK - 1) / BK;
+    const int64_t kblocks = (k + 63) / 64;
     if (m < 0 || n <= 0 || k <= 0 || n % 8 || split < 2 || split > 8 || kblocks < 4 * split) {
         bg_set_error("bg_gemm_bf16_splitk: bad shape (n must be a multiple of 8, 2 <= split <= 8 slices of at least 4 K-blocks)");
         return BG_ERR_SHAPE;
@@ -574,7 +584,7 @@ extern "C" int bg_gemm_bf16_splitk(const void* a, int64_t lda, const void* w, in
     CUtensorMap map_a, map_w;
     uint64_t dims_a[2] = {(uint64_t)k, (uint64_t)m}, str_a[1] = {(uint64_t)lda * 2};
     uint64_t dims_w[2] = {(uint64_t)k, (uint64_t)n}, str_w[1] = {(uint64_t)ldw * 2};
-    uint32_t box_a[2] = {BK, BM}, box_w[2] = {BK, 128};
+    uint32_t box_a[2] = {64, BM}, box_w[2] = {64, 128};
     int rc = bg_make_tensor_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a, dims_a, str_a, box_a,
                                 CU_TENSOR_MAP_SWIZZLE_128B);
     if (!rc) rc = bg_make_tensor_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, dims_w, str_w, box_w,
@@ -613,7 +623,7 @@ extern "C" int bg_gemm_bf16_f32out(const void* a, int64_t lda, const void* w, in
     CUtensorMap map_a, map_w;
     uint64_t dims_a[2] = {(uint64_t)k, (uint64_t)m}, str_a[1] = {(uint64_t)lda * 2};
     uint64_t dims_w[2] = {(uint64_t)k, (uint64_t)n}, str_w[1] = {(uint64_t)ldw * 2};
-    uint32_t box_a[2] = {BK, BM}, box_w[2] = {BK, 128};
+    uint32_t box_a[2] = {64, BM}, box_w[2] = {64, 128};
     int rc = bg_make_tensor_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a, dims_a, str_a, box_a,
                                 CU_TENSOR_MAP_SWIZZLE_128B);
     if (!rc) rc = bg_make_tensor_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, dims_w, str_w, box_w,
@@ -641,7 +651,7 @@ extern "C" int bg_gemm_bf16_tn(const void* at, int64_t ldat, const void* wt, int
         bg_set_error("bg_gemm_bf16_tn: pointers must be 16-byte aligned, m, n and the leading dimensions multiples of 8");
         return BG_ERR_ALIGN;
     }
-    if (split > 1 && ((k + BK - 1) / BK < 4 * split || workspace == nullptr ||
+    if (split > 1 && ((k + 63) / 64 < 4 * split || workspace == nullptr ||
                       workspace_bytes < bg_gemm_bf16_splitk_workspace_bytes(m, n, split))) {
         bg_set_error("bg_gemm_bf16_tn: K slices need at least 4 K-blocks each and a workspace of split * m * n * 4 bytes");
         return BG_ERR_WORKSPACE;
