@@ -1,6 +1,7 @@
 // Packed variable-length attention on tcgen05 tensor cores with TMEM accumulators.
 //
-// One CTA computes one query tile for one KV head.  A query tile is 128 rows: 128/G
+// A work item is one query tile for one KV head; one persistent CTA per SM walks its share of the
+// items (see item_at).  A query tile is 128 rows: 128/G
 // consecutive packed tokens times the G query heads that share the KV head (GQA folded
 // into the M dimension, so K/V tiles are fetched once for all of them).  Keys arrive in
 // tiles of 128 through TMA in two phases that share ONE running softmax:
@@ -27,6 +28,13 @@
 // from that chain.  S(j+1) reuses the buffer that held P(j-1); since
 // consecutive MMAs overlap in the tensor pipe, the issuer waits for P.V(j-1) to complete first.
 // O is only rescaled when a row's running maximum grows by more than 2^8 (lazy rescale).
+//
+// Items are pipelined: the barrier phases count key tiles across items, so while the softmax warps
+// write item i's output the producer already loads item i+1's Q and first K/V tiles and the MMA
+// thread computes its first S.  Only the first P.V of item i+1 waits (o_free) until item i's O has
+// been read out of tensor memory.  Measured per item of 9 key tiles (window 1024): one CTA per item
+// spent ~6 300 cycles before its first S was complete and ~8 000 after its last P.V was issued
+// (read-out, stores, exit, launch of the next CTA) out of ~39 000.
 #include "common.cuh"
 
 namespace {
@@ -49,6 +57,7 @@ struct AttnParams {
     int q_heads, kv_heads;
     float scale_log2;        // softmax scale * log2(e)
     int32_t* status;
+    int n_items;             // tile records x KV heads
 };
 
 template <int D>
@@ -57,15 +66,49 @@ struct Smem {
     static constexpr int Q = 0;
     static constexpr int K = Q + SLABS * SLAB;
     static constexpr int V = K + SLABS * SLAB;
-    static constexpr int BARS = V + SLABS * SLAB;
+    static constexpr int STAGE_SLABS = SLABS < 2 ? SLABS : 2;     // output staging: 128 of the head_dim columns at a time
+    static constexpr int STAGE = V + SLABS * SLAB;
+    static constexpr int BARS = STAGE + STAGE_SLABS * SLAB;
     static constexpr int TOTAL = BARS + 256 + 1024;
 };
+
+// One work item: a query tile (a record of the plan) for one KV head.
+struct Item {
+    int q_start, q_count, own_lo, own_hi, lo_max, hi_min, pre_start, pre_len;
+    int n_pre, n_tiles, kvh;
+};
+
+// The i-th item of this CTA.  Items are numbered tile-major (the KV heads of one tile side by side) over the
+// plan's heaviest-first tile list and dealt to the CTAs in rounds, every other round in reverse order, so that
+// each CTA gets one item of every weight band and the light end of one band follows the heavy end of the last.
+__device__ __forceinline__ bool item_at(const AttnParams& p, int round, Item& im) {
+    const int G = int(gridDim.x);
+    const int it = round * G + ((round & 1) ? G - 1 - int(blockIdx.x) : int(blockIdx.x));
+    if (it >= p.n_items) return false;
+    const int tile = it / p.kv_heads;
+    const int32_t* t = p.tiles + int64_t(tile) * 8;
+    im.q_start = __ldg(t + 0); im.q_count = __ldg(t + 1); im.own_lo = __ldg(t + 2); im.own_hi = __ldg(t + 3);
+    im.lo_max = __ldg(t + 4); im.hi_min = __ldg(t + 5); im.pre_start = __ldg(t + 6); im.pre_len = __ldg(t + 7);
+    im.n_pre = (im.pre_len + KEYS - 1) / KEYS;
+    im.n_tiles = im.n_pre + (im.own_hi - im.own_lo + KEYS - 1) / KEYS;
+    im.kvh = it - tile * p.kv_heads;
+    return true;
+}
+// The first item with keys at or after `round` (a record without keys has nothing to compute); false at the end.
+__device__ __forceinline__ bool next_item(const AttnParams& p, int& round, Item& im) {
+    while (item_at(p, round, im)) {
+        if (im.n_tiles > 0) return true;
+        ++round;
+    }
+    return false;
+}
 
 template <int D>
 __global__ void __launch_bounds__(THREADS, 1)
 varlen_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_ck,
-                        const __grid_constant__ CUtensorMap map_cv, const AttnParams p) {
+                        const __grid_constant__ CUtensorMap map_cv, const __grid_constant__ CUtensorMap map_o,
+                        const AttnParams p) {
     using L = Smem<D>;
     constexpr int SLABS = L::SLABS;
     extern __shared__ uint8_t smem_raw[];
@@ -79,25 +122,20 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     uint64_t* s_full = bars + 5;    // [2]
     uint64_t* p_full = bars + 7;    // 4 warp arrivals: P(j) is in tensor memory
     uint64_t* pv_done = bars + 8;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+    uint64_t* q_empty = bars + 9;   // the item's last S has been computed: the Q tile may be replaced
+    uint64_t* o_free = bars + 10;   // 4 warp arrivals: the item's O has been read out of tensor memory
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const Abort ab{abort_flag, p.status};
-    const int kvh = blockIdx.y;
     const int G = p.q_heads / p.kv_heads;
 
     // Programmatic dependent launch: wait for the predecessor before the first global read (the tile record);
     // the successor may start its own prologue right away.
     pdl_wait();
     pdl_launch_dependents();
-    const int32_t* t = p.tiles + int64_t(blockIdx.x) * 8;
-    const int q_start = t[0], q_count = t[1], own_lo = t[2], own_hi = t[3], lo_max = t[4], hi_min = t[5];
-    const int pre_start = t[6], pre_len = t[7];
-    const int n_pre = (pre_len + KEYS - 1) / KEYS;
-    const int n_own = (own_hi - own_lo + KEYS - 1) / KEYS;
-    const int n_tiles = n_pre + n_own;
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -109,6 +147,8 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         for (int b = 0; b < 2; ++b) mbar_init(&s_full[b], 1);
         mbar_init(p_full, 4);
         mbar_init(pv_done, 1);
+        mbar_init(q_empty, 1);
+        mbar_init(o_free, 4);
         mbar_fence_init();
         tma_prefetch_desc(&map_q);
         tma_prefetch_desc(&map_k);
@@ -124,99 +164,152 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_o = tmem_base + 256;
 
-    if (n_tiles > 0) {
-        if (warp == 0) {
-            // ------------------------------------------------------------ TMA producer
-            if (lane == 0) {
+    // Every role walks the same list of items.  `g` counts the key tiles of the items before the current one:
+    // key tile j of the current item is number g + j of this CTA, and the barrier phases follow that number, so
+    // the K, V and S/P hand-over runs on across item boundaries.  `done` counts the items before the current one.
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            Item im;
+            int round = 0;
+            uint32_t g = 0, done = 0;
+            bool ok = true;
+            for (; ok && next_item(p, round, im); ++round, ++done) {
+                // the Q tile of the item before has been multiplied for the last time
+                if (done > 0 && !mbar_wait_parked(q_empty, (done - 1) & 1, ab, 211)) break;
                 mbar_expect_tx(q_full, SLABS * SLAB);
                 for (int s = 0; s < SLABS; ++s)
-                    tma_load_3d(smem + L::Q + s * SLAB, &map_q, q_full, s * 64, kvh * G, q_start);
+                    tma_load_3d(smem + L::Q + s * SLAB, &map_q, q_full, s * 64, im.kvh * G, im.q_start);
                 auto load_k = [&](int j) {
-                    if (!mbar_wait_parked(k_empty, (j & 1) ^ 1, ab, 201)) return;
-                    const bool pre = j < n_pre;
-                    const int key0 = pre ? pre_start + j * KEYS : own_lo + (j - n_pre) * KEYS;
+                    if (!ok || !mbar_wait_parked(k_empty, ((g + j) & 1) ^ 1, ab, 201)) { ok = false; return; }
+                    const bool pre = j < im.n_pre;
+                    const int key0 = pre ? im.pre_start + j * KEYS : im.own_lo + (j - im.n_pre) * KEYS;
                     mbar_expect_tx(k_full, SLABS * SLAB);
                     for (int s = 0; s < SLABS; ++s)
-                        tma_load_3d(smem + L::K + s * SLAB, pre ? &map_ck : &map_k, k_full, s * 64, kvh, key0);
+                        tma_load_3d(smem + L::K + s * SLAB, pre ? &map_ck : &map_k, k_full, s * 64, im.kvh, key0);
                 };
                 auto load_v = [&](int j) {
-                    if (!mbar_wait_parked(v_empty, (j & 1) ^ 1, ab, 202)) return;
-                    const bool pre = j < n_pre;
-                    const int key0 = pre ? pre_start + j * KEYS : own_lo + (j - n_pre) * KEYS;
+                    if (!ok || !mbar_wait_parked(v_empty, ((g + j) & 1) ^ 1, ab, 202)) { ok = false; return; }
+                    const bool pre = j < im.n_pre;
+                    const int key0 = pre ? im.pre_start + j * KEYS : im.own_lo + (j - im.n_pre) * KEYS;
                     mbar_expect_tx(v_full, SLABS * SLAB);
                     for (int s = 0; s < SLABS; ++s)
-                        tma_load_3d(smem + L::V + s * SLAB, pre ? &map_cv : &map_v, v_full, s * 64, kvh, key0);
+                        tma_load_3d(smem + L::V + s * SLAB, pre ? &map_cv : &map_v, v_full, s * 64, im.kvh, key0);
                 };
                 // Issue order follows the order in which the slots drain: S(j) completes before
                 // P.V(j-1), so K(j+1) is requested before V(j).
                 load_k(0);
                 load_v(0);
-                if (n_tiles > 1) load_k(1);
-                for (int j = 1; j < n_tiles; ++j) {
-                    if (j + 1 < n_tiles) load_k(j + 1);
+                if (im.n_tiles > 1) load_k(1);
+                for (int j = 1; j < im.n_tiles; ++j) {
+                    if (j + 1 < im.n_tiles) load_k(j + 1);
                     load_v(j);
                 }
+                g += im.n_tiles;
             }
-        } else if (warp == 1) {
-            // ------------------------------------------------------------ MMA issuer
-            if (lane == 0) {
-                constexpr uint32_t idesc_s = instr_desc(ROWS, KEYS, 1, 1, 0, 0);
-                constexpr uint32_t idesc_o = instr_desc(ROWS, D, 1, 1, 0, 1);   // V is MN-major
-                const uint32_t sq = smem_u32(smem + L::Q), sk = smem_u32(smem + L::K);
-                const uint32_t sv = smem_u32(smem + L::V);
-                auto issue_s = [&](int j) {
-                    const int b = j & 1;
-                    if (!mbar_wait(k_full, j & 1, ab, 203)) return;
-                    // Buffer b still holds P(j-2) as the A operand of P.V(j-2).  Consecutive MMAs overlap in
-                    // the tensor pipe, so issue order alone does not protect it: wait for that P.V to finish.
-                    if (j >= 2 && !mbar_wait(pv_done, j & 1, ab, 204)) return;
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = instr_desc(ROWS, KEYS, 1, 1, 0, 0);
+            constexpr uint32_t idesc_o = instr_desc(ROWS, D, 1, 1, 0, 1);   // V is MN-major
+            const uint32_t sq = smem_u32(smem + L::Q), sk = smem_u32(smem + L::K);
+            const uint32_t sv = smem_u32(smem + L::V);
+            bool ok = true;
+            // S of key tile number gj.  `first`: the item's first tile (its Q tile has to have arrived); `last`: its
+            // last one (afterwards the Q tile may be replaced).
+            auto issue_s = [&](uint32_t gj, uint32_t done, bool first, bool last) {
+                const int b = gj & 1;
+                if (!ok) return;
+                if (first && !mbar_wait(q_full, done & 1, ab, 205)) { ok = false; return; }
+                if (!mbar_wait(k_full, gj & 1, ab, 203)) { ok = false; return; }
+                // Buffer b still holds P(gj-2) as the A operand of P.V(gj-2).  Consecutive MMAs overlap in the
+                // tensor pipe, so issue order alone does not protect it: wait for that P.V to finish.  An item's
+                // first S is issued after the last P.V of the item before, whose P was only stored once
+                // P.V(gj-2) had completed: nothing to wait for (and pv_done may already be a phase further).
+                if (!first && gj >= 2 && !mbar_wait(pv_done, gj & 1, ab, 204)) { ok = false; return; }
+                tc_fence_after();
+#pragma unroll
+                for (int s = 0; s < SLABS; ++s)
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        uint64_t da = smem_desc_sw128(sq + s * SLAB + kk * 32, 16, 1024);
+                        uint64_t db = smem_desc_sw128(sk + s * SLAB + kk * 32, 16, 1024);
+                        mma_bf16_ss(tmem_base + b * KEYS, da, db, idesc_s, (s | kk) != 0);
+                    }
+                mma_commit(&s_full[b]);
+                mma_commit(k_empty);
+                if (last) mma_commit(q_empty);
+            };
+            Item im, nx;
+            int round = 0;
+            uint32_t g = 0, done = 0;
+            bool have = next_item(p, round, im);
+            if (have) issue_s(0, 0, true, im.n_tiles == 1);
+            while (have && ok) {
+                int round_nx = round + 1;
+                const bool have_nx = next_item(p, round_nx, nx);
+                const int n = im.n_tiles;
+                for (int j = 0; j < n; ++j) {
+                    if (j + 1 < n) issue_s(g + j + 1, done, false, j + 2 == n);
+                    if (!ok || !mbar_wait(p_full, (g + j) & 1, ab, 206) || !mbar_wait(v_full, (g + j) & 1, ab, 207)) {
+                        ok = false;
+                        break;
+                    }
+                    // the first P.V of an item overwrites O: the epilogue of the item before has to have read it
+                    if (j == 0 && done > 0 && !mbar_wait(o_free, (done - 1) & 1, ab, 212)) {
+                        ok = false;
+                        break;
+                    }
                     tc_fence_after();
 #pragma unroll
-                    for (int s = 0; s < SLABS; ++s)
-#pragma unroll
-                        for (int kk = 0; kk < 4; ++kk) {
-                            uint64_t da = smem_desc_sw128(sq + s * SLAB + kk * 32, 16, 1024);
-                            uint64_t db = smem_desc_sw128(sk + s * SLAB + kk * 32, 16, 1024);
-                            mma_bf16_ss(tmem_base + b * KEYS, da, db, idesc_s, (s | kk) != 0);
-                        }
-                    mma_commit(&s_full[b]);
-                    mma_commit(k_empty);
-                };
-                if (mbar_wait(q_full, 0, ab, 205)) {
-                    issue_s(0);
-                    for (int j = 0; j < n_tiles; ++j) {
-                        if (j + 1 < n_tiles) issue_s(j + 1);
-                        if (!mbar_wait(p_full, j & 1, ab, 206)) break;
-                        if (!mbar_wait(v_full, j & 1, ab, 207)) break;
-                        tc_fence_after();
-#pragma unroll
-                        for (int kk = 0; kk < KEYS / 16; ++kk) {
-                            uint64_t db = smem_desc_sw128(sv + kk * 2048, SLAB, 1024);
-                            mma_bf16_ts(tmem_o, tmem_base + (j & 1) * KEYS + kk * 8, db, idesc_o, (j | kk) != 0);
-                        }
-                        mma_commit(pv_done);
-                        mma_commit(v_empty);
+                    for (int kk = 0; kk < KEYS / 16; ++kk) {
+                        uint64_t db = smem_desc_sw128(sv + kk * 2048, SLAB, 1024);
+                        mma_bf16_ts(tmem_o, tmem_base + ((g + j) & 1) * KEYS + kk * 8, db, idesc_o, (j | kk) != 0);
                     }
+                    mma_commit(pv_done);
+                    mma_commit(v_empty);
                 }
+                g += n;
+                ++done;
+                // the next item's first S runs under this item's epilogue
+                if (have_nx) issue_s(g, done, true, nx.n_tiles == 1);
+                im = nx;
+                round = round_nx;
+                have = have_nx;
             }
-        } else {
-            // ------------------------------------------------------------ softmax + epilogue (warps 2..5)
-            const int part = warp & 3;
-            const int row = part * 32 + lane;
-            const int tok_local = row / G;
-            const int head = kvh * G + row % G;
-            const bool row_valid = tok_local < q_count;
-            const int64_t token = int64_t(q_start) + tok_local;
-            const int rlo = row_valid ? p.row_lo[token] : 0;
-            const int rhi = row_valid ? p.row_hi[token] : 0;
-            const uint32_t lane_addr = uint32_t(part * 32) << 16;
-            const float c = p.scale_log2;
-            const float lazy = LAZY_LOG2 / c;
+        }
+    } else {
+        // ------------------------------------------------------------ softmax + epilogue (warps 2..5)
+        const int part = warp & 3;
+        const int row = part * 32 + lane;
+        const int tok_local = row / G;
+        const uint32_t lane_addr = uint32_t(part * 32) << 16;
+        const float c = p.scale_log2;
+        const float lazy = LAZY_LOG2 / c;
+        Item im;
+        int round = 0;
+        uint32_t g = 0;
+        bool ok = true;
+        bool have = next_item(p, round, im);
+        // this row's own-key range; the next item's record and range are fetched before the current item's
+        // epilogue, so that their latency runs under it
+        int rlo = 0, rhi = 0;
+        if (have && tok_local < im.q_count) {
+            rlo = __ldg(p.row_lo + im.q_start + tok_local);
+            rhi = __ldg(p.row_hi + im.q_start + tok_local);
+        }
+        while (ok && have) {
+            const int head = im.kvh * G + row % G;
+            const bool row_valid = tok_local < im.q_count;
+            const int64_t token = int64_t(im.q_start) + tok_local;
+            const int n_tiles = im.n_tiles, n_pre = im.n_pre, pre_start = im.pre_start, pre_len = im.pre_len;
             float m_ref = -INFINITY, l = 0.f;
 
             for (int j = 0; j < n_tiles; ++j) {
-                const int b = j & 1;
-                if (!mbar_wait(&s_full[b], (j >> 1) & 1, ab, 208)) break;
+                const uint32_t gj = g + j;
+                const int b = gj & 1;
+                if (!mbar_wait(&s_full[b], (gj >> 1) & 1, ab, 208)) { ok = false; break; }
                 tc_fence_after();
                 float s[KEYS];
 #pragma unroll
@@ -225,11 +318,11 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 tmem_wait_ld();
 
                 const bool pre = j < n_pre;
-                const int key0 = pre ? pre_start + j * KEYS : own_lo + (j - n_pre) * KEYS;
+                const int key0 = pre ? pre_start + j * KEYS : im.own_lo + (j - n_pre) * KEYS;
                 const int lo = pre ? pre_start : rlo;
                 const int hi = pre ? (row_valid ? pre_start + pre_len : pre_start) : rhi;
                 const bool need_mask = pre ? (key0 + KEYS > pre_start + pre_len) || !row_valid
-                                           : !(key0 >= lo_max && key0 + KEYS <= hi_min) || !row_valid;
+                                           : !(key0 >= im.lo_max && key0 + KEYS <= im.hi_min) || !row_valid;
                 if (need_mask) {
 #pragma unroll
                     for (int i = 0; i < KEYS; ++i) {
@@ -265,9 +358,10 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 for (int i = 0; i < KEYS / 2; ++i) asm volatile("" : "+r"(w[i]));
                 // P(j) may only be stored once P.V(j-1) has completed: a tcgen05.st into tensor memory while a
                 // TS-form MMA is still reading its A operand from tensor memory corrupted results on B200, even
-                // though the two touch different columns.  The same wait makes O stable for a rescale.
+                // though the two touch different columns.  The same wait makes O stable for a rescale.  For an
+                // item's first tile the epilogue of the item before has waited for that P.V already.
                 if (j > 0) {
-                    mbar_wait(pv_done, (j - 1) & 1, ab, 209);
+                    if (!mbar_wait(pv_done, (gj - 1) & 1, ab, 209)) { ok = false; break; }
                     tc_fence_after();
                     if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll 1
@@ -290,39 +384,89 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 __syncwarp();
                 if (lane == 0) mbar_arrive(p_full);
             }
+            if (!ok) break;
 
-            // epilogue: O / l -> bf16
-            if (mbar_wait(pv_done, (n_tiles - 1) & 1, ab, 210)) {
-                tc_fence_after();
-                const float inv = l > 0.f ? 1.f / l : 0.f;
-                __nv_bfloat16* dst = p.out + (token * p.q_heads + head) * D;
-                // a tensor-memory load takes some hundred cycles to return: up to four are in flight per wait
-                constexpr int EP = D < 128 ? D : 128;
+            // The next item's record and this row's key range in it are requested now, so that their latency runs
+            // under the epilogue; only the range is kept in registers, the record is read again (from L1) afterwards.
+            int round_nx = round + 1;
+            int rlo_nx = 0, rhi_nx = 0;
+            {
+                Item nx;
+                if (next_item(p, round_nx, nx) && tok_local < nx.q_count) {
+                    rlo_nx = __ldg(p.row_lo + nx.q_start + tok_local);
+                    rhi_nx = __ldg(p.row_hi + nx.q_start + tok_local);
+                }
+                asm volatile("" : "+r"(rlo_nx), "+r"(rhi_nx), "+r"(round_nx));
+            }
+
+            // epilogue: O / l -> bf16.  O is released to the next item's first P.V as soon as its last columns are in
+            // registers.  A full tile leaves through a staging buffer, 128 head_dim columns at a time: every thread
+            // writes its row in the 128-byte-swizzled layout and one thread issues a TMA store per 64-column slab -
+            // whole cache lines instead of 32 rows x 16 bytes per store instruction.  A tile that ends early (last
+            // tile of a run) is stored from registers, since a TMA store would also write the rows past its end.
+            if (!mbar_wait(pv_done, (g + n_tiles - 1) & 1, ab, 210)) break;
+            tc_fence_after();
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            __nv_bfloat16* dst = p.out + (token * p.q_heads + head) * D;
+            uint8_t* srow = smem + L::STAGE + row * 128;
+            const bool staged = im.q_count == ROWS / G;      // the same for every thread of the CTA
+            const bool storer = warp == 2 && lane == 0;
+            // a tensor-memory load takes some hundred cycles to return: up to four are in flight per wait
+            constexpr int EP = D < 128 ? D : 128;
 #pragma unroll 1
-                for (int half = 0; half < D; half += EP) {
-                    uint32_t o[EP];
+            for (int half = 0; half < D; half += EP) {
+                uint32_t o[EP];
 #pragma unroll
-                    for (int cc = 0; cc < EP; cc += 32) tmem_ld32(tmem_o + lane_addr + half + cc, o + cc);
-                    tmem_wait_ld();
-                    if (row_valid) {
+                for (int cc = 0; cc < EP; cc += 32) tmem_ld32(tmem_o + lane_addr + half + cc, o + cc);
+                tmem_wait_ld();
+                if (half + EP >= D) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(o_free);
+                }
+                if (staged) {
+                    // the staging buffer is free once the stores issued from it have read it
+                    if (storer) tma_store_wait_read();
+                    named_barrier(1, 128);
+                }
 #pragma unroll
-                        for (int v4 = 0; v4 < EP / 8; ++v4) {
-                            uint4 v;
-                            v.x = pack_bf16(__uint_as_float(o[v4 * 8 + 0]) * inv, __uint_as_float(o[v4 * 8 + 1]) * inv);
-                            v.y = pack_bf16(__uint_as_float(o[v4 * 8 + 2]) * inv, __uint_as_float(o[v4 * 8 + 3]) * inv);
-                            v.z = pack_bf16(__uint_as_float(o[v4 * 8 + 4]) * inv, __uint_as_float(o[v4 * 8 + 5]) * inv);
-                            v.w = pack_bf16(__uint_as_float(o[v4 * 8 + 6]) * inv, __uint_as_float(o[v4 * 8 + 7]) * inv);
-                            *reinterpret_cast<uint4*>(dst + half + v4 * 8) = v;
-                        }
+                for (int v4 = 0; v4 < EP / 8; ++v4) {
+                    uint4 v;
+                    v.x = pack_bf16(__uint_as_float(o[v4 * 8 + 0]) * inv, __uint_as_float(o[v4 * 8 + 1]) * inv);
+                    v.y = pack_bf16(__uint_as_float(o[v4 * 8 + 2]) * inv, __uint_as_float(o[v4 * 8 + 3]) * inv);
+                    v.z = pack_bf16(__uint_as_float(o[v4 * 8 + 4]) * inv, __uint_as_float(o[v4 * 8 + 5]) * inv);
+                    v.w = pack_bf16(__uint_as_float(o[v4 * 8 + 6]) * inv, __uint_as_float(o[v4 * 8 + 7]) * inv);
+                    if (staged) {
+                        const int col = v4 * 8;                  // column inside this pass
+                        const int chunk = (col & 63) >> 3;       // 16-byte chunk inside the 128-byte slab row
+                        *reinterpret_cast<uint4*>(srow + (col >> 6) * SLAB + ((chunk ^ (row & 7)) << 4)) = v;
+                    } else if (row_valid) {
+                        *reinterpret_cast<uint4*>(dst + half + v4 * 8) = v;
                     }
                 }
-                if (p.lse != nullptr && row_valid) {
-                    const float ln2 = 0.6931471805599453f;
-                    p.lse[int64_t(head) * p.tq + token] =
-                        l > 0.f ? (m_ref * c + log2f(l)) * ln2 : -INFINITY;
+                if (staged) {
+                    fence_async_proxy();
+                    named_barrier(1, 128);
+                    if (storer) {
+                        for (int sl = 0; sl < EP / 64; ++sl)
+                            tma_store_3d(&map_o, smem + L::STAGE + sl * SLAB, half + sl * 64, im.kvh * G, im.q_start);
+                        tma_store_commit();
+                    }
                 }
             }
+            if (p.lse != nullptr && row_valid) {
+                const float ln2 = 0.6931471805599453f;
+                p.lse[int64_t(head) * p.tq + token] =
+                    l > 0.f ? (m_ref * c + log2f(l)) * ln2 : -INFINITY;
+            }
+            g += n_tiles;
+            round = round_nx;
+            have = item_at(p, round, im);     // round_nx already points at an item with keys, or past the end
+            rlo = rlo_nx;
+            rhi = rhi_nx;
         }
+        // the last stores have to have read the staging buffer before the CTA gives up its shared memory
+        if (warp == 2 && lane == 0) tma_store_wait_read();
     }
 
     // ---------------------------------------------------------------- teardown
@@ -341,7 +485,7 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 
 template <int D>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mck,
-           const CUtensorMap& mcv, const AttnParams& p, int n_tiles, cudaStream_t stream) {
+           const CUtensorMap& mcv, const CUtensorMap& mo, const AttnParams& p, cudaStream_t stream) {
     static bool configured_on[kBgMaxDevices] = {};
     bool& configured = configured_on[bg_device_slot()];
     if (!configured) {
@@ -353,9 +497,10 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
         }
         configured = true;
     }
-    dim3 grid((unsigned)n_tiles, (unsigned)p.kv_heads);
+    const int sms = bg_num_sms();       // one CTA per SM (shared and tensor memory are used in full)
+    dim3 grid((unsigned)(p.n_items < sms ? p.n_items : sms));
     cudaError_t e = launch_kernel(varlen_attention_kernel<D>, grid, dim3(THREADS), Smem<D>::TOTAL, stream, 0, mq, mk, mv,
-                                  mck, mcv, p);
+                                  mck, mcv, mo, p);
     if (e != cudaSuccess) {
         bg_set_error("bg_varlen_attention: launch: %s", cudaGetErrorString(e));
         return BG_ERR_LAUNCH;
@@ -416,6 +561,15 @@ extern "C" int bg_varlen_attention(const void* q, int64_t ldq, int64_t hsq, cons
     if (!rc && cv) rc = kv_map(&mcv, cv, ts, kv_heads, head_dim, ldc, hsc);
     if (rc) return rc;
     if (!ck) { mck = mk; mcv = mv; }
+    CUtensorMap mo;      // the output [tq, q_heads, head_dim], stored in the boxes the Q tiles are loaded in
+    {
+        uint64_t dims[3] = {(uint64_t)head_dim, (uint64_t)q_heads, (uint64_t)tq};
+        uint64_t strides[2] = {(uint64_t)head_dim * 2, (uint64_t)q_heads * head_dim * 2};
+        uint32_t box[3] = {64, (uint32_t)g, (uint32_t)(ROWS / g)};
+        rc = bg_make_tensor_map(&mo, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, out, dims, strides, box,
+                                CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
+    }
 
     AttnParams p;
     p.tiles = tiles; p.row_lo = row_lo; p.row_hi = row_hi;
@@ -424,7 +578,7 @@ extern "C" int bg_varlen_attention(const void* q, int64_t ldq, int64_t hsq, cons
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = bg_status_word();
     if (!p.status) return BG_ERR_DRIVER;
+    p.n_items = n_tiles * kv_heads;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    return head_dim == 64 ? launch<64>(mq, mk, mv, mck, mcv, p, n_tiles, s)
-                          : launch<256>(mq, mk, mv, mck, mcv, p, n_tiles, s);
+    return head_dim == 64 ? launch<64>(mq, mk, mv, mck, mcv, mo, p, s) : launch<256>(mq, mk, mv, mck, mcv, mo, p, s);
 }
