@@ -1,10 +1,9 @@
 // Packed variable-length attention on tcgen05 tensor cores with TMEM accumulators.
 //
 // A work item is one query tile for one KV head; one persistent CTA per SM walks its share of the
-// items (see item_at).  A query tile is 128 rows: 128/G
-// consecutive packed tokens times the G query heads that share the KV head (GQA folded
-// into the M dimension, so K/V tiles are fetched once for all of them).  Keys arrive in
-// tiles of 128 through TMA in two phases that share ONE running softmax:
+// items (see item_at).  A query tile is 128 rows: 128/G consecutive packed tokens times the G query
+// heads that share the KV head (GQA folded into the M dimension, so K/V tiles are fetched once for
+// all of them).  Keys arrive in tiles of 128 through TMA in two phases that share ONE running softmax:
 //
 //   prefix phase   keys [prefix_start, prefix_start + prefix_len) of a second K/V pair (the
 //                  decoder's shared state memory); every row of the tile sees all of them.
@@ -18,8 +17,11 @@
 //                           its own question                       (bongard/flash_varlen.py:1-8, 61-77)
 // A tile whose rows belong to several questions of one owner streams the owner's state once.
 //
-// Roles: warp 0 = TMA producer, warp 1 = MMA issuer (S = Q K^T, O += P V), warps 2-5 = softmax
-// (thread = row).  S is double-buffered in TMEM (2 x 128 columns), O lives in TMEM (D columns).
+// Roles, by warpgroup (384 threads): warp 0 = TMA producer, warp 1 = MMA issuer (S = Q K^T, O += P V);
+// warps 4-7 = softmax (thread = row); warps 8-11 = output (thread = row).  After start-up the groups
+// re-divide the register file (setmaxnreg): a softmax thread holds a row of 128 scores and its packed
+// probabilities and gets 240 registers, the control warps 96, the output warps keep 168.
+// S is double-buffered in TMEM (2 x 128 columns), O lives in TMEM (D columns).
 // The probabilities never leave tensor memory: a softmax thread overwrites the first 64 columns
 // of the S buffer it has just read with its row of P as packed bf16 (tcgen05.st), and O += P V is
 // issued in the TS form (A = P from TMEM, B = V tile in shared memory, MN-major).  Each iteration
@@ -29,12 +31,14 @@
 // consecutive MMAs overlap in the tensor pipe, the issuer waits for P.V(j-1) to complete first.
 // O is only rescaled when a row's running maximum grows by more than 2^8 (lazy rescale).
 //
-// Items are pipelined: the barrier phases count key tiles across items, so while the softmax warps
-// write item i's output the producer already loads item i+1's Q and first K/V tiles and the MMA
-// thread computes its first S.  Only the first P.V of item i+1 waits (o_free) until item i's O has
-// been read out of tensor memory.  Measured per item of 9 key tiles (window 1024): one CTA per item
-// spent ~6 300 cycles before its first S was complete and ~8 000 after its last P.V was issued
-// (read-out, stores, exit, launch of the next CTA) out of ~39 000.
+// Items are pipelined: the barrier phases count key tiles across items, so while item i's output is
+// written the producer already loads item i+1's Q and first K/V tiles, the MMA thread computes its
+// first S and the softmax warps work on it.  The softmax warps pass an item's row sums to the output
+// warps through shared memory (l_full) and go on; the output warps read O out of tensor memory,
+// release it (o_free: only the first P.V of item i+1 waits for that) and store the tile through a
+// staging buffer with TMA.  Measured per item of 9 key tiles (window 1024): with one CTA per item,
+// ~6 300 cycles passed before its first S was complete and ~8 000 after its last P.V was issued
+// (read-out, stores, exit, launch of the next CTA) out of ~39 000; pipelined, an item takes ~32 000.
 #include "common.cuh"
 
 namespace {
@@ -43,7 +47,9 @@ using namespace bg;
 
 constexpr int ROWS = 128;         // query rows per tile (tokens x GQA group)
 constexpr int KEYS = 128;         // keys per tile
-constexpr int THREADS = 192;
+constexpr int THREADS = 384;      // warpgroup 0: TMA producer (warp 0) and MMA issuer (warp 1); 1: softmax; 2: output
+constexpr int REGS_CONTROL = 96;  // registers per thread after the warpgroups have re-divided the register file:
+constexpr int REGS_SOFTMAX = 240; //   the softmax threads hold a row of 128 scores and its packed probabilities
 constexpr int SLAB = 16384;       // 128 rows x 128 B
 constexpr float LAZY_LOG2 = 8.f;  // rescale threshold in log2 units
 
@@ -69,7 +75,8 @@ struct Smem {
     static constexpr int STAGE_SLABS = SLABS < 2 ? SLABS : 2;     // output staging: 128 of the head_dim columns at a time
     static constexpr int STAGE = V + SLABS * SLAB;
     static constexpr int BARS = STAGE + STAGE_SLABS * SLAB;
-    static constexpr int TOTAL = BARS + 256 + 1024;
+    static constexpr int ROWSUM = BARS + 256;                     // [2][128] floats: row sums and running maxima of an item
+    static constexpr int TOTAL = ROWSUM + 1024 + 1024;
 };
 
 // One work item: a query tile (a record of the plan) for one KV head.
@@ -123,8 +130,9 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     uint64_t* p_full = bars + 7;    // 4 warp arrivals: P(j) is in tensor memory
     uint64_t* pv_done = bars + 8;
     uint64_t* q_empty = bars + 9;   // the item's last S has been computed: the Q tile may be replaced
-    uint64_t* o_free = bars + 10;   // 4 warp arrivals: the item's O has been read out of tensor memory
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+    uint64_t* o_free = bars + 10;   // 4 warp arrivals: the item's O (and row sums) have been read by the output warps
+    uint64_t* l_full = bars + 11;   // 4 warp arrivals: the item's row sums are in shared memory
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -149,6 +157,7 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         mbar_init(pv_done, 1);
         mbar_init(q_empty, 1);
         mbar_init(o_free, 4);
+        mbar_init(l_full, 4);
         mbar_fence_init();
         tma_prefetch_desc(&map_q);
         tma_prefetch_desc(&map_k);
@@ -167,6 +176,11 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     // Every role walks the same list of items.  `g` counts the key tiles of the items before the current one:
     // key tile j of the current item is number g + j of this CTA, and the barrier phases follow that number, so
     // the K, V and S/P hand-over runs on across item boundaries.  `done` counts the items before the current one.
+    float* row_l = reinterpret_cast<float*>(smem + L::ROWSUM);
+    float* row_m = row_l + ROWS;
+    // The three warpgroups re-divide the register file: the softmax threads need far more than the rest.
+    if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_CONTROL));
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
@@ -272,15 +286,18 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 }
                 g += n;
                 ++done;
-                // the next item's first S runs under this item's epilogue
+                // The next item's first S follows this item's last P.V into the pipe.  (Issuing it before that P.V,
+                // as soon as its tiles had arrived, was slower: the P.V then waits behind it.)
                 if (have_nx) issue_s(g, done, true, nx.n_tiles == 1);
                 im = nx;
                 round = round_nx;
                 have = have_nx;
             }
         }
-    } else {
-        // ------------------------------------------------------------ softmax + epilogue (warps 2..5)
+    }
+    } else if (warp < 8) {
+        // ------------------------------------------------------------ softmax (warps 4..7, thread = row)
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS_SOFTMAX));
         const int part = warp & 3;
         const int row = part * 32 + lane;
         const int tok_local = row / G;
@@ -289,7 +306,7 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const float lazy = LAZY_LOG2 / c;
         Item im;
         int round = 0;
-        uint32_t g = 0;
+        uint32_t g = 0, done = 0;
         bool ok = true;
         bool have = next_item(p, round, im);
         // this row's own-key range; the next item's record and range are fetched before the current item's
@@ -300,9 +317,7 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             rhi = __ldg(p.row_hi + im.q_start + tok_local);
         }
         while (ok && have) {
-            const int head = im.kvh * G + row % G;
             const bool row_valid = tok_local < im.q_count;
-            const int64_t token = int64_t(im.q_start) + tok_local;
             const int n_tiles = im.n_tiles, n_pre = im.n_pre, pre_start = im.pre_start, pre_len = im.pre_len;
             float m_ref = -INFINITY, l = 0.f;
 
@@ -323,11 +338,17 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 const int hi = pre ? (row_valid ? pre_start + pre_len : pre_start) : rhi;
                 const bool need_mask = pre ? (key0 + KEYS > pre_start + pre_len) || !row_valid
                                            : !(key0 >= im.lo_max && key0 + KEYS <= im.hi_min) || !row_valid;
-                if (need_mask) {
+                // The visible keys of a row are one run [first, last) of the tile, and the runs of a warp's rows differ
+                // by a few keys only: a 32-key chunk inside every row's run is skipped by the whole warp.  The votes
+                // are taken by all 32 lanes (need_mask differs between the rows of a tile that ends early).
+                if (__any_sync(0xffffffffu, need_mask)) {
+                    const int first = need_mask ? lo - key0 : 0, last = need_mask ? hi - key0 : KEYS;
 #pragma unroll
-                    for (int i = 0; i < KEYS; ++i) {
-                        const int key = key0 + i;
-                        if (key < lo || key >= hi) s[i] = -INFINITY;
+                    for (int cc = 0; cc < KEYS; cc += 32) {
+                        if (__all_sync(0xffffffffu, first <= cc && last >= cc + 32)) continue;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (cc + i < first || cc + i >= last) s[cc + i] = -INFINITY;
                     }
                 }
                 float mx = s[0];
@@ -356,14 +377,14 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 for (int i = 0; i < KEYS / 2; ++i) w[i] = pack_bf16(s[2 * i], s[2 * i + 1]);
 #pragma unroll
                 for (int i = 0; i < KEYS / 2; ++i) asm volatile("" : "+r"(w[i]));
-                // P(j) may only be stored once P.V(j-1) has completed: a tcgen05.st into tensor memory while a
-                // TS-form MMA is still reading its A operand from tensor memory corrupted results on B200, even
-                // though the two touch different columns.  The same wait makes O stable for a rescale.  For an
-                // item's first tile the epilogue of the item before has waited for that P.V already.
-                if (j > 0) {
+                // P(j) may only be stored once the P.V before it has completed (for an item's first tile that is the
+                // last P.V of the item before): a tcgen05.st into tensor memory while a TS-form MMA is still
+                // reading its A operand from tensor memory corrupted results on B200, even though the two touch
+                // different columns.  The same wait makes O stable for a rescale.
+                if (gj > 0) {
                     if (!mbar_wait(pv_done, (gj - 1) & 1, ab, 209)) { ok = false; break; }
                     tc_fence_after();
-                    if (__any_sync(0xffffffffu, grow)) {
+                    if (j > 0 && __any_sync(0xffffffffu, grow)) {
 #pragma unroll 1
                         for (int cc = 0; cc < D; cc += 32) {
                             uint32_t o[32];
@@ -386,31 +407,53 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             }
             if (!ok) break;
 
-            // The next item's record and this row's key range in it are requested now, so that their latency runs
-            // under the epilogue; only the range is kept in registers, the record is read again (from L1) afterwards.
-            int round_nx = round + 1;
-            int rlo_nx = 0, rhi_nx = 0;
-            {
-                Item nx;
-                if (next_item(p, round_nx, nx) && tok_local < nx.q_count) {
-                    rlo_nx = __ldg(p.row_lo + nx.q_start + tok_local);
-                    rhi_nx = __ldg(p.row_hi + nx.q_start + tok_local);
-                }
-                asm volatile("" : "+r"(rlo_nx), "+r"(rhi_nx), "+r"(round_nx));
-            }
+            // Hand the row sums to the output warps.  The one buffer is free once they have read the item before.
+            if (done > 0 && !mbar_wait(o_free, (done - 1) & 1, ab, 213)) break;
+            row_l[row] = l;
+            row_m[row] = m_ref;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(l_full);
 
-            // epilogue: O / l -> bf16.  O is released to the next item's first P.V as soon as its last columns are in
-            // registers.  A full tile leaves through a staging buffer, 128 head_dim columns at a time: every thread
-            // writes its row in the 128-byte-swizzled layout and one thread issues a TMA store per 64-column slab -
-            // whole cache lines instead of 32 rows x 16 bytes per store instruction.  A tile that ends early (last
-            // tile of a run) is stored from registers, since a TMA store would also write the rows past its end.
-            if (!mbar_wait(pv_done, (g + n_tiles - 1) & 1, ab, 210)) break;
+            g += n_tiles;
+            ++done;
+            ++round;
+            have = next_item(p, round, im);
+            rlo = rhi = 0;
+            if (have && tok_local < im.q_count) {
+                rlo = __ldg(p.row_lo + im.q_start + tok_local);
+                rhi = __ldg(p.row_hi + im.q_start + tok_local);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ output (warps 8..11, thread = row)
+        // O / l -> bf16 while the softmax warps are already at work on the next item.  O is released to that
+        // item's first P.V as soon as its last columns are in registers.  A full tile leaves through a staging
+        // buffer, 128 head_dim columns at a time: every thread writes its row in the 128-byte-swizzled layout and
+        // one thread issues a TMA store per 64-column slab - whole cache lines instead of 32 rows x 16 bytes per
+        // store instruction.  A tile that ends early (last tile of a run) is stored from registers, since a TMA
+        // store would also write the rows past its end.
+        const int part = warp & 3;
+        const int row = part * 32 + lane;
+        const int tok_local = row / G;
+        const uint32_t lane_addr = uint32_t(part * 32) << 16;
+        const float c = p.scale_log2;
+        const bool storer = warp == 8 && lane == 0;
+        uint8_t* srow = smem + L::STAGE + row * 128;
+        Item im;
+        int round = 0;
+        uint32_t g = 0, done = 0;
+        for (; next_item(p, round, im); ++round, ++done) {
+            const int head = im.kvh * G + row % G;
+            const bool row_valid = tok_local < im.q_count;
+            const int64_t token = int64_t(im.q_start) + tok_local;
+            // one decision for the four warps: the named barriers below are not bounded waits
+            const bool ready = mbar_wait(l_full, done & 1, ab, 214) && mbar_wait(pv_done, (g + im.n_tiles - 1) & 1, ab, 210);
+            if (!named_barrier_all(1, 128, ready)) break;
             tc_fence_after();
+            const float l = row_l[row], m_ref = row_m[row];
             const float inv = l > 0.f ? 1.f / l : 0.f;
             __nv_bfloat16* dst = p.out + (token * p.q_heads + head) * D;
-            uint8_t* srow = smem + L::STAGE + row * 128;
             const bool staged = im.q_count == ROWS / G;      // the same for every thread of the CTA
-            const bool storer = warp == 2 && lane == 0;
             // a tensor-memory load takes some hundred cycles to return: up to four are in flight per wait
             constexpr int EP = D < 128 ? D : 128;
 #pragma unroll 1
@@ -459,14 +502,10 @@ varlen_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 p.lse[int64_t(head) * p.tq + token] =
                     l > 0.f ? (m_ref * c + log2f(l)) * ln2 : -INFINITY;
             }
-            g += n_tiles;
-            round = round_nx;
-            have = item_at(p, round, im);     // round_nx already points at an item with keys, or past the end
-            rlo = rlo_nx;
-            rhi = rhi_nx;
+            g += im.n_tiles;
         }
         // the last stores have to have read the staging buffer before the CTA gives up its shared memory
-        if (warp == 2 && lane == 0) tma_store_wait_read();
+        if (storer) tma_store_wait_read();
     }
 
     // ---------------------------------------------------------------- teardown

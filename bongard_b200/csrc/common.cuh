@@ -166,6 +166,22 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void named_barrier(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
+// The same barrier, returning whether `ok` held in every one of the threads: lets a group of warps take one
+// decision after bounded waits that may have ended differently from thread to thread.
+__device__ __forceinline__ bool named_barrier_all(int id, int threads, bool ok) {
+    uint32_t all;
+    asm volatile(
+        "{\n"
+        ".reg .pred p, q;\n"
+        "setp.ne.u32 q, %1, 0;\n"
+        "bar.red.and.pred p, %2, %3, q;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(all)
+        : "r"(uint32_t(ok)), "r"(id), "r"(threads)
+        : "memory");
+    return all != 0;
+}
 
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
