@@ -47,8 +47,8 @@ from bongard_b200.clocks import ClockSampler  # noqa: E402
 METRIC = 'judged_questions_per_second'
 UNIT = 'questions/s'
 # DRAM bytes per algorithmic FLOP of the bf16 GEMM, measured by ncu on the 8192-token MLP GEMMs
-# ((337.5 + 565.1) MB over (0.859 + 0.429) TFLOP); a full-size launch is scaled by its FLOPs.
-GEMM_TRAFFIC_PER_FLOP = 7.0e-4
+# ((325.9 + 566.8) MB over (0.859 + 0.429) TFLOP); a full-size launch is scaled by its FLOPs.
+GEMM_TRAFFIC_PER_FLOP = 6.9e-4
 
 
 def parse():
