@@ -339,6 +339,10 @@ def op_level(device, pk):
     freqs = ops.inv_freq(256, 1e4, dev)
     ms = timed_loop(lambda: ops.qk_norm_rope_(qkv[:, :2048].view(t, 8, 256), qkv[:, 2048:3072].view(t, 4, 256), gain, gain,
                                               pos, freqs), seconds=0.2)
+    out['qk_norm_rope_sincos'] = {'ms': ms, 'gbs': 2 * t * 3072 * 2 / ms / 1e6, 'frac_of_hbm_peak': 2 * t * 3072 * 2 / ms / 1e6 / pk['hbm']}
+    table = ops.rope_table(256, 1e4, 4096, dev)      # the form the packed engine runs: angles from a per-position table
+    ms = timed_loop(lambda: ops.qk_norm_rope_(qkv[:, :2048].view(t, 8, 256), qkv[:, 2048:3072].view(t, 4, 256), gain, gain,
+                                              pos, None, table=table), seconds=0.2)
     out['qk_norm_rope'] = {'ms': ms, 'gbs': 2 * t * 3072 * 2 / ms / 1e6, 'frac_of_hbm_peak': 2 * t * 3072 * 2 / ms / 1e6 / pk['hbm']}
     out['clocks'] = sampler.stop()
     out['peaks'] = {'bf16_burst_tflops': pk['burst'], 'hbm_gbs': pk['hbm'], 'source': pk['source']}

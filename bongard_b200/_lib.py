@@ -28,6 +28,7 @@ SIGNATURES = {
     'bg_embed_f32': ([P, P, P, P, I64, I64, F32, I64, I64, P], INT),
     'bg_qk_norm_rope': ([P, I64, INT, P, I64, INT, P, P, P, P, I64, INT, F32, INT, P], INT),
     'bg_qk_norm_rope_table': ([P, I64, INT, P, I64, INT, P, P, P, P, I64, INT, F32, P], INT),
+    'bg_qk_norm_rope_cached': ([P, I64, INT, P, I64, INT, P, P, P, P, I64, I64, INT, F32, P], INT),
     'bg_embed': ([P, P, P, P, I64, I64, F32, I64, I64, P], INT),
     'bg_gemm_bf16': ([P, I64, P, I64, P, I64, I64, I64, I64, INT, P], INT),
     'bg_transpose_bf16': ([P, I64, P, I64, I64, I64, P], INT),

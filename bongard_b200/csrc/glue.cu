@@ -339,7 +339,8 @@ __global__ void qk_norm_rope_kernel(__nv_bfloat16* __restrict__ q, int64_t ldq, 
                                     const __nv_bfloat16* __restrict__ qw, const __nv_bfloat16* __restrict__ kw,
                                     const int32_t* __restrict__ positions, const float* __restrict__ inv_freq,
                                     const __nv_bfloat16* __restrict__ cos_table,
-                                    const __nv_bfloat16* __restrict__ sin_table, int64_t tokens, float eps,
+                                    const __nv_bfloat16* __restrict__ sin_table,
+                                    const float2* __restrict__ angle_table, int angle_rows, int64_t tokens, float eps,
                                     int rotate) {
     pdl_wait();
     pdl_launch_dependents();
@@ -360,6 +361,18 @@ __global__ void qk_norm_rope_kernel(__nv_bfloat16* __restrict__ q, int64_t ldq, 
             sn[e] = __bfloat162float(sin_table[token * D + first + e]);
             cs2[e] = __bfloat162float(cos_table[token * D + D / 2 + first + e]);
             sn2[e] = __bfloat162float(sin_table[token * D + D / 2 + first + e]);
+        }
+    } else if (rotate && angle_table != nullptr) {
+        // (cos, sin) of position * inv_freq, computed once per position by rope_table_kernel with the same
+        // expression as below: the same bits without 4 sincosf per lane and token
+        int pos = positions[token];
+        pos = pos < 0 ? 0 : (pos >= angle_rows ? angle_rows - 1 : pos);
+        const float2* row = angle_table + int64_t(pos) * (D / 2) + first;
+#pragma unroll
+        for (int e = 0; e < HE; ++e) {
+            const float2 a = __ldg(row + e);
+            cs[e] = cs2[e] = a.x;
+            sn[e] = sn2[e] = a.y;
         }
     } else if (rotate) {
         const float pos = float(positions[token]);
@@ -784,8 +797,9 @@ int bg_add_rmsnorm_mxfp8(const void* y, const void* w_post, void* resid, const v
 
 static int qk_norm_rope_launch(void* q, int64_t ldq, int q_heads, void* k, int64_t ldk, int k_heads,
                                const void* q_weight, const void* k_weight, const int32_t* positions,
-                               const float* inv_freq, const void* cos_table, const void* sin_table, int64_t tokens,
-                               int head_dim, float eps, int rotate, void* stream) {
+                               const float* inv_freq, const void* cos_table, const void* sin_table,
+                               const float* angle_table, int64_t angle_rows, int64_t tokens, int head_dim, float eps,
+                               int rotate, void* stream) {
     if (tokens < 0 || (head_dim != 64 && head_dim != 128 && head_dim != 256) || q_heads < 0 || k_heads < 0) {
         bg_set_error("bg_qk_norm_rope: head_dim must be 64, 128 or 256 (got %d)", head_dim);
         return BG_ERR_SHAPE;
@@ -807,13 +821,13 @@ static int qk_norm_rope_launch(void* q, int64_t ldq, int q_heads, void* k, int64
     if (qp == nullptr) q_heads = 0;
     if (head_dim == 64)
         launch_kernel(qk_norm_rope_kernel<64>, dim3(grid), dim3(warps * 32), 0, s, 0, qp, ldq, q_heads, kp, ldk, k_heads, qw, kw, positions,
-                                                             inv_freq, ct, st, tokens, eps, rotate);
+                                                             inv_freq, ct, st, reinterpret_cast<const float2*>(angle_table), (int)angle_rows, tokens, eps, rotate);
     else if (head_dim == 128)
         launch_kernel(qk_norm_rope_kernel<128>, dim3(grid), dim3(warps * 32), 0, s, 0, qp, ldq, q_heads, kp, ldk, k_heads, qw, kw, positions,
-                                                              inv_freq, ct, st, tokens, eps, rotate);
+                                                              inv_freq, ct, st, reinterpret_cast<const float2*>(angle_table), (int)angle_rows, tokens, eps, rotate);
     else
         launch_kernel(qk_norm_rope_kernel<256>, dim3(grid), dim3(warps * 32), 0, s, 0, qp, ldq, q_heads, kp, ldk, k_heads, qw, kw, positions,
-                                                              inv_freq, ct, st, tokens, eps, rotate);
+                                                              inv_freq, ct, st, reinterpret_cast<const float2*>(angle_table), (int)angle_rows, tokens, eps, rotate);
     return check_launch("bg_qk_norm_rope");
 }
 
@@ -821,7 +835,21 @@ int bg_qk_norm_rope(void* q, int64_t ldq, int q_heads, void* k, int64_t ldk, int
                     const void* k_weight, const int32_t* positions, const float* inv_freq, int64_t tokens,
                     int head_dim, float eps, int rotate, void* stream) {
     return qk_norm_rope_launch(q, ldq, q_heads, k, ldk, k_heads, q_weight, k_weight, positions, inv_freq, nullptr,
-                               nullptr, tokens, head_dim, eps, rotate, stream);
+                               nullptr, nullptr, 0, tokens, head_dim, eps, rotate, stream);
+}
+
+// The same operation with the angles read from a table made by bg_rope_table ([rows, head_dim / 2] pairs
+// (cos, sin) of position * inv_freq; positions are clamped to the table): bit-identical results.
+int bg_qk_norm_rope_cached(void* q, int64_t ldq, int q_heads, void* k, int64_t ldk, int k_heads, const void* q_weight,
+                           const void* k_weight, const int32_t* positions, const float* rope_table,
+                           int64_t table_rows, int64_t tokens, int head_dim, float eps, void* stream) {
+    if (positions == nullptr || rope_table == nullptr || table_rows <= 0 ||
+        (reinterpret_cast<uintptr_t>(rope_table) & 7)) {
+        bg_set_error("bg_qk_norm_rope_cached: positions and an 8-byte aligned table with at least one row are required");
+        return BG_ERR_SHAPE;
+    }
+    return qk_norm_rope_launch(q, ldq, q_heads, k, ldk, k_heads, q_weight, k_weight, positions, nullptr, nullptr,
+                               nullptr, rope_table, table_rows, tokens, head_dim, eps, 1, stream);
 }
 
 int bg_qk_norm_rope_table(void* q, int64_t ldq, int q_heads, void* k, int64_t ldk, int k_heads,
@@ -832,7 +860,7 @@ int bg_qk_norm_rope_table(void* q, int64_t ldq, int q_heads, void* k, int64_t ld
         return BG_ERR_SHAPE;
     }
     return qk_norm_rope_launch(q, ldq, q_heads, k, ldk, k_heads, q_weight, k_weight, nullptr, nullptr, cos_table,
-                               sin_table, tokens, head_dim, eps, 1, stream);
+                               sin_table, nullptr, 0, tokens, head_dim, eps, 1, stream);
 }
 
 int bg_rope_table(float* table, int64_t rows, int head_dim, const float* inv_freq, void* stream) {

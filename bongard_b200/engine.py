@@ -235,7 +235,10 @@ class JudgmentEngine:
             k = qkv[:, qd:qd + kd].view(t, s.kv_heads, s.head_dim)
             v = qkv[:, qd + kd:].view(t, s.kv_heads, s.head_dim)
             if not fused:
-                ops.qk_norm_rope_(q, k, lw.q_norm, lw.k_norm, pack.positions, self._freqs(index), s.eps)
+                # with the positions' bound known, the angles come from a per-(theta) table of the same values
+                table = (ops.rope_table(s.head_dim, s.layer_theta(index), pack.longest, self.device)
+                         if pack.longest > 0 else None)
+                ops.qk_norm_rope_(q, k, lw.q_norm, lw.k_norm, pack.positions, self._freqs(index), s.eps, table=table)
             a = ops.varlen_attention(q, k, v, pack.plans[pack.keys[index]], s.scale,
                                      None if cross is None else cross[index])
             # (not on the latency path, whose few-row weight-streaming GEMM writes bf16)

@@ -200,6 +200,9 @@ def glue(args, flush):
     freqs = ops.inv_freq(256, 1e4, DEV)
     ms = timed(lambda: ops.qk_norm_rope_(q, k, gain, gain, positions, freqs), args.iters, args.warmup, flush)
     out.append(dict(op='qk_norm_rope', tokens=t, ms=ms, gbs=2 * t * 3072 * 2 / ms / 1e6))
+    table = ops.rope_table(256, 1e4, 4096, DEV)
+    ms = timed(lambda: ops.qk_norm_rope_(q, k, gain, gain, positions, None, table=table), args.iters, args.warmup, flush)
+    out.append(dict(op='qk_norm_rope_angle_table', tokens=t, ms=ms, gbs=2 * t * 3072 * 2 / ms / 1e6))
     # backward of the two norms: input + upstream gradient in, input gradient out
     ms = timed(lambda: ops.rmsnorm_backward(x, w, y), args.iters, args.warmup, flush)
     out.append(dict(op='rmsnorm_backward', tokens=t, ms=ms, gbs=3 * t * h * 2 / ms / 1e6))

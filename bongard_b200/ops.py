@@ -126,9 +126,25 @@ def inv_freq(head_dim, theta, device):
     return value.to(device)
 
 
-def qk_norm_rope_(q, k, q_weight, k_weight, positions, freqs, eps=1e-6, rotate=True):
-    """In place on q [T,Hq,D] and k [T,Hkv,D] (views with a token stride are fine)."""
+def qk_norm_rope_(q, k, q_weight, k_weight, positions, freqs, eps=1e-6, rotate=True, table=None):
+    """In place on q [T,Hq,D] and k [T,Hkv,D] (views with a token stride are fine).  `table` (from
+    rope_table, covering every position in use) replaces the per-token sincosf by a lookup of the same
+    values; `freqs` is then not read."""
     lib = _lib.load()
+    if rotate and table is not None:
+        tokens, head_dim = q.shape[0], q.shape[-1]
+        for t, name in ((q, 'q'), (k, 'k')):
+            _need(t, name)
+            if t.stride(-1) != 1 or t.stride(1) != head_dim:
+                raise ValueError(f'{name} heads must be contiguous [T, heads, D]')
+        _need(positions, 'positions', torch.int32), _need(table, 'rope table', torch.float32)
+        if table.shape[1:] != (head_dim // 2, 2) or not table.is_contiguous() or positions.numel() != tokens:
+            raise ValueError('the table must be [rows, head_dim/2, 2] and positions must have one entry per token')
+        _lib.check(lib.bg_qk_norm_rope_cached(_ptr(q), q.stride(0), q.shape[1], _ptr(k), k.stride(0), k.shape[1],
+                                              _ptr(_need(q_weight, 'q_weight')), _ptr(_need(k_weight, 'k_weight')),
+                                              _ptr(positions), _ptr(table), table.shape[0], tokens, head_dim, eps,
+                                              _stream()), 'bg_qk_norm_rope_cached')
+        return
     ref = q if q is not None else k
     tokens, head_dim = ref.shape[0], ref.shape[-1]
     for t, name in ((q, 'q'), (k, 'k')):

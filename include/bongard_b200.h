@@ -100,6 +100,14 @@ int bg_qk_norm_rope_table(void* q, int64_t ldq, int q_heads, void* k, int64_t ld
                           const void* q_weight, const void* k_weight, const void* cos_table, const void* sin_table,
                           int64_t tokens, int head_dim, float eps, void* stream);
 
+/* bg_qk_norm_rope with the angles read from a table made by bg_rope_table ([table_rows, head_dim / 2]
+ * pairs (cos, sin) of position * inv_freq in fp32; positions are clamped to the table) instead of
+ * four sincosf per lane and token: bit-identical results.  Same reference surface as bg_qk_norm_rope
+ * (bongard/attention.py:172-180 project_qk with the rotary module's angles, HF:147-166). */
+int bg_qk_norm_rope_cached(void* q, int64_t ldq, int q_heads, void* k, int64_t ldk, int k_heads, const void* q_weight,
+                           const void* k_weight, const int32_t* positions, const float* rope_table,
+                           int64_t table_rows, int64_t tokens, int head_dim, float eps, void* stream);
+
 /* out[r, :] = table[ids[r], :] * scale, or eoi_embedding where ids[r] == eoi_token.  ids int64.
  * Replaces HF:644-647 T5Gemma2TextScaledWordEmbedding.forward. */
 int bg_embed(const int64_t* ids, const void* table, const void* eoi_embedding, void* out, int64_t rows, int64_t h,

@@ -116,6 +116,13 @@ def test_qk_norm_rope(d, hq, hkv, theta):
     assert_close(q, wq, atol=1.5e-2, rtol=8e-3)
     assert_close(k, wk, atol=1.5e-2, rtol=8e-3)
     assert torch.equal(buf[:, (hq + hkv) * d:].cpu(), qkv[:, (hq + hkv) * d:])   # v untouched
+    # angles from the per-position table: the same bits as the angles computed per token
+    buf3 = qkv.to(DEV).clone()
+    q3 = buf3[:, :hq * d].view(t, hq, d)
+    k3 = buf3[:, hq * d:(hq + hkv) * d].view(t, hkv, d)
+    ops.qk_norm_rope_(q3, k3, qw.to(DEV), kw.to(DEV), positions.int().to(DEV), None,
+                      table=ops.rope_table(d, theta, max(lengths), DEV))
+    assert torch.equal(buf3, buf)
     # normalise only (decoder state keys)
     buf2 = qkv.to(DEV).clone()
     k2 = buf2[:, hq * d:(hq + hkv) * d].view(t, hkv, d)
