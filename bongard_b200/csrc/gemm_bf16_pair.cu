@@ -497,9 +497,15 @@ static int pair_launch(PairParams p, const CUtensorMap& map_a, const CUtensorMap
     p.tiles_m = (int)((m + 2 * BM - 1) / (2 * BM));
     p.tiles_n = epilogue == 1 ? (int)(n / 128) : (int)((n + BN - 1) / BN);
     {
+        // Raster: the tiles of `group_m` row panels x all column panels run before the next group.  With many
+        // column panels (gate | up: 80) a group holds as many activation rows as stay in L2 (~40 MB) while the
+        // weight streams past once per group.  With few (the q|k|v, output and down projections: 10 - 16) one
+        // wave of the grid already spans several row panels, and small groups measured best (DRAM reads of the
+        // down projection at 32 768 rows: 2.8 GB with 7 panels per group, 2.0 - 2.2 GB with 2 - 4).
         const int64_t panel = int64_t(2 * BM) * k * 2;
         int64_t g = (40ll << 20) / (panel > 0 ? panel : 1);
         p.group_m = (int)(g < 4 ? 4 : (g > 32 ? 32 : g));
+        if (p.tiles_n < 32) p.group_m = k >= 8192 ? 3 : 4;
     }
     p.status = bg_status_word();
     if (!p.status) return BG_ERR_DRIVER;
