@@ -31,7 +31,7 @@ constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK, B_BYTES = BN * BK, STAGE_BYTES = A_BYTES + B_BYTES;   // 16 + 32 KB
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 constexpr int THREADS = 320;
-constexpr int GROUP_M = 16;
+constexpr int GROUP_M_NARROW = 4, GROUP_M_WIDE = 64;   // row panels per raster group
 
 struct Fp8Params {
     int m, n, k, epilogue;
@@ -40,14 +40,15 @@ struct Fp8Params {
     const float* a_inv;     // [k / 128, m]   (K-block major: coalesced per-row reads)
     const float* w_inv;     // [w_rows / 128, k / 128]
     int tiles_m, tiles_n;
+    int group_m;            // row panels per raster group
     int32_t* status;
 };
 
-__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
-    int per_group = GROUP_M * tiles_n;
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
+    int per_group = group_m * tiles_n;
     int group = tile / per_group;
-    int first_m = group * GROUP_M;
-    int rows = min(GROUP_M, tiles_m - first_m);
+    int first_m = group * group_m;
+    int rows = min(group_m, tiles_m - first_m);
     int in_group = tile - group * per_group;
     tm = first_m + in_group % rows;
     tn = in_group / rows;
@@ -100,7 +101,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             uint32_t phase = 0;
             for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
                 int tm, tn;
-                tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+                tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
                 const int w0 = p.epilogue == 1 ? tn * 128 : tn * BN;
                 const int w1 = p.epilogue == 1 ? p.n + tn * 128 : tn * BN + 128;
                 for (int kb = 0; kb < kblocks; ++kb) {
@@ -150,7 +151,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         uint32_t step = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
             int tm, tn;
-            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+            tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
             const int row = tm * BM + row_in_tile;
             const int safe_row = row < p.m ? row : p.m - 1;
             // weight scale rows of the two 128-column halves of this tile
@@ -393,6 +394,9 @@ int bg_gemm_fp8_block128(const void* aq, int64_t lda, const float* a_inv_t, cons
     p.a_inv = a_inv_t; p.w_inv = w_inv;
     p.tiles_m = (int)((m + BM - 1) / BM);
     p.tiles_n = epilogue == 1 ? (int)(n / 128) : (int)((n + BN - 1) / BN);
+    // raster: few column panels (down, q|k|v, output projections) -> small groups of row panels; many
+    // (gate | up) -> large ones (measured at 32 768 rows: down 1 918 -> 1 962 TFLOP/s with 4 instead of 16)
+    p.group_m = p.tiles_n < 32 ? GROUP_M_NARROW : GROUP_M_WIDE;
     p.status = bg_status_word();
     if (!p.status) return BG_ERR_DRIVER;
     static bool configured_on[kBgMaxDevices] = {};

@@ -36,7 +36,7 @@ constexpr int SF_OFFSET = STAGES * TILE_BYTES;
 constexpr int BAR_OFFSET = SF_OFFSET + STAGES * SF_BYTES;
 constexpr int SMEM_BYTES = BAR_OFFSET + 256 + 1024;
 constexpr int THREADS = 320;     // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue (two per TMEM lane quadrant)
-constexpr int GROUP_M = 16;
+constexpr int GROUP_M_NARROW = 4, GROUP_M_WIDE = 64;   // row panels per raster group
 constexpr int TMEM_SF = 256;      // scale columns behind the 256-column accumulator: per ring parity A at +0, W at +16
 
 struct MxParams {
@@ -48,14 +48,15 @@ struct MxParams {
     uint8_t* out_q;         // GeGLU epilogue only: emit the result as MXFP8 (values [m, n], row stride ldo bytes)
     uint8_t* out_sf;        //   and its scale atoms [ceil(m / 128)][n / 128][512]; null -> bf16 output
     int tiles_m, tiles_n;
+    int group_m;            // row panels per raster group
     int32_t* status;
 };
 
-__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
-    int per_group = GROUP_M * tiles_n;
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
+    int per_group = group_m * tiles_n;
     int group = tile / per_group;
-    int first_m = group * GROUP_M;
-    int rows = min(GROUP_M, tiles_m - first_m);
+    int first_m = group * group_m;
+    int rows = min(group_m, tiles_m - first_m);
     int in_group = tile - group * per_group;
     tm = first_m + in_group % rows;
     tn = in_group / rows;
@@ -140,7 +141,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             uint32_t phase = 0;
             for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
                 int tm, tn;
-                tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+                tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
                 // W rows: plain -> 256 consecutive output columns; GeGLU -> 128 gate rows + 128 up rows
                 const int w0 = p.epilogue == 1 ? tn * 128 : tn * BN;
                 const int w1 = p.epilogue == 1 ? p.n + tn * 128 : tn * BN + 128;
@@ -207,7 +208,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         int local = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
             int tm, tn;
-            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+            tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
             if (!mbar_wait(acc_full, local & 1, ab, 504)) break;
             tc_fence_after();
             const int row = tm * BM + row_in_tile;
@@ -445,6 +446,9 @@ static int gemm_mxfp8_launch(const void* aq, int64_t lda, const void* a_scales, 
     p.w_sf = static_cast<const uint8_t*>(w_scales);
     p.tiles_m = (int)((m + BM - 1) / BM);
     p.tiles_n = epilogue == 1 ? (int)(n / 128) : (int)((n + BN - 1) / BN);
+    // raster: few column panels (down, q|k|v, output projections) -> small groups of row panels; many
+    // (gate | up) -> large ones (measured at 32 768 rows: down 1 918 -> 1 962 TFLOP/s with 4 instead of 16)
+    p.group_m = p.tiles_n < 32 ? GROUP_M_NARROW : GROUP_M_WIDE;
     p.status = bg_status_word();
     if (!p.status) return BG_ERR_DRIVER;
     static bool configured_on[kBgMaxDevices] = {};
