@@ -71,7 +71,7 @@ def parse():
     ap.add_argument('--cpu-seconds', type=float, default=None,
                     help='CPU work per sample (default: 15 s, less when many steps are asked for)')
     ap.add_argument('--encoder-pack-tokens', type=int, default=65536)
-    ap.add_argument('--decoder-pack-tokens', type=int, default=16384)
+    ap.add_argument('--decoder-pack-tokens', type=int, default=32768)
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-extras', action='store_true', help='skip the strong / long_context / ops keys')
     ap.add_argument('--extra-steps', type=int, default=2, help='timed steps of the strong and long_context runs')

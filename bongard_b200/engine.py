@@ -66,7 +66,7 @@ class JudgmentEngine:
     """A full replica of the judgment model on one GPU."""
 
     def __init__(self, weights, shape: ModelShape, device='cuda', *, encoder_pack_tokens=65536,
-                 decoder_pack_tokens=16384, linears='bf16', residual=None, wide_outputs=True):
+                 decoder_pack_tokens=32768, linears='bf16', residual=None, wide_outputs=True):
         ops.device_check()
         if linears not in ('bf16', 'fp8', 'mxfp8'):
             raise ValueError("linears must be 'bf16', 'fp8' or 'mxfp8'")
