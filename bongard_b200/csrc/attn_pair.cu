@@ -22,7 +22,7 @@
 // Barriers sit at the same offset in both CTAs.  Used in the leader (rank 0) only, credited by both
 // CTAs: q_full, k_full[], v_full[] (TMA bytes), p_full (8 warp arrivals).  One per CTA, signalled by
 // the leader's MMA thread with one commit per CTA: s_full[], k_empty[], v_empty[], pv_done.
-// No TMA load uses cluster multicast: each CTA fetches its own halves.
+// Every TMA load has one destination: each CTA fetches its own halves.
 #include "common.cuh"
 
 namespace {
