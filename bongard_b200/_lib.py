@@ -62,6 +62,7 @@ SIGNATURES = {
     'bg_linear_fp8_static_max_bytes': ([], I64),
     'bg_linear_fp8_static': ([P, I64, P, I64, P, P, I64, I64, I64, I64, INT, P], INT),
     'bg_attention_tile_rows': ([INT], INT),
+    'bg_attention_item_index': ([INT, INT, INT], INT),
     'bg_attention_pair_tile_rows': ([INT], INT),
     'bg_varlen_attention': ([P, I64, I64, P, P, I64, I64, P, P, I64, I64, P, P, P, I32, P, P, I64, I64, I64, INT, INT, INT,
                              F32, P], INT),

@@ -88,9 +88,11 @@ struct Item {
 // The i-th item of this CTA.  Items are numbered tile-major (the KV heads of one tile side by side) over the
 // plan's heaviest-first tile list and dealt to the CTAs in rounds, every other round in reverse order, so that
 // each CTA gets one item of every weight band and the light end of one band follows the heavy end of the last.
+__host__ __device__ __forceinline__ int item_index(int grid, int cta, int round) {
+    return round * grid + ((round & 1) ? grid - 1 - cta : cta);
+}
 __device__ __forceinline__ bool item_at(const AttnParams& p, int round, Item& im) {
-    const int G = int(gridDim.x);
-    const int it = round * G + ((round & 1) ? G - 1 - int(blockIdx.x) : int(blockIdx.x));
+    const int it = item_index(int(gridDim.x), int(blockIdx.x), round);
     if (it >= p.n_items) return false;
     const int tile = it / p.kv_heads;
     const int32_t* t = p.tiles + int64_t(tile) * 8;
@@ -556,6 +558,13 @@ int kv_map(CUtensorMap* map, const void* base, int64_t tokens, int heads, int d,
 }
 
 }  // namespace
+
+// Which work item (tile record * kv_heads + KV head) CTA `cta` of a grid of `grid` persistent CTAs takes in its
+// `round`-th turn; the CTA is done at the first index that is not below tile records x KV heads.  Host-side
+// mirror of the kernel's dealing rule, for tests and for callers that want to predict the balance of a plan.
+extern "C" int bg_attention_item_index(int grid, int cta, int round) {
+    return (grid <= 0 || cta < 0 || cta >= grid || round < 0) ? -1 : item_index(grid, cta, round);
+}
 
 // Query rows one tile of bg_varlen_attention covers (128 for every supported head size).
 // A tile record may hold up to this many rows / (q_heads / kv_heads) consecutive tokens.

@@ -305,6 +305,12 @@ int bg_linear_fp8_static(const void* x, int64_t ldx, const void* wq, int64_t ldw
  * windowed layers bongard/packing.py:154-175 packed_attention serves, and the two-partition
  * serving path bongard/attention.py:122-169. */
 int bg_attention_tile_rows(int head_dim);
+
+/* The persistent attention kernel's dealing rule: the work item (tile record * kv_heads + KV head) that
+ * CTA `cta` of `grid` CTAs takes in its `round`-th turn (a CTA stops at the first index that is not
+ * below tile records x kv_heads); -1 for arguments out of range.  Host code only (no device work);
+ * no counterpart in the reference, whose kernels are scheduled by their libraries. */
+int bg_attention_item_index(int grid, int cta, int round);
 int bg_varlen_attention(const void* q, int64_t ldq, int64_t hsq, const void* k, const void* v, int64_t ldkv,
                         int64_t hskv, const void* ck, const void* cv, int64_t ldc, int64_t hsc, void* out,
                         float* lse, const int32_t* tiles,

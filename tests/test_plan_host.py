@@ -97,3 +97,32 @@ def test_reference_packing_dispatch_binds_without_editing():
     assert module.packed_layout([2], [None], torch.device('cpu'), backend='triton') == 'native' and calls == ['triton']
     ours = module.packed_layout([2, 3], [None], torch.device('cpu'), backend='b200')
     assert isinstance(ours, packing.PackedLayout) and ours.lengths == (2, 3)
+
+
+@pytest.mark.parametrize('grid,items', [(148, 2272), (148, 148), (148, 149), (148, 5), (7, 100), (1, 9), (148, 12432)])
+def test_attention_items_are_dealt_once_and_evenly(grid, items):
+    """The persistent attention kernel's dealing rule (csrc/attn.cu item_index), through its host-side
+    mirror: every work item goes to exactly one CTA, no CTA gets more than one item more than another, and
+    over the heaviest-first list consecutive rounds run in opposite directions (the CTA that took the
+    heaviest item of one round takes the lightest of the next)."""
+    from bongard_b200 import _lib
+    lib = _lib.load()
+    ctas = min(grid, items)            # the launcher never starts more CTAs than items
+    seen, per_cta = [], []
+    for cta in range(ctas):
+        mine, rnd = [], 0
+        while True:
+            it = lib.bg_attention_item_index(ctas, cta, rnd)
+            assert it >= 0
+            if it >= items:
+                break
+            mine.append(it)
+            rnd += 1
+        assert mine == sorted(mine)
+        seen += mine
+        per_cta.append(len(mine))
+    assert sorted(seen) == list(range(items))
+    assert max(per_cta) - min(per_cta) <= 1
+    if items >= 2 * ctas:
+        assert lib.bg_attention_item_index(ctas, 0, 0) == 0 and lib.bg_attention_item_index(ctas, 0, 1) == 2 * ctas - 1
+    assert lib.bg_attention_item_index(ctas, ctas, 0) == -1 and lib.bg_attention_item_index(0, 0, 0) == -1
