@@ -81,6 +81,24 @@ def test_encoder_random(d, hq, hkv, window):
     assert_close(lse, want_lse, atol=2e-2, rtol=1e-3)
 
 
+@pytest.mark.parametrize('d,hq,hkv', [(256, 8, 4), (64, 4, 2)])
+def test_many_short_items_per_persistent_cta(d, hq, hkv):
+    """Thousands of work items with one or two key tiles each, mixed with a few long ones: every persistent CTA
+    walks through many items whose first S is also their last, full and partial tiles alternate, and the
+    barrier phases run on across all of them."""
+    gen = torch.Generator().manual_seed(5)
+    lengths = torch.randint(1, 150, (900,), generator=gen).tolist()
+    for i in range(0, 900, 97):
+        lengths[i] = 600 + i                       # a few items with 5 - 12 key tiles in between
+    t = sum(lengths)
+    q, k, v = rnd(t, hq, d, seed=21), rnd(t, hkv, d, seed=22), rnd(t, hkv, d, seed=23)
+    scale = d ** -0.5
+    out, lse = run(q, k, v, lengths, scale, None, lse=True)
+    want, want_lse = om.varlen_attention(q.float(), k.float(), v.float(), lengths, scale, None)
+    assert_close(out, want)
+    assert_close(lse, want_lse, atol=2e-2, rtol=1e-3)
+
+
 @pytest.mark.parametrize('d,hq,hkv', [(64, 4, 2), (256, 8, 4)])
 @pytest.mark.parametrize('window', [None, 1024, 20])
 def test_decoder_random(d, hq, hkv, window):
